@@ -1,0 +1,466 @@
+// Host orchestration of the engine: workspace lifetime, per-layer forward/backward
+// scheduling, gradient buffer, data-parallel reduction and the C ABI.
+//
+// Role in the reference: src/lstm.cu (buffer object :192-319, forward entry :1897-2148) and the
+// host loops of flashlstm_v2/src/lstm_forward.cu:464-966 / lstm_backward.cu:643-1250.  Unlike
+// those, nothing is allocated, registered or re-packed per call: the handle owns a workspace
+// sized at creation, weights are packed when they are set, and all work is enqueued
+// asynchronously on the caller's stream.
+#include "engine.h"
+
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace flstm_b200 {
+
+std::string &last_error_slot() {
+    static thread_local std::string slot;
+    return slot;
+}
+
+int set_error(int status, const char *fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    last_error_slot() = buf;
+    return status;
+}
+
+namespace {
+
+template <typename P>
+int dev_alloc(P **p, size_t bytes) {
+    *p = nullptr;
+    if (bytes == 0) return FLSTM_OK;
+    void *raw = nullptr;
+    cudaError_t e = cudaMalloc(&raw, bytes);
+    if (e != cudaSuccess)
+        return set_error(FLSTM_ERR_CUDA, "cudaMalloc(%zu bytes) failed: %s", bytes, cudaGetErrorString(e));
+    *p = static_cast<P *>(raw);
+    return FLSTM_OK;
+}
+
+template <typename P>
+void dev_free(P *&p) {
+    if (p) cudaFree(p);
+    p = nullptr;
+}
+
+inline char *byte_ptr(void *p) { return static_cast<char *>(p); }
+inline const char *byte_ptr(const void *p) { return static_cast<const char *>(p); }
+
+}  // namespace
+
+Engine::~Engine() {
+    tc::destroy(*this);
+    release_time_buffers();
+    for (auto &l : layers) {
+        dev_free(l.w_ih);
+        dev_free(l.w_hh);
+        dev_free(l.w_ih_t);
+        dev_free(l.w_hh_t);
+        dev_free(l.bias);
+    }
+    dev_free(grads);
+    dev_free(dc);
+    dev_free(db_part);
+    dev_free(sync_words);
+    if (comm) comm_destroy(comm);
+    if (comm_stream) cudaStreamDestroy(comm_stream);
+    if (comm_fork) cudaEventDestroy(comm_fork);
+    if (comm_join) cudaEventDestroy(comm_join);
+}
+
+void Engine::release_time_buffers() {
+    for (auto &l : layers) {
+        dev_free(l.gates);
+        dev_free(l.hs);
+        dev_free(l.cs);
+        dev_free(l.dg);
+        dev_free(l.dx);
+        dev_free(l.dg_t);
+        dev_free(l.xh_t);
+    }
+    t_cap = 0;
+}
+
+int Engine::allocate(size_t cap) {
+    const size_t B = cfg.batch, H = cfg.hidden_size, es = dtype_size(cfg.dtype);
+    const bool tcp = backend == FLSTM_BACKEND_TC;
+    for (size_t li = 0; li < layers.size(); ++li) {
+        auto &l = layers[li];
+        FLSTM_TRY(dev_alloc(&l.gates, cap * B * 4 * H * es));
+        FLSTM_TRY(dev_alloc(&l.hs, (cap + 1) * B * H * es));
+        FLSTM_TRY(dev_alloc(&l.cs, (cap + 1) * B * H * sizeof(float)));
+        if (cfg.training) {
+            FLSTM_TRY(dev_alloc(&l.dg, cap * B * 4 * H * es));
+            if (li > 0) FLSTM_TRY(dev_alloc(&l.dx, cap * B * l.in_size * es));
+            if (tcp) {
+                FLSTM_TRY(dev_alloc(&l.dg_t, cap * B * 4 * H * es));
+                FLSTM_TRY(dev_alloc(&l.xh_t, cap * B * (l.in_size + H) * es));
+            }
+        }
+    }
+    t_cap = cap;
+    if (tcp) FLSTM_TRY(tc::on_capacity_change(*this));
+    return FLSTM_OK;
+}
+
+int Engine::ensure_capacity(size_t T) {
+    if (T <= t_cap) return FLSTM_OK;
+    // The reference grows its buffers when a call brings a longer sequence (src/lstm.cu:933-970).
+    FLSTM_CUDA_TRY(cudaDeviceSynchronize());
+    release_time_buffers();
+    last_T = 0;
+    return allocate(T);
+}
+
+int Engine::set_weights(int layer, const float *w_ih, const float *w_hh, const float *b_ih, const float *b_hh,
+                        cudaStream_t s) {
+    if (layer < 0 || layer >= (int)layers.size()) return set_error(FLSTM_ERR_INVALID, "layer %d out of range", layer);
+    if (!w_ih || !w_hh || !b_ih || !b_hh) return set_error(FLSTM_ERR_INVALID, "null parameter pointer");
+    auto &l = layers[layer];
+    const size_t H = cfg.hidden_size;
+    if (backend == FLSTM_BACKEND_TC) {
+        FLSTM_TRY(tc::set_weights(*this, layer, w_ih, w_hh, b_ih, b_hh, s));
+        launches += 5;
+    } else {
+        FLSTM_TRY(simt::convert(FLSTM_DTYPE_F32, w_ih, cfg.dtype, l.w_ih, 4 * H * l.in_size, s));
+        FLSTM_TRY(simt::convert(FLSTM_DTYPE_F32, w_hh, cfg.dtype, l.w_hh, 4 * H * H, s));
+        FLSTM_TRY(simt::bias_sum(b_ih, b_hh, l.bias, 4 * H, s));
+        launches += 3;
+    }
+    l.weights_set = true;
+    return FLSTM_OK;
+}
+
+int Engine::forward(size_t T, const void *x, const void *h0, const void *c0, void *y, void *hn, void *cn,
+                    cudaStream_t s) {
+    const size_t B = cfg.batch, H = cfg.hidden_size, es = dtype_size(cfg.dtype);
+    if (T == 0 || B == 0 || H == 0) return FLSTM_OK;  // zero-sized problem: silent no-op (lstm_forward.cu:493-495)
+    if (!x) return set_error(FLSTM_ERR_INVALID, "x is null");
+    for (auto &l : layers)
+        if (!l.weights_set) return set_error(FLSTM_ERR_INVALID, "weights have not been set for every layer");
+    FLSTM_TRY(ensure_capacity(T));
+    timer.reset();
+    x_saved = x;
+    const int L = (int)layers.size();
+    for (int li = 0; li < L; ++li) {
+        auto &l = layers[li];
+        const size_t slab = B * H;
+        // initial state -> slot 0 of the state tensors
+        if (h0) FLSTM_CUDA_TRY(cudaMemcpyAsync(l.hs, byte_ptr(h0) + li * slab * es, slab * es, cudaMemcpyDeviceToDevice, s));
+        else FLSTM_CUDA_TRY(cudaMemsetAsync(l.hs, 0, slab * es, s));
+        const size_t ces = cell_io_f32 ? sizeof(float) : es;
+        if (c0) { FLSTM_TRY(simt::convert(cell_io_f32 ? FLSTM_DTYPE_F32 : cfg.dtype, byte_ptr(c0) + li * slab * ces, FLSTM_DTYPE_F32, l.cs, slab, s)); ++launches; }
+        else FLSTM_CUDA_TRY(cudaMemsetAsync(l.cs, 0, slab * sizeof(float), s));
+
+        const void *x_l = li == 0 ? x : byte_ptr(layers[li - 1].hs) + slab * es;
+        void *y_out = (li == L - 1) ? y : nullptr;
+        if (backend == FLSTM_BACKEND_TC) {
+            FLSTM_TRY(tc::forward_layer(*this, li, T, x_l, y_out, s));
+        } else {
+            // input projection for all steps at once: P = X W_ih^T + (b_ih + b_hh)
+            size_t m0 = timer.mark(s);
+            FLSTM_TRY(simt::gemm(cfg.dtype, cfg.dtype, T * B, 4 * H, l.in_size, x_l, l.in_size, true, l.w_ih,
+                                 l.in_size, true, l.gates, 4 * H, l.bias, s));
+            ++launches;
+            size_t m1 = timer.mark(s);
+            for (size_t t = 0; t < T; ++t) {
+                FLSTM_TRY(simt::step_forward(cfg.dtype, B, H, byte_ptr(l.hs) + t * slab * es, l.w_hh,
+                                             byte_ptr(l.gates) + t * B * 4 * H * es, l.cs + t * slab,
+                                             l.cs + (t + 1) * slab, byte_ptr(l.hs) + (t + 1) * slab * es,
+                                             y_out ? byte_ptr(y_out) + t * slab * es : nullptr, s));
+            }
+            launches += T;
+            size_t m2 = timer.mark(s);
+            timer.span(PH_PROJ, m0, m1);
+            timer.span(PH_RECUR_FWD, m1, m2);
+        }
+        if (hn) FLSTM_CUDA_TRY(cudaMemcpyAsync(byte_ptr(hn) + li * slab * es, byte_ptr(l.hs) + T * slab * es, slab * es, cudaMemcpyDeviceToDevice, s));
+        if (cn) { FLSTM_TRY(simt::convert(FLSTM_DTYPE_F32, l.cs + T * slab, cell_io_f32 ? FLSTM_DTYPE_F32 : cfg.dtype, byte_ptr(cn) + li * slab * ces, slab, s)); ++launches; }
+    }
+    last_T = T;
+    return FLSTM_OK;
+}
+
+int Engine::backward(size_t T, const void *dy, const void *dhn, const void *dcn, void *dx, float *dh0,
+                     float *dc0, cudaStream_t s) {
+    const size_t B = cfg.batch, H = cfg.hidden_size, es = dtype_size(cfg.dtype);
+    if (T == 0 || B == 0 || H == 0) return FLSTM_OK;
+    if (!cfg.training) return set_error(FLSTM_ERR_INVALID, "engine was created with training = 0");
+    if (last_T != T) return set_error(FLSTM_ERR_INVALID, "backward(T=%zu) does not follow a forward of the same length (last T=%zu)", T, last_T);
+    if (!dy) return set_error(FLSTM_ERR_INVALID, "dy is null");
+    const int L = (int)layers.size();
+    const size_t slab = B * H;
+    for (int li = L - 1; li >= 0; --li) {
+        auto &l = layers[li];
+        const void *x_l = li == 0 ? x_saved : byte_ptr(layers[li - 1].hs) + slab * es;
+        const void *dy_l = (li == L - 1) ? dy : layers[li + 1].dx;
+        void *dx_l = li == 0 ? dx : l.dx;
+        const void *dhn_l = dhn ? byte_ptr(dhn) + li * slab * es : nullptr;
+        const void *dcn_l = dcn ? byte_ptr(dcn) + li * slab * es : nullptr;
+        float *dh0_l = dh0 ? dh0 + li * slab : nullptr;
+        float *dc0_l = dc0 ? dc0 + li * slab : nullptr;
+        if (backend == FLSTM_BACKEND_TC) {
+            FLSTM_TRY(tc::backward_layer(*this, li, T, x_l, dy_l, dhn_l, dcn_l, dx_l, dh0_l, dc0_l, s));
+        } else {
+            size_t m0 = timer.mark(s);
+            if (dcn_l) { FLSTM_TRY(simt::convert(cfg.dtype, dcn_l, FLSTM_DTYPE_F32, dc, slab, s)); ++launches; }
+            else FLSTM_CUDA_TRY(cudaMemsetAsync(dc, 0, slab * sizeof(float), s));
+            for (size_t step = 0; step < T; ++step) {
+                size_t t = T - 1 - step;
+                const void *dg_next = (t == T - 1) ? nullptr : byte_ptr(l.dg) + (t + 1) * B * 4 * H * es;
+                FLSTM_TRY(simt::step_backward(cfg.dtype, B, H, dg_next, l.w_hh, dhn_l,
+                                              byte_ptr(dy_l) + t * slab * es,
+                                              byte_ptr(l.gates) + t * B * 4 * H * es, l.cs + (t + 1) * slab,
+                                              l.cs + t * slab, dc, byte_ptr(l.dg) + t * B * 4 * H * es, s));
+            }
+            launches += T;
+            if (dh0_l) { FLSTM_TRY(simt::final_dh(cfg.dtype, B, H, l.dg, l.w_hh, dh0_l, s)); ++launches; }
+            if (dc0_l) FLSTM_CUDA_TRY(cudaMemcpyAsync(dc0_l, dc, slab * sizeof(float), cudaMemcpyDeviceToDevice, s));
+            size_t m1 = timer.mark(s);
+            // deferred parameter gradients over the whole sequence
+            FLSTM_TRY(simt::gemm(cfg.dtype, FLSTM_DTYPE_F32, 4 * H, l.in_size, T * B, l.dg, 4 * H, false, x_l,
+                                 l.in_size, false, l.dw_ih, l.in_size, nullptr, s));
+            FLSTM_TRY(simt::gemm(cfg.dtype, FLSTM_DTYPE_F32, 4 * H, H, T * B, l.dg, 4 * H, false, l.hs, H, false,
+                                 l.dw_hh, H, nullptr, s));
+            FLSTM_TRY(simt::column_sum(cfg.dtype, l.dg, T * B, 4 * H, l.db, s));
+            launches += 3;
+            size_t m2 = timer.mark(s);
+            if (dx_l) {
+                FLSTM_TRY(simt::gemm(cfg.dtype, cfg.dtype, T * B, l.in_size, 4 * H, l.dg, 4 * H, true, l.w_ih,
+                                     l.in_size, false, dx_l, l.in_size, nullptr, s));
+                ++launches;
+            }
+            size_t m3 = timer.mark(s);
+            timer.span(PH_BPTT, m0, m1);
+            timer.span(PH_WGRAD, m1, m2);
+            timer.span(PH_XGRAD, m2, m3);
+        }
+        if (comm) {
+            // reduce this layer's gradients while the layers below keep back-propagating
+            FLSTM_CUDA_TRY(cudaEventRecord(comm_fork, s));
+            FLSTM_CUDA_TRY(cudaStreamWaitEvent(comm_stream, comm_fork, 0));
+            size_t c0 = timer.mark(comm_stream);
+            FLSTM_TRY(comm_allreduce_sum_f32(comm, grads + l.grad_offset, l.grad_count, comm_stream));
+            size_t c1 = timer.mark(comm_stream);
+            timer.span(PH_ALLREDUCE, c0, c1);
+        }
+    }
+    if (comm) {
+        FLSTM_CUDA_TRY(cudaEventRecord(comm_join, comm_stream));
+        FLSTM_CUDA_TRY(cudaStreamWaitEvent(s, comm_join, 0));
+    }
+    return FLSTM_OK;
+}
+
+// ------------------------------------------------------------------ phase timer
+size_t PhaseTimer::mark(cudaStream_t s) {
+    if (!enabled) return 0;
+    if (used == pool.size()) {
+        cudaEvent_t e;
+        if (cudaEventCreate(&e) != cudaSuccess) return 0;
+        pool.push_back(e);
+    }
+    cudaEventRecord(pool[used], s);
+    return used++;
+}
+
+int PhaseTimer::totals(float *out) {
+    for (int i = 0; i < PH_COUNT; ++i) out[i] = 0.f;
+    for (auto &sp : spans) {
+        if (sp.a >= used || sp.b >= used) continue;
+        if (cudaEventSynchronize(pool[sp.b]) != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "event sync failed");
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, pool[sp.a], pool[sp.b]) == cudaSuccess) out[sp.phase] += ms;
+    }
+    return FLSTM_OK;
+}
+
+PhaseTimer::~PhaseTimer() {
+    for (auto e : pool) cudaEventDestroy(e);
+}
+
+}  // namespace flstm_b200
+
+// ====================================================================== C ABI
+using flstm_b200::Engine;
+using flstm_b200::set_error;
+
+extern "C" {
+
+int flstm_engine_create(const flstm_engine_config *config, flstm_engine **out) {
+    if (!config || !out) return set_error(FLSTM_ERR_INVALID, "null argument");
+    *out = nullptr;
+    if (config->dtype < FLSTM_DTYPE_F32 || config->dtype > FLSTM_DTYPE_BF16)
+        return set_error(FLSTM_ERR_INVALID, "bad dtype %d", config->dtype);
+    if (config->layers < 1 || config->layers > 64) return set_error(FLSTM_ERR_INVALID, "layers must be in [1,64]");
+    if (config->batch == 0 || config->input_size == 0 || config->hidden_size == 0)
+        return set_error(FLSTM_ERR_INVALID, "batch, input_size and hidden_size must be positive");
+    if (config->backend < FLSTM_BACKEND_AUTO || config->backend > FLSTM_BACKEND_TC)
+        return set_error(FLSTM_ERR_INVALID, "bad backend %d", config->backend);
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
+        return set_error(FLSTM_ERR_CUDA, "no CUDA device: this library has no CPU path");
+    flstm_engine *h = new (std::nothrow) flstm_engine();
+    if (!h) return set_error(FLSTM_ERR_INVALID, "out of host memory");
+    Engine &e = h->impl;
+    e.cfg = *config;
+    cudaGetDevice(&e.device);
+    const bool tc_ok = flstm_b200::tc::supported(*config);
+    if (config->backend == FLSTM_BACKEND_TC && !tc_ok) {
+        delete h;
+        return set_error(FLSTM_ERR_UNSUPPORTED,
+                         "tensor-core backend needs a 16-bit dtype, hidden_size %% 64 == 0, input_size %% 64 == 0 and "
+                         "batch %% 8 == 0 on an sm_100 device");
+    }
+    e.backend = (config->backend == FLSTM_BACKEND_AUTO) ? (tc_ok ? FLSTM_BACKEND_TC : FLSTM_BACKEND_SIMT) : config->backend;
+    const size_t H = config->hidden_size, B = config->batch, es = flstm_b200::dtype_size(config->dtype);
+    e.layers.resize(config->layers);
+    size_t total = 0;
+    for (int li = 0; li < config->layers; ++li) {
+        auto &l = e.layers[li];
+        l.in_size = li == 0 ? config->input_size : H;
+        l.grad_offset = total;
+        l.grad_count = 4 * H * l.in_size + 4 * H * H + 4 * H;
+        total += l.grad_count;
+    }
+    e.grad_count = total;
+    int st = FLSTM_OK;
+    auto fail = [&](int code) { delete h; return code; };
+    {
+        void *raw = nullptr;
+        if (cudaMalloc(&raw, total * sizeof(float)) != cudaSuccess) return fail(set_error(FLSTM_ERR_CUDA, "cudaMalloc of the gradient buffer failed"));
+        e.grads = static_cast<float *>(raw);
+        cudaMemset(raw, 0, total * sizeof(float));
+        if (cudaMalloc(&raw, B * H * sizeof(float)) != cudaSuccess) return fail(set_error(FLSTM_ERR_CUDA, "cudaMalloc failed"));
+        e.dc = static_cast<float *>(raw);
+    }
+    for (auto &l : e.layers) {
+        l.dw_ih = e.grads + l.grad_offset;
+        l.dw_hh = l.dw_ih + 4 * H * l.in_size;
+        l.db = l.dw_hh + 4 * H * H;
+        void *raw = nullptr;
+        if (cudaMalloc(&raw, 4 * H * l.in_size * es) != cudaSuccess) return fail(set_error(FLSTM_ERR_CUDA, "cudaMalloc failed"));
+        l.w_ih = raw;
+        if (cudaMalloc(&raw, 4 * H * H * es) != cudaSuccess) return fail(set_error(FLSTM_ERR_CUDA, "cudaMalloc failed"));
+        l.w_hh = raw;
+        if (cudaMalloc(&raw, 4 * H * sizeof(float)) != cudaSuccess) return fail(set_error(FLSTM_ERR_CUDA, "cudaMalloc failed"));
+        l.bias = static_cast<float *>(raw);
+    }
+    if (e.backend == FLSTM_BACKEND_TC) {
+        st = flstm_b200::tc::init(e);
+        if (st != FLSTM_OK) return fail(st);
+    }
+    st = e.allocate(config->max_seq_len ? config->max_seq_len : 1);
+    if (st != FLSTM_OK) return fail(st);
+    *out = h;
+    return FLSTM_OK;
+}
+
+int flstm_engine_destroy(flstm_engine *engine) {
+    if (!engine) return FLSTM_OK;
+    cudaSetDevice(engine->impl.device);
+    cudaDeviceSynchronize();
+    delete engine;
+    return FLSTM_OK;
+}
+
+int flstm_engine_set_weights(flstm_engine *engine, int layer, const float *w_ih, const float *w_hh,
+                             const float *b_ih, const float *b_hh, void *stream) {
+    if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    return engine->impl.set_weights(layer, w_ih, w_hh, b_ih, b_hh, static_cast<cudaStream_t>(stream));
+}
+
+int flstm_engine_forward(flstm_engine *engine, size_t seq_len, const void *x, const void *h0, const void *c0,
+                         void *y, void *h_n, void *c_n, void *stream) {
+    if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    return engine->impl.forward(seq_len, x, h0, c0, y, h_n, c_n, static_cast<cudaStream_t>(stream));
+}
+
+int flstm_engine_backward(flstm_engine *engine, size_t seq_len, const void *dy, const void *d_hn,
+                          const void *d_cn, void *dx, float *dh0, float *dc0, void *stream) {
+    if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    return engine->impl.backward(seq_len, dy, d_hn, d_cn, dx, dh0, dc0, static_cast<cudaStream_t>(stream));
+}
+
+int flstm_engine_grad_ptrs(flstm_engine *engine, int layer, float **dw_ih, float **dw_hh, float **db) {
+    if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    if (layer < 0 || layer >= (int)engine->impl.layers.size()) return set_error(FLSTM_ERR_INVALID, "layer out of range");
+    auto &l = engine->impl.layers[layer];
+    if (dw_ih) *dw_ih = l.dw_ih;
+    if (dw_hh) *dw_hh = l.dw_hh;
+    if (db) *db = l.db;
+    return FLSTM_OK;
+}
+
+int flstm_engine_grad_buffer(flstm_engine *engine, float **flat, size_t *count) {
+    if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    if (flat) *flat = engine->impl.grads;
+    if (count) *count = engine->impl.grad_count;
+    return FLSTM_OK;
+}
+
+int flstm_engine_cache_ptrs(flstm_engine *engine, int layer, void **gates, float **cells, void **hiddens,
+                            int *gate_layout) {
+    if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    if (layer < 0 || layer >= (int)engine->impl.layers.size()) return set_error(FLSTM_ERR_INVALID, "layer out of range");
+    auto &l = engine->impl.layers[layer];
+    if (gates) *gates = l.gates;
+    if (cells) *cells = l.cs;
+    if (hiddens) *hiddens = l.hs;
+    if (gate_layout) *gate_layout = engine->impl.backend == FLSTM_BACKEND_TC ? 1 : 0;
+    return FLSTM_OK;
+}
+
+int flstm_engine_set_cell_io_f32(flstm_engine *engine, int enabled) {
+    if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    engine->impl.cell_io_f32 = enabled != 0;
+    return FLSTM_OK;
+}
+
+int flstm_engine_backend(const flstm_engine *engine) { return engine ? engine->impl.backend : -1; }
+
+int flstm_comm_unique_id(void *id128) { return flstm_b200::comm_unique_id(id128); }
+
+int flstm_engine_attach_comm(flstm_engine *engine, const void *id128, int rank, int world_size) {
+    if (!engine || !id128) return set_error(FLSTM_ERR_INVALID, "null argument");
+    Engine &e = engine->impl;
+    if (e.comm) return set_error(FLSTM_ERR_INVALID, "a communicator is already attached");
+    cudaSetDevice(e.device);
+    int st = flstm_b200::comm_create(id128, rank, world_size, &e.comm);
+    if (st != FLSTM_OK) return st;
+    if (cudaStreamCreateWithFlags(&e.comm_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&e.comm_fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&e.comm_join, cudaEventDisableTiming) != cudaSuccess)
+        return set_error(FLSTM_ERR_CUDA, "could not create the communication stream");
+    return FLSTM_OK;
+}
+
+int flstm_engine_enable_timing(flstm_engine *engine, int enabled) {
+    if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    engine->impl.timer.enabled = enabled != 0;
+    engine->impl.timer.reset();
+    return FLSTM_OK;
+}
+
+int flstm_engine_phase_ms(flstm_engine *engine, float *out6) {
+    if (!engine || !out6) return set_error(FLSTM_ERR_INVALID, "null argument");
+    return engine->impl.timer.totals(out6);
+}
+
+unsigned long long flstm_engine_launch_count(const flstm_engine *engine) {
+    return engine ? engine->impl.launches : 0ull;
+}
+
+const char *flstm_last_error(void) { return flstm_b200::last_error_slot().c_str(); }
+
+const char *flstm_version(void) { return "flashlstm-b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

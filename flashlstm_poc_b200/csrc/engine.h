@@ -1,0 +1,115 @@
+// Internal C++ view of the engine handle (the C ABI in include/flashlstm_b200/engine.h wraps it).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <vector>
+
+#include "flashlstm_b200/engine.h"
+
+namespace flstm_b200 {
+
+struct Comm;  // data-parallel communicator (comm.cu)
+
+// Device-time accounting per phase with CUDA events; records only when enabled, never syncs
+// until the totals are read.
+enum Phase { PH_PROJ = 0, PH_RECUR_FWD, PH_BPTT, PH_WGRAD, PH_XGRAD, PH_ALLREDUCE, PH_COUNT };
+struct PhaseTimer {
+    bool enabled = false;
+    std::vector<cudaEvent_t> pool;
+    size_t used = 0;
+    struct Span { int phase; size_t a, b; };
+    std::vector<Span> spans;
+    void reset() { used = 0; spans.clear(); }
+    size_t mark(cudaStream_t s);
+    void span(int phase, size_t a, size_t b) { if (enabled) spans.push_back({phase, a, b}); }
+    int totals(float *out);
+    ~PhaseTimer();
+};
+
+// Per-layer device buffers.  "T" below is the engine's storage type.
+struct LayerBuffers {
+    size_t in_size = 0;      // I_l
+    void *w_ih = nullptr;    // T (4H, I_l)   SIMT: torch row order; TC: tile-interleaved rows
+    void *w_hh = nullptr;    // T (4H, H)     same row order as w_ih
+    void *w_ih_t = nullptr;  // T (I_l, 4H)   TC only: W_ih^T, torch gate order along 4H
+    void *w_hh_t = nullptr;  // T (H, 4H)     TC only: W_hh^T, torch gate order along 4H
+    float *bias = nullptr;   // fp32 (4H)     b_ih + b_hh, same order as the rows of w_ih
+    void *gates = nullptr;   // T (Tcap, B, 4H)  input projection, overwritten by the gate cache
+    void *hs = nullptr;      // T (Tcap+1, B, H) slot 0 = h0, slot t+1 = h_t
+    float *cs = nullptr;     // fp32 (Tcap+1, B, H)
+    void *dg = nullptr;      // T (Tcap, B, 4H)  pre-activation gradients (training)
+    void *dx = nullptr;      // T (Tcap, B, I_l) gradient w.r.t. this layer's input (layers > 0)
+    void *dg_t = nullptr;    // T (4H, Tcap*B)   TC only: dG^T for the weight-gradient GEMMs
+    void *xh_t = nullptr;    // T (I_l + H, Tcap*B) TC only: [X | H_prev]^T
+    float *dw_ih = nullptr;  // views into the flat gradient buffer
+    float *dw_hh = nullptr;
+    float *db = nullptr;
+    size_t grad_offset = 0;  // element offset of this layer's [dW_ih | dW_hh | db] slice
+    size_t grad_count = 0;
+    bool weights_set = false;
+};
+
+struct Engine {
+    flstm_engine_config cfg{};
+    int backend = FLSTM_BACKEND_SIMT;
+    int device = 0;
+    size_t t_cap = 0;  // sequence capacity of the time-sized buffers
+    std::vector<LayerBuffers> layers;
+    float *grads = nullptr;  // flat fp32: per layer [dW_ih | dW_hh | db]
+    size_t grad_count = 0;
+    float *dc = nullptr;     // fp32 (B,H) cell-gradient carry
+    float *db_part = nullptr;  // TC: per batch-tile partial bias gradients
+    unsigned int *sync_words = nullptr;  // TC: grid-barrier counters + error word
+    size_t last_T = 0;       // sequence length of the last forward (0 = none)
+    unsigned long long launches = 0;
+    bool cell_io_f32 = false;       // c0 / c_n cross the API as fp32 instead of the engine dtype
+    const void *x_saved = nullptr;  // layer-0 input of the last forward (caller keeps it alive)
+    PhaseTimer timer;
+    Comm *comm = nullptr;
+    cudaStream_t comm_stream = nullptr;
+    cudaEvent_t comm_fork = nullptr, comm_join = nullptr;
+    void *tc_state = nullptr;  // tensor-core path: cached tensor maps etc. (tc_engine.cu)
+
+    ~Engine();
+    int allocate(size_t t_cap);
+    void release_time_buffers();
+    int ensure_capacity(size_t T);
+    int set_weights(int layer, const float *w_ih, const float *w_hh, const float *b_ih, const float *b_hh,
+                    cudaStream_t s);
+    int forward(size_t T, const void *x, const void *h0, const void *c0, void *y, void *hn, void *cn,
+                cudaStream_t s);
+    int backward(size_t T, const void *dy, const void *dhn, const void *dcn, void *dx, float *dh0,
+                 float *dc0, cudaStream_t s);
+};
+
+}  // namespace flstm_b200
+
+// The opaque handle of the C ABI.
+struct flstm_engine {
+    flstm_b200::Engine impl;
+};
+
+namespace flstm_b200 {
+
+// Tensor-core path entry points (tc_engine.cu).  `supported` decides AUTO resolution.
+namespace tc {
+bool supported(const flstm_engine_config &cfg);
+int init(Engine &e);
+void destroy(Engine &e);
+int on_capacity_change(Engine &e);
+int set_weights(Engine &e, int layer, const float *w_ih, const float *w_hh, const float *b_ih,
+                const float *b_hh, cudaStream_t s);
+int forward_layer(Engine &e, int layer, size_t T, const void *x_l, void *y_out, cudaStream_t s);
+int backward_layer(Engine &e, int layer, size_t T, const void *x_l, const void *dy_l, const void *dhn_l,
+                   const void *dcn_l, void *dx_l, float *dh0_l, float *dc0_l, cudaStream_t s);
+}  // namespace tc
+
+// Communicator (comm.cu): NCCL loaded at run time with dlopen.
+int comm_unique_id(void *id128);
+int comm_create(const void *id128, int rank, int world, Comm **out);
+void comm_destroy(Comm *c);
+int comm_allreduce_sum_f32(Comm *c, float *buf, size_t count, cudaStream_t s);
+
+}  // namespace flstm_b200

@@ -1,0 +1,47 @@
+// Host-side launchers of every kernel in the library.  All launches are asynchronous on the
+// given stream and return a flstm_status.  `dtype` is a flstm_dtype value.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+
+namespace flstm_b200 {
+
+// ------------------------------------------------------------------ generic (any shape)
+namespace simt {
+
+// dst[i] = (TOut) src[i]
+int convert(int src_dtype, const void *src, int dst_dtype, void *dst, size_t n, cudaStream_t s);
+// out = b_ih + b_hh (fp32, n entries)
+int bias_sum(const float *b_ih, const float *b_hh, float *out, size_t n, cudaStream_t s);
+// strided gather of whole (B,H) slabs: dst[k] = (dst dtype) src[k*stride_slabs] for k < count
+int gather_slabs(int src_dtype, const void *src, size_t slab_elems, size_t stride_slabs, size_t count,
+                 int dst_dtype, void *dst, cudaStream_t s);
+
+// C[M,N] (row-major, ldc) = sum_k A(m,k) B(k,n) (+ bias[n]); fp32 accumulation.
+//   a_kcontig: A(m,k) = A[m*lda + k]   else A(m,k) = A[k*lda + m]
+//   b_kcontig: B(k,n) = B[n*ldb + k]   else B(k,n) = B[k*ldb + n]
+int gemm(int ab_dtype, int c_dtype, size_t M, size_t N, size_t K, const void *A, size_t lda,
+         bool a_kcontig, const void *B, size_t ldb, bool b_kcontig, void *C, size_t ldc,
+         const float *bias, cudaStream_t s);
+
+// One forward time step: gates = p_t + h_prev W_hh^T, activations, cell/hidden update.
+// p_t (B,4H) holds the input projection (bias included) and is overwritten with the
+// post-activation gates i,f,g,o (the gate cache).  y_t is optional.
+int step_forward(int dtype, size_t B, size_t H, const void *h_prev, const void *w_hh, void *p_t,
+                 const float *c_prev, float *c_next, void *h_next, void *y_t, cudaStream_t s);
+
+// One backward time step (reverse order): dh = dy_t + dg_next W_hh (or + dh_init at the last
+// step, where dg_next == nullptr), then the fused pointwise backward -> dg_t, dc (in/out).
+int step_backward(int dtype, size_t B, size_t H, const void *dg_next, const void *w_hh,
+                  const void *dh_init, const void *dy_t, const void *gates_t, const float *c_t,
+                  const float *c_prev, float *dc, void *dg_t, cudaStream_t s);
+// dh0 (fp32) = dg_0 W_hh
+int final_dh(int dtype, size_t B, size_t H, const void *dg0, const void *w_hh, float *dh0, cudaStream_t s);
+
+// out[n] = sum_r dg[r, n] over R rows (deterministic order)
+int column_sum(int dtype, const void *dg, size_t R, size_t N, float *out, cudaStream_t s);
+
+}  // namespace simt
+}  // namespace flstm_b200

@@ -1,0 +1,131 @@
+/*
+ * Native engine C ABI of the B200 LSTM forward/backward engine.
+ *
+ * Everything crosses this boundary as plain pointers and sizes.  Pointers are DEVICE
+ * pointers unless a comment says otherwise; `stream` arguments are cudaStream_t handles
+ * passed as void* (NULL = the legacy default stream).  Every function returns a
+ * flstm_status; the message of the last failure on the calling thread is available from
+ * flstm_last_error().  No function aborts the process and none falls back to the CPU.
+ *
+ * The reference surfaces (include/flashlstm/lstm_api.h and include/lstm.hpp) are thin
+ * shims over this handle API.  Compared with the reference's entry points
+ * (include/flashlstm/lstm_api.h:23-56, flashlstm_v2/include/lstm.hpp:132-213) the handle
+ * adds what those cannot express: stacked layers, BF16, device-resident I/O, a retained
+ * gate cache for the backward pass and batch-sharded multi-GPU weight-gradient reduction.
+ *
+ * Semantics are torch.nn.LSTM's: gate row order i,f,g,o in every (4H, .) tensor; two
+ * biases that are summed; seq-major contiguous (T,B,.) tensors; states shaped (L,B,H).
+ */
+#ifndef FLASHLSTM_B200_ENGINE_H
+#define FLASHLSTM_B200_ENGINE_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    FLSTM_OK = 0,
+    FLSTM_ERR_INVALID = 1,     /* bad argument / misuse                                   */
+    FLSTM_ERR_CUDA = 2,        /* a CUDA runtime or driver call failed                    */
+    FLSTM_ERR_TIMEOUT = 3,     /* a bounded device-side wait gave up (kernel returned)    */
+    FLSTM_ERR_UNSUPPORTED = 4, /* shape / dtype not supported by the requested backend    */
+    FLSTM_ERR_COMM = 5         /* communicator (NCCL) failure                             */
+} flstm_status;
+
+typedef enum {
+    FLSTM_DTYPE_F32 = 0, /* fp32 storage, fp32 FMA arithmetic                             */
+    FLSTM_DTYPE_F16 = 1, /* fp16 storage, fp32 accumulate, fp32 cell state                */
+    FLSTM_DTYPE_BF16 = 2 /* bf16 storage, fp32 accumulate, fp32 cell state                */
+} flstm_dtype;
+
+typedef enum {
+    FLSTM_BACKEND_AUTO = 0, /* tensor-core path when the shape allows it, else SIMT       */
+    FLSTM_BACKEND_SIMT = 1, /* CUDA-core kernels: any shape, any dtype                    */
+    FLSTM_BACKEND_TC = 2    /* tcgen05/TMEM + TMA kernels (16-bit dtypes, aligned shapes) */
+} flstm_backend;
+
+typedef struct {
+    int dtype;          /* flstm_dtype: type of x, y, h0, c0, h_n, c_n, dY, d_hn, d_cn, dX */
+    int layers;         /* >= 1                                                            */
+    size_t batch;       /* per-GPU batch                                                   */
+    size_t input_size;  /* I of layer 0 (upper layers consume H)                           */
+    size_t hidden_size; /* H                                                               */
+    size_t max_seq_len; /* workspace is sized for this T; a longer T grows it              */
+    int training;       /* 1: forward keeps the gate cache + cell states for backward      */
+    int backend;        /* flstm_backend                                                   */
+} flstm_engine_config;
+
+typedef struct flstm_engine flstm_engine;
+
+/* Allocates the workspace on the CURRENT device.  Replaces the per-call cudaMalloc of
+ * ~25 buffers in the reference (flashlstm_v2/src/lstm_forward.cu:555-645). */
+int flstm_engine_create(const flstm_engine_config *config, flstm_engine **out);
+int flstm_engine_destroy(flstm_engine *engine);
+
+/* Snapshot + pack one layer's fp32 parameters (w_ih (4H,I_l), w_hh (4H,H), b_ih, b_hh (4H)).
+ * Replaces pack_weights_kernel / FuseWeightsKernel / FuseBiasKernel
+ * (src/kernels.cu:45-84, flashlstm_v2/src/lstm_forward.cu:180-217); done once per weight
+ * update instead of on every forward and backward call. */
+int flstm_engine_set_weights(flstm_engine *engine, int layer, const float *w_ih, const float *w_hh,
+                             const float *b_ih, const float *b_hh, void *stream);
+
+/* y (T,B,H), h_n/c_n (L,B,H) may be NULL when not wanted; h0/c0 NULL = zeros.
+ * Asynchronous on `stream`.  In training mode x must stay valid and unchanged until the
+ * matching flstm_engine_backward has been enqueued (it is re-read for dW_ih). */
+int flstm_engine_forward(flstm_engine *engine, size_t seq_len, const void *x, const void *h0,
+                         const void *c0, void *y, void *h_n, void *c_n, void *stream);
+
+/* Consumes the cache of the LAST forward call.  dy (T,B,H); d_hn/d_cn (L,B,H) nullable;
+ * dx (T,B,I) in the engine dtype, nullable; dh0/dc0 (L,B,H) fp32, nullable.  Weight and
+ * bias gradients are written (not accumulated) into the engine's flat fp32 gradient buffer
+ * (see flstm_engine_grad_ptrs).  With a communicator attached the flat buffer holds the
+ * SUM over ranks when the call's work completes on `stream`. */
+int flstm_engine_backward(flstm_engine *engine, size_t seq_len, const void *dy, const void *d_hn,
+                          const void *d_cn, void *dx, float *dh0, float *dc0, void *stream);
+
+/* Device pointers into the flat gradient buffer of one layer: dW_ih (4H,I_l), dW_hh (4H,H),
+ * db (4H) (db_ih == db_hh == db, as in flashlstm_v2/src/lstm_backward.cu:1218-1231). */
+int flstm_engine_grad_ptrs(flstm_engine *engine, int layer, float **dw_ih, float **dw_hh, float **db);
+/* The whole flat buffer, layer after layer as [dW_ih | dW_hh | db]. */
+int flstm_engine_grad_buffer(flstm_engine *engine, float **flat, size_t *count);
+
+/* Post-activation gate cache of one layer from the last training forward: (T,B,4H) in the
+ * engine dtype, plus the fp32 cell states (T+1,B,H) and the hidden states (T+1,B,H) whose
+ * slot 0 is the initial state.  `gate_layout` is set to 0 when columns are in torch order
+ * (g*H+u) and to 1 when they are tile-interleaved (((u/16)*4+g)*16 + u%16). */
+int flstm_engine_cache_ptrs(flstm_engine *engine, int layer, void **gates, float **cells,
+                            void **hiddens, int *gate_layout);
+
+/* The cell state is fp32 inside the engine.  With this switch on, the c0 and c_n arguments of
+ * flstm_engine_forward are fp32 (L,B,H) tensors instead of tensors in the engine dtype. */
+int flstm_engine_set_cell_io_f32(flstm_engine *engine, int enabled);
+
+/* Which backend the engine resolved to (flstm_backend, never AUTO). */
+int flstm_engine_backend(const flstm_engine *engine);
+
+/* Batch-sharded data parallelism: one engine per GPU/process.  flstm_comm_unique_id fills a
+ * 128-byte id on rank 0 (send it to the other ranks by any means); every rank then calls
+ * flstm_engine_attach_comm.  The only collective is one sum-allreduce per layer over that
+ * layer's slice of the flat gradient buffer, issued on an internal stream as soon as the
+ * layer's weight-gradient kernels finish, so it overlaps the back-propagation of the layers
+ * below it.  The reference has no multi-GPU path. */
+int flstm_comm_unique_id(void *id128);
+int flstm_engine_attach_comm(flstm_engine *engine, const void *id128, int rank, int world_size);
+
+/* Per-phase device time of the last forward/backward pair in milliseconds (needs
+ * flstm_engine_enable_timing(engine, 1); adds event records, no synchronisation).
+ * out[0..5] = projection, recurrent forward, BPTT, weight-grad, input-grad, allreduce. */
+int flstm_engine_enable_timing(flstm_engine *engine, int enabled);
+int flstm_engine_phase_ms(flstm_engine *engine, float *out6);
+/* Number of kernels this library launched on behalf of `engine` since creation. */
+unsigned long long flstm_engine_launch_count(const flstm_engine *engine);
+
+const char *flstm_last_error(void);
+const char *flstm_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHLSTM_B200_ENGINE_H */

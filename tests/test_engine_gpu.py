@@ -1,0 +1,124 @@
+"""Parity of the CUDA engine (through the C ABI) with the CPU oracle, the reference-derived golden
+vectors and torch.nn.LSTM.  Tolerances are the stated bar: max-abs <= 2e-3 for fp32, relative
+L2 <= 1e-2 for FP16/BF16, against fp32 CPU ground truth computed on the same (rounded) inputs."""
+import numpy as np
+import pytest
+import torch
+
+from flashlstm_poc_b200.workloads import WORKLOADS, Inputs, Workload, make_inputs
+from oracle import lstm_oracle as orc
+from tests.gpu_helpers import assert_parity, run_engine, run_oracle
+from tests.helpers import golden_cases, torch_lstm_reference
+
+pytestmark = pytest.mark.gpu
+
+BACKENDS = ["simt", "auto"]
+
+
+@pytest.mark.parametrize("path", golden_cases(), ids=lambda p: p.split("/")[-1][:-4])
+def test_fp32_engine_matches_reference_golden(path):
+    """The golden vectors come from running the reference's own CPU code; shapes include odd sizes
+    (H=5, I=3) that no tile divides."""
+    g = np.load(path)
+    T, B, I = g["x"].shape
+    H = g["w_hh"].shape[1]
+    w = Workload("golden", "f32", 1, I, H, B, T, seed=0)
+    t = lambda k: torch.from_numpy(g[k])
+    inp = Inputs([t("w_ih")], [t("w_hh")], [t("b_ih")], [t("b_hh")], t("x"), t("h0"), t("c0"), t("dy"))
+    got, eng = run_engine(w, inp, dhn=t("dhn"), dcn=t("dcn"))
+    ref = {"y": g["y"], "hn": g["hn"], "cn": g["cn"], "dx": g["dx"], "dh0": g["dh0"], "dc0": g["dc0"],
+           "dw_ih": [g["dw_ih"]], "dw_hh": [g["dw_hh"]], "db": [g["db_ih"]]}
+    assert_parity(got, ref, "f32", fp32_max_abs=1e-4)
+    gates = eng.gate_cache(0, T).float().cpu().numpy()
+    assert orc.max_abs_err(gates, g["gates"]) < 1e-5
+    eng.close()
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("L,T,B,I,H", [(1, 12, 8, 64, 64), (2, 9, 16, 128, 64), (1, 5, 3, 7, 6), (3, 4, 8, 64, 128)])
+def test_engine_matches_oracle(backend, dtype, L, T, B, I, H):
+    w = Workload("t", dtype, L, I, H, B, T, seed=11, state_std=0.5)
+    inp = make_inputs(w)
+    torch.manual_seed(5)
+    rnd = lambda: torch.randn(L, B, H).to({"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[dtype]).float()
+    dhn, dcn = rnd(), rnd()
+    got, eng = run_engine(w, inp, backend=backend, dhn=dhn, dcn=dcn)
+    ref = run_oracle(inp, dhn, dcn)
+    assert_parity(got, ref, dtype)
+    eng.close()
+
+
+def test_config1_fp32_full_size_against_torch_lstm():
+    """BASELINE config 1 at full size, ground truth = fp32 CPU torch.nn.LSTM (loss = sum(y*dY))."""
+    w = WORKLOADS["c1_fp32_h256"]
+    inp = make_inputs(w)
+    got, eng = run_engine(w, inp)
+    ref = torch_lstm_reference(inp)
+    ref["db"] = ref["db_ih"]
+    assert_parity(got, ref, "f32")
+    eng.close()
+
+
+@pytest.mark.parametrize("name,scale", [("c2_fp16_h1024", dict(seq_len=64, batch=64)),
+                                        ("c3_bf16_l2_h2048", dict(seq_len=32, batch=32, input_size=512, hidden_size=512)),
+                                        ("c5_bf16_l4_h1024", dict(seq_len=16, batch=64, input_size=256, hidden_size=256))])
+def test_scaled_baseline_configs(name, scale):
+    """The 16-bit BASELINE configurations at sizes the CPU oracle finishes in seconds."""
+    w = WORKLOADS[name].scaled(**scale)
+    inp = make_inputs(w)
+    got, eng = run_engine(w, inp)
+    ref = run_oracle(inp)
+    assert_parity(got, ref, w.dtype)
+    eng.close()
+
+
+def test_repeatable_and_cache_layout():
+    """Two runs give bit-identical results (a race in a persistent kernel's barrier would not), and
+    the gate cache read back in torch order matches the oracle's activations."""
+    w = Workload("t", "f16", 1, 64, 64, 16, 10, seed=3, state_std=0.3)
+    inp = make_inputs(w)
+    a, eng = run_engine(w, inp)
+    b, eng2 = run_engine(w, inp, repeat=2)
+    for k in ("y", "dx", "dh0"):
+        assert np.array_equal(a[k], b[k]), k
+    assert np.array_equal(a["dw_hh"][0], b["dw_hh"][0])
+    ref = run_oracle(inp)
+    gates = eng.gate_cache(0, w.seq_len).float().cpu().numpy()
+    assert orc.max_abs_err(gates, ref["gates"][0]) < 5e-3
+    eng.close(); eng2.close()
+
+
+def test_sequence_length_may_change_between_calls():
+    """The v1 contract: T differs per call and the workspace grows (src/lstm.cu:933-970)."""
+    w = Workload("t", "f16", 1, 32, 32, 4, 6, seed=9)
+    base = make_inputs(w)
+    dev = torch.device("cuda", 0)
+    from flashlstm_poc_b200.engine import Engine
+
+    eng = Engine("f16", 1, 4, 32, 32, max_seq_len=6, training=False, device=dev)
+    eng.set_weights(0, base.w_ih[0].to(dev), base.w_hh[0].to(dev), base.b_ih[0].to(dev), base.b_hh[0].to(dev))
+    for T in (6, 3, 13):
+        ww = w.scaled(seq_len=T, training=False)
+        inp = make_inputs(ww)
+        inp.w_ih, inp.w_hh, inp.b_ih, inp.b_hh = base.w_ih, base.w_hh, base.b_ih, base.b_hh
+        y, hn, cn = eng.forward(inp.x.to(dev, torch.float16))
+        ref = run_oracle(inp)
+        assert orc.rel_l2_err(y.float().cpu().numpy(), ref["y"]) < 1e-2
+    eng.close()
+
+
+def test_errors_are_reported():
+    from flashlstm_poc_b200._lib import FlashLstmError
+    from flashlstm_poc_b200.engine import Engine
+
+    dev = torch.device("cuda", 0)
+    eng = Engine("f16", 1, 2, 8, 8, 4, device=dev)
+    x = torch.zeros(4, 2, 8, dtype=torch.float16, device=dev)
+    with pytest.raises(FlashLstmError, match="weights"):
+        eng.forward(x)
+    with pytest.raises(ValueError):
+        eng.forward(x.float())
+    with pytest.raises(FlashLstmError):
+        Engine("f32", 1, 2, 8, 8, 4, backend="tc", device=dev)  # tensor-core path is 16-bit only
+    eng.close()
