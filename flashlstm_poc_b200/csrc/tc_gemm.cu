@@ -1,0 +1,350 @@
+// Dense contractions on the 5th-generation tensor cores: D[M,N] = A * B^T (+ bias) with 16-bit
+// operands and fp32 accumulation in TMEM.
+//
+//   warp 0   TMA producer: cp.async.bulk.tensor tiles -> shared-memory ring (mbarrier full/empty)
+//   warp 1   UMMA issuer : one elected thread issues tcgen05.mma (128 x BN x 16) from shared memory
+//                          descriptors into one of two TMEM accumulators; tcgen05.commit releases
+//                          ring slots and publishes finished accumulators
+//   warps 2-5 epilogue   : tcgen05.ld TMEM -> registers -> (bias, convert) -> global, overlapping the
+//                          next tile's main loop through the second accumulator
+// The grid is persistent (one CTA per SM, static round-robin over output tiles).
+//
+// Used for (shapes at the benchmark configurations, per layer):
+//   input projection  P[T*B,4H]  = X[T*B,I] W_ih^T + b      (K-major x K-major, 16-bit out)
+//   input gradient    dX[T*B,I]  = dG[T*B,4H] W_ih          (K-major x K-major via W_ih^T, 16-bit out)
+//   weight gradients  dW[4H,I|H] = dG^T [X|H_prev]          (MN-major x MN-major: both operands are read
+//                                                            as stored, reduction dim T*B outermost; fp32 out)
+// These replace the reference's CUTLASS mma.sync instantiations (src/lstm_internal.h:48-68,
+// flashlstm_v2/src/gemm.cu:208-359) and its per-32-step chunked dW/dX GEMMs with beta=1
+// (flashlstm_v2/src/lstm_backward.cu:1112-1171).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "tc_common.cuh"
+#include "tc_kernels.h"
+
+namespace flstm_b200 {
+namespace tc {
+
+namespace {
+
+constexpr int BM = 128, BK = 64;
+constexpr int kGemmThreads = 192;
+
+template <int BN>
+struct GemmShape {
+    static constexpr int kStages = (BN == 256) ? 4 : 6;
+    static constexpr int kABytes = BM * BK * 2;
+    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTmemCols = 2 * BN;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+enum OutMode { OUT_F16 = 0, OUT_BF16 = 1, OUT_F32 = 2 };
+
+template <int MODE>
+__device__ __forceinline__ void store_row32(void *dst_row, int col0, const uint32_t (&acc)[32], const float *bias,
+                                            int n_valid) {
+    // dst_row: start of this thread's output row; writes columns [col0, col0+32) clipped to n_valid
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
+    if (bias) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < n_valid) v[i] += __ldg(bias + col0 + i);
+    }
+    if (MODE == OUT_F32) {
+        float *p = static_cast<float *>(dst_row) + col0;
+        if (n_valid >= 32 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                reinterpret_cast<float4 *>(p)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else {
+            for (int i = 0; i < 32 && i < n_valid; ++i) p[i] = v[i];
+        }
+    } else {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if (MODE == OUT_F16) {
+                __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+                packed[i] = *reinterpret_cast<uint32_t *>(&h);
+            } else {
+                __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                packed[i] = *reinterpret_cast<uint32_t *>(&h);
+            }
+        }
+        uint16_t *p = static_cast<uint16_t *>(dst_row) + col0;
+        if (n_valid >= 32 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                reinterpret_cast<uint4 *>(p)[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+        } else {
+            for (int i = 0; i < 32 && i < n_valid; ++i)
+                p[i] = (i & 1) ? (uint16_t)(packed[i >> 1] >> 16) : (uint16_t)(packed[i >> 1] & 0xFFFF);
+        }
+    }
+}
+
+template <int BN, int MODE, bool HAS_BIAS, bool MN_MAJOR>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, void *__restrict__ D,
+            size_t ldd, const float *__restrict__ bias, int M, int N, int K, uint32_t idesc,
+            unsigned int *__restrict__ err_word) {
+    using S = GemmShape<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::kStages * S::kStageBytes);
+    uint64_t *full = bars, *empty = bars + S::kStages;
+    uint64_t *tfull = bars + 2 * S::kStages, *tempty = tfull + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty + 2);
+    volatile uint32_t *abort_w = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < S::kStages; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&tfull[i], 1);
+            mbar_init(&tempty[i], 4);
+        }
+        *abort_w = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tm_a);
+        tma_prefetch_desc(&tm_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, S::kTmemCols);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN;
+    const int tiles = num_m * num_n, kblocks = (K + BK - 1) / BK;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+                const int m0 = (tile / num_n) * BM, n0 = (tile % num_n) * BN;
+                bool ok = true;
+                for (int kb = 0; kb < kblocks && ok; ++kb) {
+                    ok = mbar_wait(&empty[stage], phase ^ 1, abort_w);
+                    if (!ok) break;
+                    uint8_t *sa = smem + stage * S::kStageBytes, *sb = sa + S::kABytes;
+                    mbar_expect_tx(&full[stage], S::kStageBytes);
+                    if (!MN_MAJOR) {
+                        tma_load_2d(sa, &tm_a, kb * BK, m0, &full[stage]);
+                        tma_load_2d(sb, &tm_b, kb * BK, n0, &full[stage]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tm_a, m0 + j * 64, kb * BK, &full[stage]);
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tm_b, n0 + j * 64, kb * BK, &full[stage]);
+                    }
+                    if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+                const int buf = it & 1;
+                const uint32_t bphase = (it >> 1) & 1;
+                if (!mbar_wait(&tempty[buf], bphase ^ 1, abort_w)) break;
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                bool ok = true;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = mbar_wait(&full[stage], phase, abort_w);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t a_base = smem_u32(smem + stage * S::kStageBytes), b_base = a_base + S::kABytes;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        uint64_t da, db;
+                        if (!MN_MAJOR) {
+                            da = umma_desc_kmajor_sw128(a_base + k * 32);
+                            db = umma_desc_kmajor_sw128(b_base + k * 32);
+                        } else {
+                            da = umma_desc_mnmajor_sw128(a_base + k * 2048, 8192);
+                            db = umma_desc_mnmajor_sw128(b_base + k * 2048, 8192);
+                        }
+                        umma_f16(d_tmem, da, db, idesc, (kb | k) != 0);
+                    }
+                    umma_commit(&empty[stage]);
+                    if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(&tfull[buf]);
+            }
+        }
+    } else {
+        const int q = warp & 3;  // TMEM lane quadrant this warp may access
+        int it = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+            const int buf = it & 1;
+            const uint32_t bphase = (it >> 1) & 1;
+            const int m0 = (tile / num_n) * BM, n0 = (tile % num_n) * BN;
+            if (!mbar_wait(&tfull[buf], bphase, abort_w)) break;
+            tcgen05_fence_after();
+            const int row = m0 + q * 32 + lane;
+            const size_t esz = (MODE == OUT_F32) ? 4 : 2;
+            char *dst_row = static_cast<char *>(D) + (size_t)row * ldd * esz;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t acc[32];
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c, acc);
+                tmem_ld_wait();
+                const int n_valid = N - (n0 + c);
+                if (row < M && n_valid > 0) store_row32<MODE>(dst_row, n0 + c, acc, HAS_BIAS ? bias : nullptr, n_valid);
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty[buf]);
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, S::kTmemCols);
+    if (threadIdx.x == 0 && *abort_w) atomicExch(err_word, 1u);
+}
+
+template <int BN, int MODE, bool HAS_BIAS, bool MN_MAJOR>
+int launch(const CUtensorMap &ta, const CUtensorMap &tb, void *D, size_t ldd, const float *bias, int M, int N, int K,
+           uint32_t idesc, unsigned int *err_word, int sms, cudaStream_t s) {
+    using S = GemmShape<BN>;
+    auto kern = gemm_kernel<BN, MODE, HAS_BIAS, MN_MAJOR>;
+    static bool configured = false;  // per instantiation
+    if (!configured) {
+        FLSTM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes));
+        configured = true;
+    }
+    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = tiles < sms ? tiles : sms;
+    kern<<<grid, kGemmThreads, S::kSmemBytes, s>>>(ta, tb, D, ldd, bias, M, N, K, idesc, err_word);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "tc gemm launch failed: %s", cudaGetErrorString(e));
+    return FLSTM_OK;
+}
+
+template <int BN>
+int dispatch(int out_dtype, bool has_bias, bool mn, const CUtensorMap &ta, const CUtensorMap &tb, void *D, size_t ldd,
+             const float *bias, int M, int N, int K, uint32_t idesc, unsigned int *err, int sms, cudaStream_t s) {
+    if (mn) {
+        if (out_dtype != FLSTM_DTYPE_F32 || has_bias)
+            return set_error(FLSTM_ERR_UNSUPPORTED, "MN-major operands are instantiated for fp32 output without bias");
+        return launch<BN, OUT_F32, false, true>(ta, tb, D, ldd, bias, M, N, K, idesc, err, sms, s);
+    }
+    switch (out_dtype) {
+        case FLSTM_DTYPE_F32:
+            if (has_bias) return set_error(FLSTM_ERR_UNSUPPORTED, "bias with fp32 output is not instantiated");
+            return launch<BN, OUT_F32, false, false>(ta, tb, D, ldd, bias, M, N, K, idesc, err, sms, s);
+        case FLSTM_DTYPE_F16:
+            return has_bias ? launch<BN, OUT_F16, true, false>(ta, tb, D, ldd, bias, M, N, K, idesc, err, sms, s)
+                            : launch<BN, OUT_F16, false, false>(ta, tb, D, ldd, bias, M, N, K, idesc, err, sms, s);
+        case FLSTM_DTYPE_BF16:
+            return has_bias ? launch<BN, OUT_BF16, true, false>(ta, tb, D, ldd, bias, M, N, K, idesc, err, sms, s)
+                            : launch<BN, OUT_BF16, false, false>(ta, tb, D, ldd, bias, M, N, K, idesc, err, sms, s);
+    }
+    return set_error(FLSTM_ERR_INVALID, "bad output dtype");
+}
+
+}  // namespace
+
+int gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, size_t lda, const void *B, size_t ldb,
+         void *D, size_t ldd, const float *bias, bool mn_major, unsigned int *err_word, int sms, cudaStream_t s) {
+    if (dtype != FLSTM_DTYPE_F16 && dtype != FLSTM_DTYPE_BF16)
+        return set_error(FLSTM_ERR_UNSUPPORTED, "tensor-core GEMM operands must be f16 or bf16");
+    if (M == 0 || N == 0 || K == 0) return FLSTM_OK;
+    if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+        return set_error(FLSTM_ERR_UNSUPPORTED, "tensor-core GEMM needs 16-byte aligned operands and row pitches");
+    const int BN = (N > 128) ? 256 : 128;
+    CUtensorMap ta, tb;
+    if (!mn_major) {
+        // A is (M,K) with K contiguous, B is (N,K) with K contiguous
+        FLSTM_TRY(make_tensor_map_2d(&ta, A, M, K, lda, BM, BK, true));
+        FLSTM_TRY(make_tensor_map_2d(&tb, B, N, K, ldb, BN, BK, true));
+    } else {
+        // A is stored (K,M) with M contiguous, B is stored (K,N) with N contiguous; 64x64 boxes
+        FLSTM_TRY(make_tensor_map_2d(&ta, A, K, M, lda, BK, 64, true));
+        FLSTM_TRY(make_tensor_map_2d(&tb, B, K, N, ldb, BK, 64, true));
+    }
+    const uint32_t idesc = umma_idesc_f16(BM, BN, dtype == FLSTM_DTYPE_BF16 ? 1 : 0, mn_major ? 1 : 0, mn_major ? 1 : 0);
+    if (BN == 256)
+        return dispatch<256>(out_dtype, bias != nullptr, mn_major, ta, tb, D, ldd, bias, (int)M, (int)N, (int)K, idesc,
+                             err_word, sms, s);
+    return dispatch<128>(out_dtype, bias != nullptr, mn_major, ta, tb, D, ldd, bias, (int)M, (int)N, (int)K, idesc,
+                         err_word, sms, s);
+}
+
+// ------------------------------------------------------------------ tensor-map encoding (host)
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+    return fn;
+}
+
+}  // namespace
+
+int make_tensor_map_2d(CUtensorMap *out, const void *base, uint64_t rows, uint64_t cols, uint64_t row_pitch_elems,
+                       uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return set_error(FLSTM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {row_pitch_elems * 2};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return set_error(FLSTM_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for a %llux%llu tensor, pitch %llu, box %ux%u",
+                         (int)r, (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)row_pitch_elems,
+                         box_rows, box_cols);
+    return FLSTM_OK;
+}
+
+int make_tensor_map_3d(CUtensorMap *out, const void *base, uint64_t d2, uint64_t rows, uint64_t cols,
+                       uint64_t row_pitch_elems, uint64_t d2_pitch_elems, uint32_t box_rows, uint32_t box_cols,
+                       bool swizzle128) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return set_error(FLSTM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[3] = {cols, rows, d2};
+    cuuint64_t strides[2] = {row_pitch_elems * 2, d2_pitch_elems * 2};
+    cuuint32_t box[3] = {box_cols, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(FLSTM_ERR_CUDA, "cuTensorMapEncodeTiled (3-D) failed (%d)", (int)r);
+    return FLSTM_OK;
+}
+
+}  // namespace tc
+}  // namespace flstm_b200
