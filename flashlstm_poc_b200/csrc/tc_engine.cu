@@ -1,27 +1,279 @@
-// Tensor-core (tcgen05 / TMEM / TMA) path of the engine.
+// Tensor-core (tcgen05 / TMEM / TMA) path of the engine: planning, tensor maps, weight packing in
+// the tile-interleaved gate order, and the per-layer forward / backward schedules.
+//
+// Gate order.  Every 4H-indexed tensor of this path (rows of W_ih and W_hh, the bias, the columns
+// of the projection / gate cache and of dG) uses the tile-interleaved order
+//     index(g, u) = ((u / 16) * 4 + g) * 16 + u % 16
+// so that the 64 rows a recurrent CTA owns are the four gates of 16 hidden units.  Weight and bias
+// gradients are written back in torch order (g*H + u) by the GEMM epilogue / a small kernel.
+#include <cstdlib>
+#include <vector>
+
 #include "common.cuh"
 #include "engine.h"
 #include "kernels.h"
+#include "tc_common.cuh"
 #include "tc_kernels.h"
 
 namespace flstm_b200 {
 namespace tc {
 
-bool supported(const flstm_engine_config &) { return false; }
-int init(Engine &) { return FLSTM_OK; }
-void destroy(Engine &) {}
-int on_capacity_change(Engine &) { return FLSTM_OK; }
-int set_weights(Engine &, int, const float *, const float *, const float *, const float *, cudaStream_t) {
-    return set_error(FLSTM_ERR_UNSUPPORTED, "tensor-core path not available");
-}
-int forward_layer(Engine &, int, size_t, const void *, void *, cudaStream_t) {
-    return set_error(FLSTM_ERR_UNSUPPORTED, "tensor-core path not available");
-}
-int backward_layer(Engine &, int, size_t, const void *, const void *, const void *, const void *, void *, float *,
-                   float *, cudaStream_t) {
-    return set_error(FLSTM_ERR_UNSUPPORTED, "tensor-core path not available");
+namespace {
+
+struct TcLayer {
+    CUtensorMap tm_w;   // w_hh (4H, H), 64x64 boxes, 128B swizzle
+    CUtensorMap tm_h;   // hs (Tcap+1, B, H), 1 x BT x 64 boxes, 128B swizzle
+    CUtensorMap tm_g;   // gates (Tcap, B, 4H), 1 x BT x 64 boxes, no swizzle
+    CUtensorMap tm_dg;  // dG (Tcap, B, 4H), 1 x BT x 64 boxes, 128B swizzle (BPTT operand)
+};
+
+struct TcState {
+    int sms = 0;
+    size_t smem_limit = 0;
+    FwdPlan fwd{};
+    BwdPlan bwd{};
+    bool bwd_ok = false;
+    std::vector<TcLayer> layers;
+    unsigned int *err_host = nullptr;  // pinned mirror of the device error word
+};
+
+TcState *state(Engine &e) { return static_cast<TcState *>(e.tc_state); }
+
+__device__ __forceinline__ int interleaved_to_torch_row(int r, int H) {
+    const int tile = r >> 6, g = (r >> 4) & 3, u = r & 15;
+    return g * H + tile * 16 + u;
 }
 
+template <typename T>
+__global__ void pack_rows_kernel(const float *__restrict__ w, int H, int K, T *__restrict__ out) {
+    const size_t total = (size_t)4 * H * K;
+    size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const int r = (int)(i / K), k = (int)(i % K);
+        st(out + i, w[(size_t)interleaved_to_torch_row(r, H) * K + k]);
+    }
+}
+
+__global__ void pack_bias_kernel(const float *__restrict__ a, const float *__restrict__ b, int H, float *__restrict__ out) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < 4 * H) {
+        const int o = interleaved_to_torch_row(r, H);
+        out[r] = a[o] + b[o];
+    }
+}
+
+__global__ void unpermute_kernel(const float *__restrict__ in, int H, float *__restrict__ out) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < 4 * H) out[interleaved_to_torch_row(r, H)] = in[r];
+}
+
+int check_launch(const char *what) {
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(err));
+    return FLSTM_OK;
+}
+
+inline char *byte_ptr(void *p) { return static_cast<char *>(p); }
+inline const char *byte_ptr(const void *p) { return static_cast<const char *>(p); }
+
+}  // namespace
+
+int pack_weights_interleaved(int dtype, const float *w, size_t H, size_t K, void *out, cudaStream_t s) {
+    const size_t total = 4 * H * K;
+    int grid = (int)((total + 255) / 256);
+    if (grid > 148 * 16) grid = 148 * 16;
+    if (dtype == FLSTM_DTYPE_F16) pack_rows_kernel<<<grid, 256, 0, s>>>(w, (int)H, (int)K, static_cast<__half *>(out));
+    else pack_rows_kernel<<<grid, 256, 0, s>>>(w, (int)H, (int)K, static_cast<__nv_bfloat16 *>(out));
+    return check_launch("pack_weights");
+}
+
+int pack_bias_interleaved(const float *b_ih, const float *b_hh, size_t H, float *out, cudaStream_t s) {
+    pack_bias_kernel<<<(int)((4 * H + 255) / 256), 256, 0, s>>>(b_ih, b_hh, (int)H, out);
+    return check_launch("pack_bias");
+}
+
+int unpermute_vector(const float *in, size_t H, float *out, cudaStream_t s) {
+    unpermute_kernel<<<(int)((4 * H + 255) / 256), 256, 0, s>>>(in, (int)H, out);
+    return check_launch("unpermute");
+}
+
+bool supported(const flstm_engine_config &cfg) {
+    if (cfg.dtype != FLSTM_DTYPE_F16 && cfg.dtype != FLSTM_DTYPE_BF16) return false;
+    if (cfg.hidden_size % 64 || cfg.input_size % 8) return false;
+    const char *off = std::getenv("FLSTM_DISABLE_TC");
+    if (off && off[0] == '1') return false;
+    int dev = 0, major = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return false;
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (major != 10) return false;
+    FwdPlan fp;
+    int optin = 0;
+    cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    if (plan_fwd((int)cfg.batch, (int)cfg.hidden_size, device_sm_count(), (size_t)optin, &fp) != FLSTM_OK) return false;
+    if (cfg.training) {
+        BwdPlan bp;
+        if (plan_bwd((int)cfg.batch, (int)cfg.hidden_size, device_sm_count(), (size_t)optin, &bp) != FLSTM_OK) return false;
+    }
+    return true;
+}
+
+int init(Engine &e) {
+    TcState *st = new TcState();
+    e.tc_state = st;
+    st->sms = device_sm_count();
+    int optin = 0;
+    FLSTM_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, e.device));
+    st->smem_limit = (size_t)optin;
+    FLSTM_TRY(plan_fwd((int)e.cfg.batch, (int)e.cfg.hidden_size, st->sms, st->smem_limit, &st->fwd));
+    if (e.cfg.training) {
+        FLSTM_TRY(plan_bwd((int)e.cfg.batch, (int)e.cfg.hidden_size, st->sms, st->smem_limit, &st->bwd));
+        st->bwd_ok = true;
+    }
+    st->layers.resize(e.layers.size());
+    void *raw = nullptr;
+    FLSTM_CUDA_TRY(cudaMalloc(&raw, 1024 * sizeof(unsigned int)));
+    e.sync_words = static_cast<unsigned int *>(raw);
+    FLSTM_CUDA_TRY(cudaMemset(raw, 0, 1024 * sizeof(unsigned int)));
+    FLSTM_CUDA_TRY(cudaMalloc(&raw, 4 * e.cfg.hidden_size * sizeof(float)));
+    e.db_part = static_cast<float *>(raw);
+    FLSTM_CUDA_TRY(cudaMallocHost(&raw, sizeof(unsigned int)));
+    st->err_host = static_cast<unsigned int *>(raw);
+    *st->err_host = 0;
+    return FLSTM_OK;
+}
+
+void destroy(Engine &e) {
+    TcState *st = state(e);
+    if (!st) return;
+    if (st->err_host) cudaFreeHost(st->err_host);
+    delete st;
+    e.tc_state = nullptr;
+}
+
+int on_capacity_change(Engine &e) {
+    TcState *st = state(e);
+    const size_t B = e.cfg.batch, H = e.cfg.hidden_size, cap = e.t_cap;
+    for (size_t li = 0; li < e.layers.size(); ++li) {
+        auto &l = e.layers[li];
+        auto &t = st->layers[li];
+        FLSTM_TRY(make_tensor_map_2d(&t.tm_w, l.w_hh, 4 * H, H, H, 64, 64, true));
+        FLSTM_TRY(make_tensor_map_3d(&t.tm_h, l.hs, cap + 1, B, H, H, B * H, st->fwd.BT, 64, true));
+        FLSTM_TRY(make_tensor_map_3d(&t.tm_g, l.gates, cap, B, 4 * H, 4 * H, B * 4 * H, st->fwd.BT, 64, false));
+        if (e.cfg.training && l.dg)
+            FLSTM_TRY(make_tensor_map_3d(&t.tm_dg, l.dg, cap, B, 4 * H, 4 * H, B * 4 * H, st->bwd.BT, 64, true));
+    }
+    return FLSTM_OK;
+}
+
+int set_weights(Engine &e, int layer, const float *w_ih, const float *w_hh, const float *b_ih, const float *b_hh,
+                cudaStream_t s) {
+    auto &l = e.layers[layer];
+    const size_t H = e.cfg.hidden_size;
+    FLSTM_TRY(pack_weights_interleaved(e.cfg.dtype, w_ih, H, l.in_size, l.w_ih, s));
+    FLSTM_TRY(pack_weights_interleaved(e.cfg.dtype, w_hh, H, H, l.w_hh, s));
+    FLSTM_TRY(pack_bias_interleaved(b_ih, b_hh, H, l.bias, s));
+    return FLSTM_OK;
+}
+
+// Deferred error reporting: the device error word is mirrored into pinned host memory after each
+// layer; a non-zero mirror fails the NEXT call (and flstm_engine_synchronize reports it at once).
+static int check_async_error(Engine &e) {
+    TcState *st = state(e);
+    if (st && *st->err_host) {
+        const unsigned int code = *st->err_host;
+        *st->err_host = 0;
+        cudaMemset(e.sync_words, 0, sizeof(unsigned int));
+        return set_error(FLSTM_ERR_TIMEOUT, "a bounded device-side wait expired in a persistent kernel (code %u)", code);
+    }
+    return FLSTM_OK;
+}
+
+int poll_error(Engine &e) { return check_async_error(e); }
+
+int forward_layer(Engine &e, int li, size_t T, const void *x_l, void *y_out, cudaStream_t s) {
+    TcState *st = state(e);
+    FLSTM_TRY(check_async_error(e));
+    auto &l = e.layers[li];
+    auto &t = st->layers[li];
+    const size_t B = e.cfg.batch, H = e.cfg.hidden_size;
+    unsigned int *err = e.sync_words;
+    size_t m0 = e.timer.mark(s);
+    // P = X W_ih^T + (b_ih + b_hh), 16-bit, columns tile-interleaved
+    FLSTM_TRY(gemm(e.cfg.dtype, e.cfg.dtype, T * B, 4 * H, l.in_size, x_l, l.in_size, false, l.w_ih, l.in_size, false,
+                   l.gates, 4 * H, l.bias, 0, err, st->sms, s));
+    size_t m1 = e.timer.mark(s);
+    FLSTM_CUDA_TRY(cudaMemsetAsync(e.sync_words + 1, 0, (size_t)st->fwd.ngroups * sizeof(unsigned int), s));
+    FwdParams p{};
+    p.cs = l.cs;
+    p.hs = l.hs;
+    p.y = y_out;
+    p.counters = e.sync_words + 1;
+    p.err = err;
+    p.T = (int)T;
+    p.B = (int)B;
+    p.H = (int)H;
+    p.store_gates = e.cfg.training ? 1 : 0;
+    FLSTM_TRY(lstm_forward_persistent(e.cfg.dtype, st->fwd, t.tm_w, t.tm_h, t.tm_g, p, s));
+    size_t m2 = e.timer.mark(s);
+    e.timer.span(PH_PROJ, m0, m1);
+    e.timer.span(PH_RECUR_FWD, m1, m2);
+    e.launches += 2;
+    FLSTM_CUDA_TRY(cudaMemcpyAsync(st->err_host, err, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
+    return FLSTM_OK;
+}
+
+int backward_layer(Engine &e, int li, size_t T, const void *x_l, const void *dy_l, const void *dhn_l,
+                   const void *dcn_l, void *dx_l, float *dh0_l, float *dc0_l, cudaStream_t s) {
+    TcState *st = state(e);
+    FLSTM_TRY(check_async_error(e));
+    if (!st->bwd_ok) return set_error(FLSTM_ERR_UNSUPPORTED, "tensor-core backward is not planned for this engine");
+    auto &l = e.layers[li];
+    auto &t = st->layers[li];
+    const size_t B = e.cfg.batch, H = e.cfg.hidden_size;
+    unsigned int *err = e.sync_words;
+    size_t m0 = e.timer.mark(s);
+    FLSTM_CUDA_TRY(cudaMemsetAsync(e.sync_words + 1, 0, (size_t)st->bwd.ngroups * sizeof(unsigned int), s));
+    BwdParams p{};
+    p.cs = l.cs;
+    p.gates = l.gates;
+    p.dg = l.dg;
+    p.dy = dy_l;
+    p.dhn = dhn_l;
+    p.dcn = dcn_l;
+    p.dh0 = dh0_l;
+    p.dc0 = dc0_l;
+    p.dc = e.dc;
+    p.counters = e.sync_words + 1;
+    p.err = err;
+    p.T = (int)T;
+    p.B = (int)B;
+    p.H = (int)H;
+    FLSTM_TRY(lstm_backward_persistent(e.cfg.dtype, st->bwd, t.tm_w, t.tm_dg, p, s));
+    size_t m1 = e.timer.mark(s);
+    // dW = dG^T [X | H_prev]: both operands read as stored (reduction dim T*B outermost); rows of
+    // the product are written back in torch gate order
+    FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, l.in_size, T * B, l.dg, 4 * H, true, x_l, l.in_size, true,
+                   l.dw_ih, l.in_size, nullptr, (int)H, err, st->sms, s));
+    FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, H, T * B, l.dg, 4 * H, true, l.hs, H, true, l.dw_hh, H, nullptr,
+                   (int)H, err, st->sms, s));
+    FLSTM_TRY(simt::column_sum(e.cfg.dtype, l.dg, T * B, 4 * H, e.db_part, s));
+    FLSTM_TRY(unpermute_vector(e.db_part, H, l.db, s));
+    size_t m2 = e.timer.mark(s);
+    if (dx_l) {
+        // dX = dG W_ih: W_ih (rows tile-interleaved, like dG's columns) is read as stored
+        FLSTM_TRY(gemm(e.cfg.dtype, e.cfg.dtype, T * B, l.in_size, 4 * H, l.dg, 4 * H, false, l.w_ih, l.in_size, true,
+                       dx_l, l.in_size, nullptr, 0, err, st->sms, s));
+        ++e.launches;
+    }
+    size_t m3 = e.timer.mark(s);
+    e.timer.span(PH_BPTT, m0, m1);
+    e.timer.span(PH_WGRAD, m1, m2);
+    e.timer.span(PH_XGRAD, m2, m3);
+    e.launches += 5;
+    FLSTM_CUDA_TRY(cudaMemcpyAsync(st->err_host, err, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
+    return FLSTM_OK;
+}
 
 // A device word per device for the stand-alone entry points (never freed; 4 bytes).
 static unsigned int *standalone_error_word() {
@@ -47,14 +299,17 @@ int device_sm_count() {
 }  // namespace flstm_b200
 
 extern "C" int flstm_tc_gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, const void *B,
-                             void *D, size_t ldd, const float *bias, int mn_major, void *stream) {
+                             void *D, size_t ldd, const float *bias, int layout, void *stream) {
     using namespace flstm_b200;
     if (!A || !B || !D) return set_error(FLSTM_ERR_INVALID, "null pointer argument");
+    if (layout < 0 || layout > 2) return set_error(FLSTM_ERR_INVALID, "layout must be 0, 1 or 2");
     unsigned int *err = tc::standalone_error_word();
     if (!err) return set_error(FLSTM_ERR_CUDA, "could not allocate the error word");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const size_t lda = mn_major ? M : K, ldb = mn_major ? N : K;
-    FLSTM_TRY(tc::gemm(dtype, out_dtype, M, N, K, A, lda, B, ldb, D, ldd, bias, mn_major != 0, err, tc::device_sm_count(), s));
+    const bool a_mn = layout == 1, b_mn = layout >= 1;
+    const size_t lda = a_mn ? M : K, ldb = b_mn ? N : K;
+    FLSTM_TRY(tc::gemm(dtype, out_dtype, M, N, K, A, lda, a_mn, B, ldb, b_mn, D, ldd, bias, 0, err,
+                       tc::device_sm_count(), s));
     unsigned int h = 0;
     FLSTM_CUDA_TRY(cudaMemcpyAsync(&h, err, sizeof(h), cudaMemcpyDeviceToHost, s));
     FLSTM_CUDA_TRY(cudaStreamSynchronize(s));

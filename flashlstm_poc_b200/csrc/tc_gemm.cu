@@ -89,10 +89,17 @@ __device__ __forceinline__ void store_row32(void *dst_row, int col0, const uint3
     }
 }
 
-template <int BN, int MODE, bool HAS_BIAS, bool MN_MAJOR>
+// Output rows may be written through the inverse of the tile-interleaved gate order: row
+// r' = ((u/16)*4 + g)*16 + u%16 of the product goes to row g*H + u of D (unperm_h = H, else 0).
+__device__ __forceinline__ int unpermute_gate_row(int r, int H) {
+    const int tile = r >> 6, g = (r >> 4) & 3, u = r & 15;
+    return g * H + tile * 16 + u;
+}
+
+template <int BN, int MODE, bool HAS_BIAS, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, void *__restrict__ D,
-            size_t ldd, const float *__restrict__ bias, int M, int N, int K, uint32_t idesc,
+            size_t ldd, const float *__restrict__ bias, int M, int N, int K, uint32_t idesc, int unperm_h,
             unsigned int *__restrict__ err_word) {
     using S = GemmShape<BN>;
     extern __shared__ uint8_t smem_raw[];
@@ -142,12 +149,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     if (!ok) break;
                     uint8_t *sa = smem + stage * S::kStageBytes, *sb = sa + S::kABytes;
                     mbar_expect_tx(&full[stage], S::kStageBytes);
-                    if (!MN_MAJOR) {
+                    if (!A_MN) {
                         tma_load_2d(sa, &tm_a, kb * BK, m0, &full[stage]);
-                        tma_load_2d(sb, &tm_b, kb * BK, n0, &full[stage]);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tm_a, m0 + j * 64, kb * BK, &full[stage]);
+                    }
+                    if (!B_MN) {
+                        tma_load_2d(sb, &tm_b, kb * BK, n0, &full[stage]);
+                    } else {
 #pragma unroll
                         for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tm_b, n0 + j * 64, kb * BK, &full[stage]);
                     }
@@ -175,14 +185,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     const uint32_t a_base = smem_u32(smem + stage * S::kStageBytes), b_base = a_base + S::kABytes;
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
-                        uint64_t da, db;
-                        if (!MN_MAJOR) {
-                            da = umma_desc_kmajor_sw128(a_base + k * 32);
-                            db = umma_desc_kmajor_sw128(b_base + k * 32);
-                        } else {
-                            da = umma_desc_mnmajor_sw128(a_base + k * 2048, 8192);
-                            db = umma_desc_mnmajor_sw128(b_base + k * 2048, 8192);
-                        }
+                        const uint64_t da = A_MN ? umma_desc_mnmajor_sw128(a_base + k * 2048, 8192)
+                                                 : umma_desc_kmajor_sw128(a_base + k * 32);
+                        const uint64_t db = B_MN ? umma_desc_mnmajor_sw128(b_base + k * 2048, 8192)
+                                                 : umma_desc_kmajor_sw128(b_base + k * 32);
                         umma_f16(d_tmem, da, db, idesc, (kb | k) != 0);
                     }
                     umma_commit(&empty[stage]);
@@ -203,7 +209,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             tcgen05_fence_after();
             const int row = m0 + q * 32 + lane;
             const size_t esz = (MODE == OUT_F32) ? 4 : 2;
-            char *dst_row = static_cast<char *>(D) + (size_t)row * ldd * esz;
+            const int out_row = (unperm_h && row < M) ? unpermute_gate_row(row, unperm_h) : row;
+            char *dst_row = static_cast<char *>(D) + (size_t)out_row * ldd * esz;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t acc[32];
@@ -223,72 +230,96 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     if (threadIdx.x == 0 && *abort_w) atomicExch(err_word, 1u);
 }
 
-template <int BN, int MODE, bool HAS_BIAS, bool MN_MAJOR>
-int launch(const CUtensorMap &ta, const CUtensorMap &tb, void *D, size_t ldd, const float *bias, int M, int N, int K,
-           uint32_t idesc, unsigned int *err_word, int sms, cudaStream_t s) {
+struct GemmArgs {
+    CUtensorMap ta, tb;
+    void *D;
+    size_t ldd;
+    const float *bias;
+    int M, N, K;
+    uint32_t idesc;
+    int unperm_h;
+    unsigned int *err;
+    int sms;
+    cudaStream_t s;
+};
+
+template <int BN, int MODE, bool HAS_BIAS, bool A_MN, bool B_MN>
+int launch(const GemmArgs &g) {
     using S = GemmShape<BN>;
-    auto kern = gemm_kernel<BN, MODE, HAS_BIAS, MN_MAJOR>;
+    auto kern = gemm_kernel<BN, MODE, HAS_BIAS, A_MN, B_MN>;
     static bool configured = false;  // per instantiation
     if (!configured) {
         FLSTM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes));
         configured = true;
     }
-    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    const int grid = tiles < sms ? tiles : sms;
-    kern<<<grid, kGemmThreads, S::kSmemBytes, s>>>(ta, tb, D, ldd, bias, M, N, K, idesc, err_word);
+    const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
+    const int grid = tiles < g.sms ? tiles : g.sms;
+    kern<<<grid, kGemmThreads, S::kSmemBytes, g.s>>>(g.ta, g.tb, g.D, g.ldd, g.bias, g.M, g.N, g.K, g.idesc, g.unperm_h,
+                                                    g.err);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "tc gemm launch failed: %s", cudaGetErrorString(e));
     return FLSTM_OK;
 }
 
 template <int BN>
-int dispatch(int out_dtype, bool has_bias, bool mn, const CUtensorMap &ta, const CUtensorMap &tb, void *D, size_t ldd,
-             const float *bias, int M, int N, int K, uint32_t idesc, unsigned int *err, int sms, cudaStream_t s) {
-    if (mn) {
+int dispatch(int out_dtype, bool a_mn, bool b_mn, const GemmArgs &g) {
+    const bool has_bias = g.bias != nullptr;
+    if (a_mn && b_mn) {
         if (out_dtype != FLSTM_DTYPE_F32 || has_bias)
-            return set_error(FLSTM_ERR_UNSUPPORTED, "MN-major operands are instantiated for fp32 output without bias");
-        return launch<BN, OUT_F32, false, true>(ta, tb, D, ldd, bias, M, N, K, idesc, err, sms, s);
+            return set_error(FLSTM_ERR_UNSUPPORTED, "MN-major x MN-major is instantiated for fp32 output without bias");
+        return launch<BN, OUT_F32, false, true, true>(g);
+    }
+    if (a_mn) return set_error(FLSTM_ERR_UNSUPPORTED, "MN-major A with K-major B is not instantiated");
+    if (b_mn) {
+        if (has_bias) return set_error(FLSTM_ERR_UNSUPPORTED, "bias with an MN-major B is not instantiated");
+        switch (out_dtype) {
+            case FLSTM_DTYPE_F32: return launch<BN, OUT_F32, false, false, true>(g);
+            case FLSTM_DTYPE_F16: return launch<BN, OUT_F16, false, false, true>(g);
+            case FLSTM_DTYPE_BF16: return launch<BN, OUT_BF16, false, false, true>(g);
+        }
+        return set_error(FLSTM_ERR_INVALID, "bad output dtype");
     }
     switch (out_dtype) {
         case FLSTM_DTYPE_F32:
             if (has_bias) return set_error(FLSTM_ERR_UNSUPPORTED, "bias with fp32 output is not instantiated");
-            return launch<BN, OUT_F32, false, false>(ta, tb, D, ldd, bias, M, N, K, idesc, err, sms, s);
+            return launch<BN, OUT_F32, false, false, false>(g);
         case FLSTM_DTYPE_F16:
-            return has_bias ? launch<BN, OUT_F16, true, false>(ta, tb, D, ldd, bias, M, N, K, idesc, err, sms, s)
-                            : launch<BN, OUT_F16, false, false>(ta, tb, D, ldd, bias, M, N, K, idesc, err, sms, s);
+            return has_bias ? launch<BN, OUT_F16, true, false, false>(g) : launch<BN, OUT_F16, false, false, false>(g);
         case FLSTM_DTYPE_BF16:
-            return has_bias ? launch<BN, OUT_BF16, true, false>(ta, tb, D, ldd, bias, M, N, K, idesc, err, sms, s)
-                            : launch<BN, OUT_BF16, false, false>(ta, tb, D, ldd, bias, M, N, K, idesc, err, sms, s);
+            return has_bias ? launch<BN, OUT_BF16, true, false, false>(g) : launch<BN, OUT_BF16, false, false, false>(g);
     }
     return set_error(FLSTM_ERR_INVALID, "bad output dtype");
 }
 
 }  // namespace
 
-int gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, size_t lda, const void *B, size_t ldb,
-         void *D, size_t ldd, const float *bias, bool mn_major, unsigned int *err_word, int sms, cudaStream_t s) {
+int gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, size_t lda, bool a_mn, const void *B,
+         size_t ldb, bool b_mn, void *D, size_t ldd, const float *bias, int unperm_h, unsigned int *err_word, int sms,
+         cudaStream_t s) {
     if (dtype != FLSTM_DTYPE_F16 && dtype != FLSTM_DTYPE_BF16)
         return set_error(FLSTM_ERR_UNSUPPORTED, "tensor-core GEMM operands must be f16 or bf16");
     if (M == 0 || N == 0 || K == 0) return FLSTM_OK;
     if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
         return set_error(FLSTM_ERR_UNSUPPORTED, "tensor-core GEMM needs 16-byte aligned operands and row pitches");
     const int BN = (N > 128) ? 256 : 128;
-    CUtensorMap ta, tb;
-    if (!mn_major) {
-        // A is (M,K) with K contiguous, B is (N,K) with K contiguous
-        FLSTM_TRY(make_tensor_map_2d(&ta, A, M, K, lda, BM, BK, true));
-        FLSTM_TRY(make_tensor_map_2d(&tb, B, N, K, ldb, BN, BK, true));
-    } else {
-        // A is stored (K,M) with M contiguous, B is stored (K,N) with N contiguous; 64x64 boxes
-        FLSTM_TRY(make_tensor_map_2d(&ta, A, K, M, lda, BK, 64, true));
-        FLSTM_TRY(make_tensor_map_2d(&tb, B, K, N, ldb, BK, 64, true));
-    }
-    const uint32_t idesc = umma_idesc_f16(BM, BN, dtype == FLSTM_DTYPE_BF16 ? 1 : 0, mn_major ? 1 : 0, mn_major ? 1 : 0);
-    if (BN == 256)
-        return dispatch<256>(out_dtype, bias != nullptr, mn_major, ta, tb, D, ldd, bias, (int)M, (int)N, (int)K, idesc,
-                             err_word, sms, s);
-    return dispatch<128>(out_dtype, bias != nullptr, mn_major, ta, tb, D, ldd, bias, (int)M, (int)N, (int)K, idesc,
-                         err_word, sms, s);
+    GemmArgs g{};
+    // K-major: (rows, K) with K contiguous, box rows x 64.  MN-major: stored (K, rows), 64 x 64 boxes.
+    if (!a_mn) FLSTM_TRY(make_tensor_map_2d(&g.ta, A, M, K, lda, BM, BK, true));
+    else FLSTM_TRY(make_tensor_map_2d(&g.ta, A, K, M, lda, BK, 64, true));
+    if (!b_mn) FLSTM_TRY(make_tensor_map_2d(&g.tb, B, N, K, ldb, BN, BK, true));
+    else FLSTM_TRY(make_tensor_map_2d(&g.tb, B, K, N, ldb, BK, 64, true));
+    g.D = D;
+    g.ldd = ldd;
+    g.bias = bias;
+    g.M = (int)M;
+    g.N = (int)N;
+    g.K = (int)K;
+    g.idesc = umma_idesc_f16(BM, BN, dtype == FLSTM_DTYPE_BF16 ? 1 : 0, a_mn ? 1 : 0, b_mn ? 1 : 0);
+    g.unperm_h = unperm_h;
+    g.err = err_word;
+    g.sms = sms;
+    g.s = s;
+    return BN == 256 ? dispatch<256>(out_dtype, a_mn, b_mn, g) : dispatch<128>(out_dtype, a_mn, b_mn, g);
 }
 
 // ------------------------------------------------------------------ tensor-map encoding (host)

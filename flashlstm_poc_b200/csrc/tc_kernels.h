@@ -1,21 +1,97 @@
 // Host-side launchers of the tensor-core path kernels (tc_*.cu).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <cstddef>
+#include <cstdint>
 
 namespace flstm_b200 {
 namespace tc {
 
 // D[M,N] (row pitch ldd, dtype out_dtype) = A B^T (+ bias[N]), fp32 accumulation in TMEM.
-//   mn_major == false: A is (M,K) row-major with pitch lda, B is (N,K) row-major with pitch ldb.
-//   mn_major == true : A is stored (K,M) with pitch lda, B is stored (K,N) with pitch ldb (fp32 out only).
+//   a_mn == false: A is (M,K) row-major with pitch lda;  a_mn == true: A is stored (K,M) with pitch lda.
+//   b_mn == false: B is (N,K) row-major with pitch ldb;  b_mn == true: B is stored (K,N) with pitch ldb.
+//   unperm_h != 0: output rows are written through the inverse tile-interleaved gate order (H = unperm_h).
 // `err_word` is a device word the kernel sets to 1 if a bounded wait expired.
-int gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, size_t lda, const void *B, size_t ldb,
-         void *D, size_t ldd, const float *bias, bool mn_major, unsigned int *err_word, int sms, cudaStream_t s);
+int gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, size_t lda, bool a_mn, const void *B,
+         size_t ldb, bool b_mn, void *D, size_t ldd, const float *bias, int unperm_h, unsigned int *err_word, int sms,
+         cudaStream_t s);
 
 int device_sm_count();
+
+// ------------------------------------------------------------------ persistent recurrent forward
+struct FwdPlan {
+    int BT;        // sequences per batch tile (UMMA N): 32 or 64
+    int rt;        // row tiles (64 gate rows = 16 hidden units x 4 gates) per CTA
+    int cta_rows;  // CTAs along the row-tile axis = (H/16) / rt
+    int ngroups;   // batch groups (each with its own step barrier)
+    int nt;        // batch tiles per group
+    int stages;    // TMA ring depth
+    bool resident; // W_hh slice stays in shared memory for the whole sequence
+    int smem_bytes;
+    int grid;
+};
+
+struct FwdParams {
+    float *cs;            // fp32 (T+1, B, H) cell states, slot 0 = c0
+    void *hs;             // 16-bit (T+1, B, H) hidden states, slot 0 = h0
+    void *y;              // optional 16-bit (T, B, H) copy of h_t for the caller
+    unsigned int *counters;  // one step counter per batch group, zeroed before the launch
+    unsigned int *err;    // error word: non-zero after a bounded wait expired
+    int T, B, H;
+    int store_gates;      // write the activated gates back (the gate cache)
+    // filled by the launcher from the plan
+    int rt, cta_rows, nt, stages;
+    uint32_t idesc;
+};
+
+int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan);
+// tm_w: W_hh rows tile-interleaved (4H, H), box 64x64, 128B swizzle.  tm_h: hidden states as
+// (T+1, B, H), box 1 x BT x 64, 128B swizzle.  tm_g: projection / gate cache as (T, B, 4H), box
+// 1 x BT x 64, no swizzle (loaded and stored).
+int lstm_forward_persistent(int dtype, const FwdPlan &plan, const CUtensorMap &tm_w, const CUtensorMap &tm_h,
+                            const CUtensorMap &tm_g, FwdParams p, cudaStream_t s);
+
+// ------------------------------------------------------------------ persistent BPTT
+struct BwdPlan {
+    int BT;        // sequences per batch tile
+    int KS;        // cluster size: CTAs that split the K = 4H contraction of one 64-unit tile
+    int jt;        // unit tiles = H / 64
+    int ngroups, nt, stages;
+    bool resident;
+    int smem_bytes;
+    int grid;
+};
+
+struct BwdParams {
+    const float *cs;      // fp32 (T+1, B, H) cell states from the forward
+    const void *gates;    // 16-bit (T, B, 4H) post-activation gate cache, tile-interleaved columns
+    void *dg;             // 16-bit (T, B, 4H) pre-activation gradients (written), same column order
+    const void *dy;       // 16-bit (T, B, H)
+    const void *dhn;      // 16-bit (B, H) or null
+    const void *dcn;      // 16-bit (B, H) or null
+    float *dh0, *dc0;     // fp32 (B, H) or null
+    float *dc;            // fp32 (B, H) scratch for the cell-gradient carry (used when nt > 1)
+    unsigned int *counters;
+    unsigned int *err;
+    int T, B, H;
+    int jt, nt, stages;
+    uint32_t idesc;
+};
+
+int plan_bwd(int B, int H, int sms, size_t smem_limit, BwdPlan *plan);
+// tm_w: the same map as the forward's (W_hh rows tile-interleaved, 64x64 boxes): the BPTT reads the
+// slice as an MN-major operand.  tm_dg: dG as (T, B, 4H), box 1 x BT x 64, 128B swizzle.
+int lstm_backward_persistent(int dtype, const BwdPlan &plan, const CUtensorMap &tm_w, const CUtensorMap &tm_dg,
+                             BwdParams p, cudaStream_t s);
+
+// fp32 (4H, K) torch-ordered rows -> 16-bit tile-interleaved rows; bias likewise (b_ih + b_hh)
+int pack_weights_interleaved(int dtype, const float *w, size_t H, size_t K, void *out, cudaStream_t s);
+int pack_bias_interleaved(const float *b_ih, const float *b_hh, size_t H, float *out, cudaStream_t s);
+// out[g*H + u] = in[tile-interleaved index of (g,u)]
+int unpermute_vector(const float *in, size_t H, float *out, cudaStream_t s);
 
 }  // namespace tc
 }  // namespace flstm_b200

@@ -1,0 +1,580 @@
+// Persistent BPTT kernel: ONE launch runs the whole reverse recurrence of one layer.
+//
+// Per reverse step the recurrence needs dh_{t} = dY_t + dG_{t+1} W_hh, a contraction over K = 4H.
+// Work split: a cluster of KS CTAs owns 64 hidden units (unit tile j); CTA kq of the cluster
+// contracts over its quarter (1/KS) of K with its slice of W_hh resident in shared memory (read as
+// stored, i.e. as an MN-major UMMA operand), the KS partial results are reduce-scattered through
+// distributed shared memory (st.shared::cluster + a remote mbarrier arrive), and every CTA then runs
+// the fused pointwise backward for its 64/KS units:
+//   producer warp : waits on the grid barrier for dG_{t+1}, streams it (BT x 64 chunks) via TMA
+//   MMA warp      : tcgen05.mma M=64 (hidden units) x N=BT (batch) x K=16 into TMEM
+//   4 epilogue warps: tcgen05.ld -> partials to the owner CTA's shared memory -> sum -> gate cache
+//                   (128-bit-segment loads), c_t, c_{t-1}, dY_t -> dG_t (16-bit, tile-interleaved),
+//                   dc carry in registers -> publish dG_t (release add on the group's counter)
+// The cell state is READ from the forward's cache; it is never reconstructed from y and o as the
+// reference does (flashlstm_v2/src/lstm_backward.cu:188-197).
+//
+// Replaces, per step, BackwardPointwiseKernel + GemmNN (flashlstm_v2/src/lstm_backward.cu:158-227,
+// 1057-1101) and the whole recompute loop (:991-1054), which the gate cache makes unnecessary.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "tc_common.cuh"
+#include "tc_kernels.h"
+
+namespace flstm_b200 {
+namespace tc {
+
+namespace {
+
+constexpr int kBwdThreads = 192;
+constexpr int kChunkBytesW = 64 * 64 * 2;
+
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int *p) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(unsigned int *p, unsigned int v) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cta address -> shared::cluster address of the same offset in CTA `rank`
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_w) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait_cluster(bar, parity)) {
+        if ((++spins & 255u) == 0) {
+            if (*abort_w) return false;
+            if (global_timer_ns() - t0 > kWaitLimitNs) {
+                *abort_w = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ bool wait_counter(const unsigned int *ctr, unsigned int target, unsigned int *err_word,
+                                             volatile uint32_t *abort_w) {
+    if (ld_acquire_gpu(ctr) >= target) return true;
+    const unsigned long long t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (ld_acquire_gpu(ctr) < target) {
+        if ((++spins & 63u) == 0) {
+            if (*abort_w) return false;
+            if (*reinterpret_cast<volatile unsigned int *>(err_word)) {
+                *abort_w = 1;
+                return false;
+            }
+            if (global_timer_ns() - t0 > kWaitLimitNs) {
+                *abort_w = 1;
+                atomicExch(err_word, 3u);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+template <bool BF16>
+__device__ __forceinline__ float load16(const uint16_t *p) {
+    if (BF16) return __bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(p));
+    return __half2float(*reinterpret_cast<const __half *>(p));
+}
+template <bool BF16>
+__device__ __forceinline__ uint16_t to16(float v) {
+    if (BF16) {
+        __nv_bfloat16 h = __float2bfloat16_rn(v);
+        return *reinterpret_cast<uint16_t *>(&h);
+    }
+    __half h = __float2half_rn(v);
+    return *reinterpret_cast<uint16_t *>(&h);
+}
+
+struct PairIn {
+    float gi, gf, gg, go, ct, cp, dy;
+};
+
+}  // namespace
+
+struct BwdSmemLayout {
+    int w_bytes, ring_stage_bytes, stages, red_bytes, total;
+};
+
+__host__ __device__ inline BwdSmemLayout bwd_smem_layout(int BT, int H, int KS, bool resident, int stages) {
+    BwdSmemLayout l;
+    const int kc_per = (H / 16) / KS;  // 64-wide K chunks this CTA contracts over
+    l.w_bytes = resident ? kc_per * kChunkBytesW : 0;
+    l.ring_stage_bytes = BT * 128 + (resident ? 0 : kChunkBytesW);
+    l.stages = stages;
+    l.red_bytes = 2 * KS * (64 / KS) * (BT + 1) * 4;  // 2 x [KS sources][64/KS units][BT+1]
+    l.total = l.w_bytes + stages * l.ring_stage_bytes + l.red_bytes + 1024 + 512;
+    return l;
+}
+
+template <int BT, int KS, bool W_RESIDENT, bool BF16>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_dg, BwdParams p) {
+    constexpr int UPO = 64 / KS;            // units this CTA owns after the reduce-scatter
+    constexpr int UQ = UPO / 16;            // 16-unit groups per owner
+    constexpr int PAIRS = UQ * (BT / 8);    // (unit, sequence) pairs per epilogue thread
+    constexpr bool PREFETCH = PAIRS <= 8;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int KCper = (p.H / 16) / KS;
+    const BwdSmemLayout L = bwd_smem_layout(BT, p.H, KS, W_RESIDENT, p.stages);
+    uint8_t *s_w = smem;
+    uint8_t *s_ring = s_w + L.w_bytes;
+    float *s_red = reinterpret_cast<float *>(s_ring + L.stages * L.ring_stage_bytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(s_red) + L.red_bytes);
+    uint64_t *full = bars, *empty = bars + L.stages;
+    uint64_t *tfull = empty + L.stages, *tempty = tfull + 2;
+    uint64_t *rbar = tempty + 2;  // [2] reduce-scatter arrival barriers (64 arrivals each)
+    uint64_t *wbar = rbar + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(wbar + 1);
+    volatile uint32_t *abort_w = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kq = (KS > 1) ? (int)cluster_ctarank() : 0;
+    const int cl = blockIdx.x / KS;          // cluster index
+    const int ng = cl / p.jt;                // batch group
+    const int j = cl % p.jt;                 // unit tile: hidden units [64j, 64j+64)
+    unsigned int *counter = p.counters + ng;
+    constexpr int kTmemCols = (2 * BT < 32) ? 32 : 2 * BT;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < L.stages; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&tfull[i], 1);
+            mbar_init(&tempty[i], 4);
+            mbar_init(&rbar[i], 64);
+        }
+        mbar_init(wbar, 1);
+        *abort_w = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tm_w);
+        tma_prefetch_desc(&tm_dg);
+    }
+    if (warp == 5) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    if (KS > 1) cluster_sync_all();  // every CTA's barriers exist before any remote arrive
+    const uint32_t tmem_base = *tmem_slot;
+    const int nt_count = p.nt;
+    const int c_first = kq * KCper;  // first K chunk (= forward row tile) of this CTA
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ producer
+        if (elect_one()) {
+            bool ok = true;
+            if (W_RESIDENT) {
+                mbar_expect_tx(wbar, (uint32_t)(KCper * kChunkBytesW));
+                for (int c = 0; c < KCper; ++c)
+                    tma_load_2d(s_w + c * kChunkBytesW, &tm_w, j * 64, (c_first + c) * 64, wbar);
+            }
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int s = 1; s <= p.T && ok; ++s) {
+                const int t_src = p.T - s;  // dG_{t+1} with t = T-1-s
+                ok = wait_counter(counter, (unsigned)(p.jt * KS * 4) * (unsigned)s, p.err, abort_w);
+                if (!ok) break;
+                fence_proxy_async_all();
+                for (int n = 0; n < nt_count && ok; ++n) {
+                    const int b0 = (ng * nt_count + n) * BT;
+                    for (int c = 0; c < KCper; ++c) {
+                        ok = mbar_wait(&empty[stage], phase ^ 1, abort_w);
+                        if (!ok) break;
+                        uint8_t *sd = s_ring + stage * L.ring_stage_bytes;
+                        mbar_expect_tx(&full[stage], (uint32_t)L.ring_stage_bytes);
+                        tma_load_3d(sd, &tm_dg, (c_first + c) * 64, b0, t_src, &full[stage]);
+                        if (!W_RESIDENT) tma_load_2d(sd + BT * 128, &tm_w, j * 64, (c_first + c) * 64, &full[stage]);
+                        if (++stage == L.stages) { stage = 0; phase ^= 1; }
+                    }
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            bool ok = true;
+            if (W_RESIDENT) ok = mbar_wait(wbar, 0, abort_w);
+            int stage = 0;
+            uint32_t phase = 0;
+            const uint32_t items = (uint32_t)p.T * nt_count;
+            for (uint32_t wi = 0; wi < items && ok; ++wi) {
+                const int buf = wi & 1;
+                ok = mbar_wait(&tempty[buf], ((wi >> 1) & 1) ^ 1, abort_w);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BT;
+                for (int c = 0; c < KCper; ++c) {
+                    ok = mbar_wait(&full[stage], phase, abort_w);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t dg_base = smem_u32(s_ring + stage * L.ring_stage_bytes);
+                    const uint32_t w_base = W_RESIDENT ? smem_u32(s_w + c * kChunkBytesW) : dg_base + BT * 128;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma_f16(d_tmem, umma_desc_mnmajor_sw128(w_base + k * 2048, 8192),
+                                 umma_desc_kmajor_sw128(dg_base + k * 32), p.idesc, (c | k) != 0);
+                    umma_commit(&empty[stage]);
+                    if (++stage == L.stages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(&tfull[buf]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (128 threads)
+        const int tid = threadIdx.x;
+        const int u16 = tid & 15, nb = tid >> 4;
+        const size_t slab = (size_t)p.B * p.H;
+        const size_t G = (size_t)4 * p.H;
+        const uint16_t *gates = static_cast<const uint16_t *>(p.gates);
+        const uint16_t *dy = static_cast<const uint16_t *>(p.dy);
+        const uint16_t *dhn = static_cast<const uint16_t *>(p.dhn);
+        const uint16_t *dcn = static_cast<const uint16_t *>(p.dcn);
+        uint16_t *dg = static_cast<uint16_t *>(p.dg);
+        const bool keep_dc = nt_count == 1;
+        float dc_keep[PAIRS];
+        const uint32_t red_local = smem_u32(s_red);
+        const uint32_t rbar_local = smem_u32(rbar);
+        uint32_t wi = 0;  // MMA item counter (iterations s >= 1)
+        bool ok = true;
+        for (int s = 0; s <= p.T && ok; ++s) {
+            const int t = p.T - 1 - s;  // time step whose dG is produced (t = -1: only dh0 / dc0)
+            for (int n = 0; n < nt_count && ok; ++n) {
+                const int b0 = (ng * nt_count + n) * BT;
+                PairIn in[PAIRS];
+                float dc_in[PAIRS];
+                auto unit_of = [&](int q) { return j * 64 + kq * UPO + q * 16 + u16; };
+                auto load_pair = [&](int q, int i, PairIn &v) {
+                    const int b = b0 + nb + 8 * i, U = unit_of(q);
+                    if (b < p.B && t >= 0) {
+                        const uint16_t *grow = gates + ((size_t)t * p.B + b) * G + (size_t)(U >> 4) * 64 + (U & 15);
+                        v.gi = load16<BF16>(grow);
+                        v.gf = load16<BF16>(grow + 16);
+                        v.gg = load16<BF16>(grow + 32);
+                        v.go = load16<BF16>(grow + 48);
+                        const size_t idx = (size_t)b * p.H + U;
+                        v.ct = p.cs[(size_t)(t + 1) * slab + idx];
+                        v.cp = p.cs[(size_t)t * slab + idx];
+                        v.dy = load16<BF16>(dy + (size_t)t * slab + idx);
+                    } else {
+                        v = PairIn{0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    }
+                };
+                // cell-gradient carry entering this step
+#pragma unroll
+                for (int q = 0; q < UQ; ++q)
+#pragma unroll
+                    for (int i = 0; i < BT / 8; ++i) {
+                        const int k = q * (BT / 8) + i;
+                        const int b = b0 + nb + 8 * i;
+                        const size_t idx = (size_t)b * p.H + unit_of(q);
+                        if (s == 0) dc_in[k] = (dcn && b < p.B) ? load16<BF16>(dcn + idx) : 0.f;
+                        else if (keep_dc) dc_in[k] = dc_keep[k];
+                        else dc_in[k] = (b < p.B) ? p.dc[idx] : 0.f;
+                        if (PREFETCH) load_pair(q, i, in[k]);
+                    }
+                // dh contribution from the step above: reduce-scattered partial products
+                float dh_in[PAIRS];
+                if (s == 0) {
+#pragma unroll
+                    for (int q = 0; q < UQ; ++q)
+#pragma unroll
+                        for (int i = 0; i < BT / 8; ++i) {
+                            const int b = b0 + nb + 8 * i;
+                            dh_in[q * (BT / 8) + i] = (dhn && b < p.B) ? load16<BF16>(dhn + (size_t)b * p.H + unit_of(q)) : 0.f;
+                        }
+                } else {
+                    const int buf = wi & 1, rb = wi & 1;
+                    ok = mbar_wait(&tfull[buf], (wi >> 1) & 1, abort_w);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    // phase A: lanes 0..15 of warp w hold units 16w+lane of the tile, all BT sequences
+#pragma unroll
+                    for (int c0 = 0; c0 < BT; c0 += 32) {
+                        uint32_t acc[32];
+                        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BT + c0, acc);
+                        tmem_ld_wait();
+                        if (lane < 16) {
+                            const int row = warp * 16 + lane;        // unit within the tile
+                            const uint32_t owner = row / UPO, lu = row % UPO;
+                            const uint32_t off = (uint32_t)(((rb * KS + kq) * UPO + lu) * (BT + 1) + c0) * 4u;
+                            if (KS > 1) {
+                                const uint32_t dst = map_to_rank(red_local + off, owner);
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) st_cluster_f32(dst + 4 * i, __uint_as_float(acc[i]));
+                            } else {
+                                float *dst = s_red + off / 4;
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) dst[i] = __uint_as_float(acc[i]);
+                            }
+                        }
+                    }
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&tempty[buf]);
+                    if (lane < 16) {
+                        const uint32_t owner = (warp * 16 + lane) / UPO;
+                        if (KS > 1) mbar_arrive_cluster(map_to_rank(rbar_local + rb * 8, owner));
+                        else mbar_arrive(&rbar[rb]);
+                    }
+                    ok = mbar_wait_cluster(&rbar[rb], (wi >> 1) & 1, abort_w);
+                    if (!ok) break;
+                    const float *red = s_red + (size_t)rb * KS * UPO * (BT + 1);
+#pragma unroll
+                    for (int q = 0; q < UQ; ++q)
+#pragma unroll
+                        for (int i = 0; i < BT / 8; ++i) {
+                            const int lu = q * 16 + u16, nn = nb + 8 * i;
+                            float acc = 0.f;
+#pragma unroll
+                            for (int src = 0; src < KS; ++src) acc += red[(src * UPO + lu) * (BT + 1) + nn];
+                            dh_in[q * (BT / 8) + i] = acc;
+                        }
+                    // every warp has read this item's partials before any warp sends the next item's
+                    named_barrier_sync(1, 128);
+                    ++wi;
+                }
+                // fused pointwise backward for the owned (unit, sequence) pairs
+#pragma unroll
+                for (int q = 0; q < UQ; ++q)
+#pragma unroll
+                    for (int i = 0; i < BT / 8; ++i) {
+                        const int k = q * (BT / 8) + i;
+                        const int b = b0 + nb + 8 * i, U = unit_of(q);
+                        if (b >= p.B) continue;
+                        const size_t idx = (size_t)b * p.H + U;
+                        if (t < 0) {
+                            if (p.dh0) p.dh0[idx] = dh_in[k];
+                            if (p.dc0) p.dc0[idx] = dc_in[k];
+                            continue;
+                        }
+                        PairIn v;
+                        if (PREFETCH) v = in[k];
+                        else load_pair(q, i, v);
+                        const float dh = v.dy + dh_in[k];
+                        const float tc = tanh_fast(v.ct);
+                        const float d_o = dh * tc;
+                        const float dcv = dc_in[k] + dh * v.go * (1.f - tc * tc);
+                        const float dai = dcv * v.gg * v.gi * (1.f - v.gi);
+                        const float daf = dcv * v.cp * v.gf * (1.f - v.gf);
+                        const float dag = dcv * v.gi * (1.f - v.gg * v.gg);
+                        const float dao = d_o * v.go * (1.f - v.go);
+                        const float dcp = dcv * v.gf;
+                        if (keep_dc) dc_keep[k] = dcp;
+                        else p.dc[idx] = dcp;
+                        uint16_t *drow = dg + ((size_t)t * p.B + b) * G + (size_t)(U >> 4) * 64 + (U & 15);
+                        drow[0] = to16<BF16>(dai);
+                        drow[16] = to16<BF16>(daf);
+                        drow[32] = to16<BF16>(dag);
+                        drow[48] = to16<BF16>(dao);
+                    }
+            }
+            if (!ok) break;
+            if (t >= 0) {
+                // publish dG_t: generic-proxy stores -> visible to the other CTAs' TMA loads
+                fence_proxy_async_all();
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) red_release_gpu_add(counter, 1u);
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (KS > 1) cluster_sync_all();  // nobody leaves while a peer may still write into its shared memory
+    if (warp == 5) tmem_dealloc(tmem_base, kTmemCols);
+    if (threadIdx.x == 0 && *abort_w) atomicCAS(p.err, 0u, 1u);
+}
+
+// ------------------------------------------------------------------ host side
+template <int BT, int KS, bool RES, bool BF16>
+static int launch_bwd(const CUtensorMap &tw, const CUtensorMap &tdg, const BwdParams &p, int grid, int smem_bytes,
+                      cudaStream_t s) {
+    auto kern = lstm_bwd_kernel<BT, KS, RES, BF16>;
+    static int configured = 0;
+    if (configured < smem_bytes) {
+        FLSTM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        configured = smem_bytes;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kBwdThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    attr[na].id = cudaLaunchAttributeCooperative;  // co-residency: CTAs wait on one another
+    attr[na].val.cooperative = 1;
+    ++na;
+    if (KS > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = KS;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tdg, p);
+    if (e != cudaSuccess && KS > 1) {
+        // some drivers reject cooperative + cluster: co-residency was checked with
+        // cudaOccupancyMaxActiveClusters at planning time, so launch with the cluster attribute only
+        cudaGetLastError();
+        cfg.attrs = attr + 1;
+        cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, kern, tw, tdg, p);
+    }
+    if (e != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "BPTT launch failed: %s", cudaGetErrorString(e));
+    return FLSTM_OK;
+}
+
+template <int BT, int KS, bool RES>
+static int max_clusters(int smem_bytes, int grid) {
+    auto kern = lstm_bwd_kernel<BT, KS, RES, false>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kBwdThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = KS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return n;
+}
+
+static int query_clusters(const BwdPlan &pl) {
+#define FLSTM_BWD_Q(BT_, KS_, RES_) \
+    if (pl.BT == BT_ && pl.KS == KS_ && pl.resident == RES_) return max_clusters<BT_, KS_, RES_>(pl.smem_bytes, pl.grid);
+    FLSTM_BWD_Q(32, 2, true) FLSTM_BWD_Q(32, 2, false) FLSTM_BWD_Q(32, 4, true) FLSTM_BWD_Q(32, 4, false)
+    FLSTM_BWD_Q(64, 2, true) FLSTM_BWD_Q(64, 2, false) FLSTM_BWD_Q(64, 4, true) FLSTM_BWD_Q(64, 4, false)
+#undef FLSTM_BWD_Q
+    return -1;
+}
+
+int plan_bwd(int B, int H, int sms, size_t smem_limit, BwdPlan *plan) {
+    if (H % 64 != 0 || H < 64) return set_error(FLSTM_ERR_UNSUPPORTED, "hidden size must be a multiple of 64");
+    const int jt = H / 64, kc_total = H / 16;
+    // split K = 4H so that a CTA's slice of W_hh (kc_total/KS chunks of 8 KB) can stay resident
+    int KS = 1;
+    while (KS < 4 && ((kc_total / KS) * kChunkBytesW > 128 * 1024 || jt * KS * 2 <= sms / 2) && (kc_total % (KS * 2) == 0) &&
+           jt * KS * 2 <= sms)
+        KS *= 2;
+    if (jt * KS > sms) return set_error(FLSTM_ERR_UNSUPPORTED, "hidden size too large for the persistent BPTT kernel");
+    const int BT = (B >= 128) ? 64 : 32;
+    const int tiles = (B + BT - 1) / BT;
+    int ngroups = sms / (jt * KS);
+    if (ngroups > tiles) ngroups = tiles;
+    if (ngroups < 1) ngroups = 1;
+    int nt = (tiles + ngroups - 1) / ngroups;
+    ngroups = (tiles + nt - 1) / nt;
+    bool resident = true;
+    int stages = 8;
+    BwdSmemLayout l = bwd_smem_layout(BT, H, KS, true, stages);
+    while ((size_t)l.total > smem_limit && stages > 4) l = bwd_smem_layout(BT, H, KS, true, --stages);
+    if ((size_t)l.total > smem_limit) {
+        resident = false;
+        stages = 12;
+        l = bwd_smem_layout(BT, H, KS, false, stages);
+        while ((size_t)l.total > smem_limit && stages > 2) l = bwd_smem_layout(BT, H, KS, false, --stages);
+        if ((size_t)l.total > smem_limit) return set_error(FLSTM_ERR_UNSUPPORTED, "BPTT kernel does not fit shared memory");
+    }
+    plan->BT = BT;
+    plan->KS = KS;
+    plan->jt = jt;
+    plan->ngroups = ngroups;
+    plan->nt = nt;
+    plan->stages = stages;
+    plan->resident = resident;
+    plan->smem_bytes = l.total;
+    plan->grid = jt * KS * ngroups;
+    if (KS > 1) {
+        // clusters must all be co-resident: shrink the number of batch groups until they are
+        for (;;) {
+            const int fit = query_clusters(*plan);
+            if (fit < 0 || fit * KS >= plan->grid || plan->ngroups == 1) break;
+            plan->ngroups -= 1;
+            plan->nt = (tiles + plan->ngroups - 1) / plan->ngroups;
+            plan->ngroups = (tiles + plan->nt - 1) / plan->nt;
+            plan->grid = jt * KS * plan->ngroups;
+        }
+    }
+    return FLSTM_OK;
+}
+
+int lstm_backward_persistent(int dtype, const BwdPlan &plan, const CUtensorMap &tm_w, const CUtensorMap &tm_dg,
+                             BwdParams p, cudaStream_t s) {
+    const bool bf16 = dtype == FLSTM_DTYPE_BF16;
+    p.jt = plan.jt;
+    p.nt = plan.nt;
+    p.stages = plan.stages;
+    p.idesc = umma_idesc_f16(64, plan.BT, bf16 ? 1 : 0, /*A MN-major*/ 1, /*B K-major*/ 0);
+#define FLSTM_BWD_CASE(BT_, KS_, RES_)                                                                         \
+    if (plan.BT == BT_ && plan.KS == KS_ && plan.resident == RES_)                                             \
+        return bf16 ? launch_bwd<BT_, KS_, RES_, true>(tm_w, tm_dg, p, plan.grid, plan.smem_bytes, s)          \
+                    : launch_bwd<BT_, KS_, RES_, false>(tm_w, tm_dg, p, plan.grid, plan.smem_bytes, s);
+    FLSTM_BWD_CASE(32, 1, true) FLSTM_BWD_CASE(32, 1, false) FLSTM_BWD_CASE(32, 2, true) FLSTM_BWD_CASE(32, 2, false)
+    FLSTM_BWD_CASE(32, 4, true) FLSTM_BWD_CASE(32, 4, false) FLSTM_BWD_CASE(64, 1, true) FLSTM_BWD_CASE(64, 1, false)
+    FLSTM_BWD_CASE(64, 2, true) FLSTM_BWD_CASE(64, 2, false) FLSTM_BWD_CASE(64, 4, true) FLSTM_BWD_CASE(64, 4, false)
+#undef FLSTM_BWD_CASE
+    return set_error(FLSTM_ERR_UNSUPPORTED, "no BPTT kernel for this plan");
+}
+
+}  // namespace tc
+}  // namespace flstm_b200

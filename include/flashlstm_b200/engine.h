@@ -125,13 +125,15 @@ unsigned long long flstm_engine_launch_count(const flstm_engine *engine);
 /* The dense-contraction building block of the path on the tcgen05 tensor cores, exported for
  * unit tests and profiling: D[M,N] = A B^T (+ bias[N]) with f16/bf16 operands (`dtype`) and fp32
  * accumulation; D has dtype `out_dtype` (the operand dtype or FLSTM_DTYPE_F32) and row pitch ldd.
- * mn_major == 0: A is (M,K) and B is (N,K), both row-major (what the input projection and the
- * input gradient use; replaces the GEMMs of src/lstm_internal.h:48-68).  mn_major == 1: A is
- * stored (K,M) and B is stored (K,N) (what the weight gradients dW = dG^T [X|H] use, reading both
- * operands as they lie in memory; replaces flashlstm_v2/src/lstm_backward.cu:1112-1141); fp32
- * output only.  Synchronous; returns FLSTM_ERR_TIMEOUT if a bounded device-side wait expired. */
+ *   layout 0: A is (M,K), B is (N,K), both row-major -- the input projection X W_ih^T
+ *             (replaces the GEMMs of src/lstm_internal.h:48-68);
+ *   layout 2: A is (M,K) row-major, B is stored (K,N) -- the input gradient dG W_ih, reading
+ *             W_ih as it lies in memory (replaces flashlstm_v2/src/lstm_backward.cu:1159-1171);
+ *   layout 1: A is stored (K,M), B is stored (K,N) -- the weight gradients dG^T [X|H], reduction
+ *             dimension outermost (replaces flashlstm_v2/src/lstm_backward.cu:1112-1141); fp32 out.
+ * Synchronous; returns FLSTM_ERR_TIMEOUT if a bounded device-side wait expired. */
 int flstm_tc_gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, const void *B,
-                  void *D, size_t ldd, const float *bias, int mn_major, void *stream);
+                  void *D, size_t ldd, const float *bias, int layout, void *stream);
 
 const char *flstm_last_error(void);
 const char *flstm_version(void);

@@ -62,6 +62,25 @@ def test_mnmajor_gemm(dtype, M, N, K):
     assert _rel(got, want) < 1e-5
 
 
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (512, 256, 1024), (200, 192, 136), (2048, 1024, 4096)])
+def test_mixed_major_gemm(dtype, M, N, K):
+    """A K-major, B stored (K,N): the input-gradient form dX = dG W_ih with W_ih read as stored."""
+    torch.manual_seed(M + 7 * N + K)
+    td = DT[dtype][1]
+    A = torch.randn(M, K, device="cuda").to(td)
+    Bt = torch.randn(K, N, device="cuda").to(td)
+    want = A.double() @ Bt.double()
+    lib = _lib.load()
+    for out, tol in (("f32", 1e-5), (dtype, 2e-3 if dtype == "f16" else 1e-2)):
+        out_code, out_td = (0, torch.float32) if out == "f32" else DT[out]
+        D = torch.full((M, N), float("nan"), dtype=out_td, device="cuda")
+        st = lib.flstm_tc_gemm(DT[dtype][0], out_code, M, N, K, A.data_ptr(), Bt.data_ptr(), D.data_ptr(), N, None, 2,
+                               torch.cuda.current_stream().cuda_stream)
+        assert st == 0, lib.flstm_last_error()
+        assert _rel(D, want) < tol
+
+
 def test_gemm_rejects_unaligned():
     lib = _lib.load()
     A = torch.zeros(64, 60, dtype=torch.float16, device="cuda")
