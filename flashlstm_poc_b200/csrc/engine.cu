@@ -70,6 +70,7 @@ Engine::~Engine() {
     dev_free(dc);
     dev_free(db_part);
     dev_free(sync_words);
+    dev_free(trace);
     if (comm) comm_destroy(comm);
     if (comm_stream) cudaStreamDestroy(comm_stream);
     if (comm_fork) cudaEventDestroy(comm_fork);
@@ -440,6 +441,33 @@ int flstm_engine_attach_comm(flstm_engine *engine, const void *id128, int rank, 
         cudaEventCreateWithFlags(&e.comm_fork, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&e.comm_join, cudaEventDisableTiming) != cudaSuccess)
         return set_error(FLSTM_ERR_CUDA, "could not create the communication stream");
+    return FLSTM_OK;
+}
+
+int flstm_engine_enable_trace(flstm_engine *engine, int steps) {
+    if (!engine || steps < 0) return set_error(FLSTM_ERR_INVALID, "bad argument");
+    Engine &e = engine->impl;
+    cudaDeviceSynchronize();
+    if (e.trace) cudaFree(e.trace);
+    e.trace = nullptr;
+    e.trace_steps = 0;
+    if (steps == 0) return FLSTM_OK;
+    void *raw = nullptr;
+    const size_t bytes = (size_t)2 * steps * 16 * sizeof(long long);
+    if (cudaMalloc(&raw, bytes) != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "trace allocation failed");
+    cudaMemset(raw, 0, bytes);
+    e.trace = static_cast<long long *>(raw);
+    e.trace_steps = steps;
+    return FLSTM_OK;
+}
+
+int flstm_engine_read_trace(flstm_engine *engine, long long *out_host, size_t count) {
+    if (!engine || !out_host) return set_error(FLSTM_ERR_INVALID, "null argument");
+    Engine &e = engine->impl;
+    const size_t have = (size_t)2 * e.trace_steps * 16;
+    if (!e.trace || count > have) return set_error(FLSTM_ERR_INVALID, "trace holds %zu values", have);
+    if (cudaMemcpy(out_host, e.trace, count * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess)
+        return set_error(FLSTM_ERR_CUDA, "trace copy failed");
     return FLSTM_OK;
 }
 

@@ -70,6 +70,8 @@ struct Engine {
     Comm *comm = nullptr;
     cudaStream_t comm_stream = nullptr;
     cudaEvent_t comm_fork = nullptr, comm_join = nullptr;
+    long long *trace = nullptr;  // device: [2 (fwd,bwd)][trace_steps][16] clock stamps of CTA 0
+    int trace_steps = 0;
     void *tc_state = nullptr;  // tensor-core path: cached tensor maps etc. (tc_engine.cu)
 
     ~Engine();

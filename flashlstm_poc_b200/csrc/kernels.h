@@ -43,5 +43,13 @@ int final_dh(int dtype, size_t B, size_t H, const void *dg0, const void *w_hh, f
 // out[n] = sum_r dg[r, n] over R rows (deterministic order)
 int column_sum(int dtype, const void *dg, size_t R, size_t N, float *out, cudaStream_t s);
 
+// Two-pass form for tall matrices: `scratch` holds kColumnSumSplits x N fp32 partial sums (every
+// entry is overwritten, nothing needs clearing).  unperm_h != 0 writes `out` in torch gate order
+// from tile-interleaved columns (H = unperm_h).
+constexpr int kColumnSumSplits = 32;
+int column_sum_scratch_floats(size_t N);
+int column_sum_two_pass(int dtype, const void *dg, size_t R, size_t N, float *scratch, float *out, int unperm_h,
+                        cudaStream_t s);
+
 }  // namespace simt
 }  // namespace flstm_b200

@@ -241,6 +241,44 @@ column_sum_kernel(const T *__restrict__ dg, size_t R, size_t N, float *__restric
     }
 }
 
+// Two-pass form for tall matrices: pass 1 sums a slice of the rows per block into
+// partial[split][col]; pass 2 adds the splits in a fixed order (deterministic).
+template <typename T>
+__global__ void __launch_bounds__(256)
+column_sum_partial_kernel(const T *__restrict__ dg, size_t R, size_t N, int splits, float *__restrict__ partial) {
+    __shared__ float part[8][33];
+    const int cl = threadIdx.x % 32, rl = threadIdx.x / 32;
+    const size_t col = (size_t)blockIdx.x * 32 + cl;
+    const size_t rows_per = (R + splits - 1) / splits;
+    const size_t r0 = (size_t)blockIdx.y * rows_per;
+    const size_t r1 = r0 + rows_per < R ? r0 + rows_per : R;
+    float s = 0.f;
+    if (col < N)
+        for (size_t r = r0 + rl; r < r1; r += 8) s += ld(dg + r * N + col);
+    part[rl][cl] = s;
+    __syncthreads();
+    if (rl == 0 && col < N) {
+        float t = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t += part[i][cl];
+        partial[(size_t)blockIdx.y * N + col] = t;
+    }
+}
+
+__global__ void column_sum_final_kernel(const float *__restrict__ partial, size_t N, int splits, float *__restrict__ out,
+                                        int unperm_h) {
+    const size_t col = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (col >= N) return;
+    float t = 0.f;
+    for (int s = 0; s < splits; ++s) t += partial[(size_t)s * N + col];
+    size_t o = col;
+    if (unperm_h) {  // tile-interleaved gate order -> torch order
+        const int r = (int)col, tile = r >> 6, g = (r >> 4) & 3, u = r & 15;
+        o = (size_t)g * unperm_h + tile * 16 + u;
+    }
+    out[o] = t;
+}
+
 inline int grid_1d(size_t n, int block = 256, int cap = 148 * 16) {
     size_t g = (n + block - 1) / block;
     if (g < 1) g = 1;
@@ -403,6 +441,23 @@ int column_sum(int dtype, const void *dg, size_t R, size_t N, float *out, cudaSt
         default: return set_error(FLSTM_ERR_INVALID, "column_sum: bad dtype %d", dtype);
     }
     return check_launch("column_sum");
+}
+
+int column_sum_scratch_floats(size_t N) { return (int)(kColumnSumSplits * N); }
+
+int column_sum_two_pass(int dtype, const void *dg, size_t R, size_t N, float *scratch, float *out, int unperm_h,
+                        cudaStream_t s) {
+    if (N == 0) return FLSTM_OK;
+    dim3 grid(ceil_div(N, 32), kColumnSumSplits);
+    switch (dtype) {
+        case FLSTM_DTYPE_F32: column_sum_partial_kernel<<<grid, 256, 0, s>>>((const float *)dg, R, N, kColumnSumSplits, scratch); break;
+        case FLSTM_DTYPE_F16: column_sum_partial_kernel<<<grid, 256, 0, s>>>((const __half *)dg, R, N, kColumnSumSplits, scratch); break;
+        case FLSTM_DTYPE_BF16: column_sum_partial_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16 *)dg, R, N, kColumnSumSplits, scratch); break;
+        default: return set_error(FLSTM_ERR_INVALID, "column_sum: bad dtype %d", dtype);
+    }
+    FLSTM_TRY(check_launch("column_sum_partial"));
+    column_sum_final_kernel<<<ceil_div(N, 256), 256, 0, s>>>(scratch, N, kColumnSumSplits, out, unperm_h);
+    return check_launch("column_sum_final");
 }
 
 }  // namespace simt

@@ -63,9 +63,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait.  `abort_word` lives in shared memory and is shared by every waiter of the CTA.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_word) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_test_wait(bar, parity)) return true;
     const unsigned long long t0 = global_timer_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
@@ -101,6 +114,12 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *m, int x, int y, int z, int w, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
         : "memory");
 }
 // shared -> global
@@ -191,6 +210,27 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n, int ab_forma
     return (1u << 4) | ((uint32_t)ab_format << 7) | ((uint32_t)ab_format << 10) | ((uint32_t)a_mn_major << 15) |
            ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
+// Same, with the accumulate flag known at compile time (no predicate set-up in the issue loop).
+template <bool ACC>
+__device__ __forceinline__ void umma_f16_imm(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+    if (ACC) {
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "setp.eq.u32 p, 1, 1;\n"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+            "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "setp.eq.u32 p, 1, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+            "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc)
+            : "memory");
+    }
+}
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                          uint32_t accumulate) {
@@ -216,6 +256,11 @@ int make_tensor_map_2d(CUtensorMap *out, const void *base, uint64_t rows, uint64
 int make_tensor_map_3d(CUtensorMap *out, const void *base, uint64_t d2, uint64_t rows, uint64_t cols,
                        uint64_t row_pitch_elems, uint64_t d2_pitch_elems, uint32_t box_rows, uint32_t box_cols,
                        bool swizzle128);
+// A (steps, rows, width) 16-bit tensor seen as (steps, width/64, rows, 64): one box of
+// 1 x chunks x box_rows x 64 lands in shared memory as `chunks` consecutive [box_rows x 128 B]
+// swizzled K-major UMMA operand tiles, so one copy brings several 64-wide K chunks of a tile.
+int make_tensor_map_chunked(CUtensorMap *out, const void *base, uint64_t steps, uint64_t rows, uint64_t width,
+                            uint32_t box_rows, uint32_t chunks);
 
 }  // namespace tc
 }  // namespace flstm_b200

@@ -135,7 +135,7 @@ int init(Engine &e) {
     FLSTM_CUDA_TRY(cudaMalloc(&raw, 1024 * sizeof(unsigned int)));
     e.sync_words = static_cast<unsigned int *>(raw);
     FLSTM_CUDA_TRY(cudaMemset(raw, 0, 1024 * sizeof(unsigned int)));
-    FLSTM_CUDA_TRY(cudaMalloc(&raw, 4 * e.cfg.hidden_size * sizeof(float)));
+    FLSTM_CUDA_TRY(cudaMalloc(&raw, (size_t)simt::column_sum_scratch_floats(4 * e.cfg.hidden_size) * sizeof(float)));
     e.db_part = static_cast<float *>(raw);
     FLSTM_CUDA_TRY(cudaMallocHost(&raw, sizeof(unsigned int)));
     st->err_host = static_cast<unsigned int *>(raw);
@@ -158,10 +158,10 @@ int on_capacity_change(Engine &e) {
         auto &l = e.layers[li];
         auto &t = st->layers[li];
         FLSTM_TRY(make_tensor_map_2d(&t.tm_w, l.w_hh, 4 * H, H, H, 64, 64, true));
-        FLSTM_TRY(make_tensor_map_3d(&t.tm_h, l.hs, cap + 1, B, H, H, B * H, st->fwd.BT, 64, true));
+        FLSTM_TRY(make_tensor_map_chunked(&t.tm_h, l.hs, cap + 1, B, H, st->fwd.BT, st->fwd.ch));
         FLSTM_TRY(make_tensor_map_3d(&t.tm_g, l.gates, cap, B, 4 * H, 4 * H, B * 4 * H, st->fwd.BT, 64, false));
         if (e.cfg.training && l.dg)
-            FLSTM_TRY(make_tensor_map_3d(&t.tm_dg, l.dg, cap, B, 4 * H, 4 * H, B * 4 * H, st->bwd.BT, 64, true));
+            FLSTM_TRY(make_tensor_map_chunked(&t.tm_dg, l.dg, cap, B, 4 * H, st->bwd.BT, st->bwd.ch));
     }
     return FLSTM_OK;
 }
@@ -208,12 +208,15 @@ int forward_layer(Engine &e, int li, size_t T, const void *x_l, void *y_out, cud
     p.cs = l.cs;
     p.hs = l.hs;
     p.y = y_out;
+    p.gates = l.gates;
     p.counters = e.sync_words + 1;
     p.err = err;
     p.T = (int)T;
     p.B = (int)B;
     p.H = (int)H;
     p.store_gates = e.cfg.training ? 1 : 0;
+    p.trace = (li == 0) ? e.trace : nullptr;
+    p.trace_steps = e.trace_steps;
     FLSTM_TRY(lstm_forward_persistent(e.cfg.dtype, st->fwd, t.tm_w, t.tm_h, t.tm_g, p, s));
     size_t m2 = e.timer.mark(s);
     e.timer.span(PH_PROJ, m0, m1);
@@ -244,6 +247,8 @@ int backward_layer(Engine &e, int li, size_t T, const void *x_l, const void *dy_
     p.dh0 = dh0_l;
     p.dc0 = dc0_l;
     p.dc = e.dc;
+    p.trace = (li == 0 && e.trace) ? e.trace + (size_t)e.trace_steps * 16 : nullptr;
+    p.trace_steps = e.trace_steps;
     p.counters = e.sync_words + 1;
     p.err = err;
     p.T = (int)T;
@@ -257,8 +262,7 @@ int backward_layer(Engine &e, int li, size_t T, const void *x_l, const void *dy_
                    l.dw_ih, l.in_size, nullptr, (int)H, err, st->sms, s));
     FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, H, T * B, l.dg, 4 * H, true, l.hs, H, true, l.dw_hh, H, nullptr,
                    (int)H, err, st->sms, s));
-    FLSTM_TRY(simt::column_sum(e.cfg.dtype, l.dg, T * B, 4 * H, e.db_part, s));
-    FLSTM_TRY(unpermute_vector(e.db_part, H, l.db, s));
+    FLSTM_TRY(simt::column_sum_two_pass(e.cfg.dtype, l.dg, T * B, 4 * H, e.db_part, l.db, (int)H, s));
     size_t m2 = e.timer.mark(s);
     if (dx_l) {
         // dX = dG W_ih: W_ih (rows tile-interleaved, like dG's columns) is read as stored

@@ -377,5 +377,20 @@ int make_tensor_map_3d(CUtensorMap *out, const void *base, uint64_t d2, uint64_t
     return FLSTM_OK;
 }
 
+int make_tensor_map_chunked(CUtensorMap *out, const void *base, uint64_t steps, uint64_t rows, uint64_t width,
+                            uint32_t box_rows, uint32_t chunks) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return set_error(FLSTM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[4] = {64, rows, width / 64, steps};
+    cuuint64_t strides[3] = {width * 2, 128, rows * width * 2};
+    cuuint32_t box[4] = {64, box_rows, chunks, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(FLSTM_ERR_CUDA, "cuTensorMapEncodeTiled (chunked) failed (%d)", (int)r);
+    return FLSTM_OK;
+}
+
 }  // namespace tc
 }  // namespace flstm_b200

@@ -29,6 +29,7 @@ struct FwdPlan {
     int ngroups;   // batch groups (each with its own step barrier)
     int nt;        // batch tiles per group
     int stages;    // TMA ring depth
+    int ch;        // 64-wide K chunks per ring stage (one TMA copy each)
     bool resident; // W_hh slice stays in shared memory for the whole sequence
     int smem_bytes;
     int grid;
@@ -38,19 +39,22 @@ struct FwdParams {
     float *cs;            // fp32 (T+1, B, H) cell states, slot 0 = c0
     void *hs;             // 16-bit (T+1, B, H) hidden states, slot 0 = h0
     void *y;              // optional 16-bit (T, B, H) copy of h_t for the caller
+    void *gates;          // 16-bit (T, B, 4H): holds P on entry, the activated gates on exit
     unsigned int *counters;  // one step counter per batch group, zeroed before the launch
     unsigned int *err;    // error word: non-zero after a bounded wait expired
     int T, B, H;
     int store_gates;      // write the activated gates back (the gate cache)
+    long long *trace;     // optional: CTA 0 stamps clock64() at 16 points of each of the first trace_steps steps
+    int trace_steps;
     // filled by the launcher from the plan
-    int rt, cta_rows, nt, stages;
+    int rt, cta_rows, nt, stages, ch;
     uint32_t idesc;
 };
 
 int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan);
-// tm_w: W_hh rows tile-interleaved (4H, H), box 64x64, 128B swizzle.  tm_h: hidden states as
-// (T+1, B, H), box 1 x BT x 64, 128B swizzle.  tm_g: projection / gate cache as (T, B, 4H), box
-// 1 x BT x 64, no swizzle (loaded and stored).
+// tm_w: W_hh rows tile-interleaved (4H, H), box 64x64, 128B swizzle.  tm_h: hidden states as a
+// chunked map (make_tensor_map_chunked) with box rows BT and plan.ch chunks.  tm_g: projection as
+// (T, B, 4H), box 1 x BT x 64, no swizzle.
 int lstm_forward_persistent(int dtype, const FwdPlan &plan, const CUtensorMap &tm_w, const CUtensorMap &tm_h,
                             const CUtensorMap &tm_g, FwdParams p, cudaStream_t s);
 
@@ -60,6 +64,7 @@ struct BwdPlan {
     int KS;        // cluster size: CTAs that split the K = 4H contraction of one 64-unit tile
     int jt;        // unit tiles = H / 64
     int ngroups, nt, stages;
+    int ch;        // 64-wide K chunks per ring stage (one TMA copy each)
     bool resident;
     int smem_bytes;
     int grid;
@@ -76,14 +81,17 @@ struct BwdParams {
     float *dc;            // fp32 (B, H) scratch for the cell-gradient carry (used when nt > 1)
     unsigned int *counters;
     unsigned int *err;
+    long long *trace;     // optional per-step clock64() stamps of CTA 0 (see FwdParams)
+    int trace_steps;
     int T, B, H;
-    int jt, nt, stages;
+    int jt, nt, stages, ch;
     uint32_t idesc;
 };
 
 int plan_bwd(int B, int H, int sms, size_t smem_limit, BwdPlan *plan);
 // tm_w: the same map as the forward's (W_hh rows tile-interleaved, 64x64 boxes): the BPTT reads the
-// slice as an MN-major operand.  tm_dg: dG as (T, B, 4H), box 1 x BT x 64, 128B swizzle.
+// slice as an MN-major operand.  tm_dg: dG as a chunked map (make_tensor_map_chunked) of width 4H
+// with box rows BT and plan.ch chunks.
 int lstm_backward_persistent(int dtype, const BwdPlan &plan, const CUtensorMap &tm_w, const CUtensorMap &tm_dg,
                              BwdParams p, cudaStream_t s);
 

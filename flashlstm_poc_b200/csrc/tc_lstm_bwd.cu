@@ -56,8 +56,8 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t ra
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
     return r;
 }
-__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr) : "memory");
@@ -138,13 +138,13 @@ struct BwdSmemLayout {
     int w_bytes, ring_stage_bytes, stages, red_bytes, total;
 };
 
-__host__ __device__ inline BwdSmemLayout bwd_smem_layout(int BT, int H, int KS, bool resident, int stages) {
+__host__ __device__ inline BwdSmemLayout bwd_smem_layout(int BT, int H, int KS, bool resident, int stages, int ch) {
     BwdSmemLayout l;
     const int kc_per = (H / 16) / KS;  // 64-wide K chunks this CTA contracts over
     l.w_bytes = resident ? kc_per * kChunkBytesW : 0;
-    l.ring_stage_bytes = BT * 128 + (resident ? 0 : kChunkBytesW);
+    l.ring_stage_bytes = ch * (BT * 128 + (resident ? 0 : kChunkBytesW));
     l.stages = stages;
-    l.red_bytes = 2 * KS * (64 / KS) * (BT + 1) * 4;  // 2 x [KS sources][64/KS units][BT+1]
+    l.red_bytes = 2 * KS * (64 / KS) * (BT + 4) * 4;  // 2 x [KS sources][64/KS units][BT+4]
     l.total = l.w_bytes + stages * l.ring_stage_bytes + l.red_bytes + 1024 + 512;
     return l;
 }
@@ -158,8 +158,9 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     constexpr bool PREFETCH = PAIRS <= 8;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const int KCper = (p.H / 16) / KS;
-    const BwdSmemLayout L = bwd_smem_layout(BT, p.H, KS, W_RESIDENT, p.stages);
+    constexpr int RS = BT + 4;  // row stride of the reduce buffer (floats), keeps float4 alignment
+    const int KCper = (p.H / 16) / KS, CH = p.ch, NLOAD = KCper / CH;
+    const BwdSmemLayout L = bwd_smem_layout(BT, p.H, KS, W_RESIDENT, p.stages, CH);
     uint8_t *s_w = smem;
     uint8_t *s_ring = s_w + L.w_bytes;
     float *s_red = reinterpret_cast<float *>(s_ring + L.stages * L.ring_stage_bytes);
@@ -206,6 +207,11 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
     const int nt_count = p.nt;
     const int c_first = kq * KCper;  // first K chunk (= forward row tile) of this CTA
+    const bool tracing = p.trace != nullptr && blockIdx.x == 0;
+#define FLSTM_STAMP(step, slot)                                                     \
+    do {                                                                            \
+        if (tracing && (step) < p.trace_steps) p.trace[(step) * 16 + (slot)] = clock64(); \
+    } while (0)
 
     if (warp == 4) {
         // ------------------------------------------------------------ producer
@@ -223,18 +229,24 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 ok = wait_counter(counter, (unsigned)(p.jt * KS * 4) * (unsigned)s, p.err, abort_w);
                 if (!ok) break;
                 fence_proxy_async_all();
+                FLSTM_STAMP(s, 0);
                 for (int n = 0; n < nt_count && ok; ++n) {
                     const int b0 = (ng * nt_count + n) * BT;
-                    for (int c = 0; c < KCper; ++c) {
+                    for (int ld = 0; ld < NLOAD; ++ld) {
                         ok = mbar_wait(&empty[stage], phase ^ 1, abort_w);
                         if (!ok) break;
                         uint8_t *sd = s_ring + stage * L.ring_stage_bytes;
                         mbar_expect_tx(&full[stage], (uint32_t)L.ring_stage_bytes);
-                        tma_load_3d(sd, &tm_dg, (c_first + c) * 64, b0, t_src, &full[stage]);
-                        if (!W_RESIDENT) tma_load_2d(sd + BT * 128, &tm_w, j * 64, (c_first + c) * 64, &full[stage]);
+                        // CH chunks of the dG tile with one copy: (x, row, chunk, step)
+                        tma_load_4d(sd, &tm_dg, 0, b0, c_first + ld * CH, t_src, &full[stage]);
+                        if (!W_RESIDENT)
+                            for (int c = 0; c < CH; ++c)
+                                tma_load_2d(sd + CH * BT * 128 + c * kChunkBytesW, &tm_w, j * 64,
+                                            (c_first + ld * CH + c) * 64, &full[stage]);
                         if (++stage == L.stages) { stage = 0; phase ^= 1; }
                     }
                 }
+                FLSTM_STAMP(s, 1);
             }
         }
     } else if (warp == 5) {
@@ -244,6 +256,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             if (W_RESIDENT) ok = mbar_wait(wbar, 0, abort_w);
             int stage = 0;
             uint32_t phase = 0;
+            const uint32_t s_w_u32 = smem_u32(s_w), idesc = p.idesc;
             const uint32_t items = (uint32_t)p.T * nt_count;
             for (uint32_t wi = 0; wi < items && ok; ++wi) {
                 const int buf = wi & 1;
@@ -251,21 +264,32 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 if (!ok) break;
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BT;
-                for (int c = 0; c < KCper; ++c) {
+                for (int ld = 0; ld < NLOAD; ++ld) {
                     ok = mbar_wait(&full[stage], phase, abort_w);
                     if (!ok) break;
+                    if (ld == 0) FLSTM_STAMP((int)(wi / nt_count) + 1, 2);
+                    if (ld == NLOAD - 1) FLSTM_STAMP((int)(wi / nt_count) + 1, 3);
                     tcgen05_fence_after();
-                    const uint32_t dg_base = smem_u32(s_ring + stage * L.ring_stage_bytes);
-                    const uint32_t w_base = W_RESIDENT ? smem_u32(s_w + c * kChunkBytesW) : dg_base + BT * 128;
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma_f16(d_tmem, umma_desc_mnmajor_sw128(w_base + k * 2048, 8192),
-                                 umma_desc_kmajor_sw128(dg_base + k * 32), p.idesc, (c | k) != 0);
+                    const uint32_t st_base = smem_u32(s_ring + stage * L.ring_stage_bytes);
+                    for (int c = 0; c < CH; ++c) {
+                        const int kc = ld * CH + c;
+                        const uint32_t dg_base = st_base + c * BT * 128;
+                        const uint32_t w_base = W_RESIDENT ? s_w_u32 + (uint32_t)kc * kChunkBytesW
+                                                           : st_base + CH * BT * 128 + c * kChunkBytesW;
+                        // K steps of 16: +2048 bytes on the MN-major W slice, +32 bytes on the K-major dG tile
+                        const uint64_t dw = umma_desc_mnmajor_sw128(w_base, 8192), dd = umma_desc_kmajor_sw128(dg_base);
+                        if (kc == 0) umma_f16_imm<false>(d_tmem, dw, dd, idesc);
+                        else umma_f16_imm<true>(d_tmem, dw, dd, idesc);
+                        umma_f16_imm<true>(d_tmem, dw + 128, dd + 2, idesc);
+                        umma_f16_imm<true>(d_tmem, dw + 256, dd + 4, idesc);
+                        umma_f16_imm<true>(d_tmem, dw + 384, dd + 6, idesc);
+                    }
                     umma_commit(&empty[stage]);
                     if (++stage == L.stages) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
                 umma_commit(&tfull[buf]);
+                FLSTM_STAMP((int)(wi / nt_count) + 1, 4);
             }
         }
     } else {
@@ -335,6 +359,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     const int buf = wi & 1, rb = wi & 1;
                     ok = mbar_wait(&tfull[buf], (wi >> 1) & 1, abort_w);
                     if (!ok) break;
+                    if (tid == 0) FLSTM_STAMP(s, 5);
                     tcgen05_fence_after();
                     // phase A: lanes 0..15 of warp w hold units 16w+lane of the tile, all BT sequences
 #pragma unroll
@@ -345,15 +370,18 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         if (lane < 16) {
                             const int row = warp * 16 + lane;        // unit within the tile
                             const uint32_t owner = row / UPO, lu = row % UPO;
-                            const uint32_t off = (uint32_t)(((rb * KS + kq) * UPO + lu) * (BT + 1) + c0) * 4u;
+                            const uint32_t off = (uint32_t)(((rb * KS + kq) * UPO + lu) * RS + c0) * 4u;
                             if (KS > 1) {
                                 const uint32_t dst = map_to_rank(red_local + off, owner);
 #pragma unroll
-                                for (int i = 0; i < 32; ++i) st_cluster_f32(dst + 4 * i, __uint_as_float(acc[i]));
+                                for (int i = 0; i < 8; ++i)
+                                    st_cluster_v4(dst + 16 * i, acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
                             } else {
-                                float *dst = s_red + off / 4;
+                                float4 *dst = reinterpret_cast<float4 *>(s_red + off / 4);
 #pragma unroll
-                                for (int i = 0; i < 32; ++i) dst[i] = __uint_as_float(acc[i]);
+                                for (int i = 0; i < 8; ++i)
+                                    dst[i] = make_float4(__uint_as_float(acc[4 * i]), __uint_as_float(acc[4 * i + 1]),
+                                                         __uint_as_float(acc[4 * i + 2]), __uint_as_float(acc[4 * i + 3]));
                             }
                         }
                     }
@@ -365,9 +393,11 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         if (KS > 1) mbar_arrive_cluster(map_to_rank(rbar_local + rb * 8, owner));
                         else mbar_arrive(&rbar[rb]);
                     }
+                    if (tid == 0) FLSTM_STAMP(s, 9);
                     ok = mbar_wait_cluster(&rbar[rb], (wi >> 1) & 1, abort_w);
                     if (!ok) break;
-                    const float *red = s_red + (size_t)rb * KS * UPO * (BT + 1);
+                    if (tid == 0) FLSTM_STAMP(s, 10);
+                    const float *red = s_red + (size_t)rb * KS * UPO * RS;
 #pragma unroll
                     for (int q = 0; q < UQ; ++q)
 #pragma unroll
@@ -375,11 +405,12 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                             const int lu = q * 16 + u16, nn = nb + 8 * i;
                             float acc = 0.f;
 #pragma unroll
-                            for (int src = 0; src < KS; ++src) acc += red[(src * UPO + lu) * (BT + 1) + nn];
+                            for (int src = 0; src < KS; ++src) acc += red[(src * UPO + lu) * RS + nn];
                             dh_in[q * (BT / 8) + i] = acc;
                         }
                     // every warp has read this item's partials before any warp sends the next item's
                     named_barrier_sync(1, 128);
+                    if (tid == 0) FLSTM_STAMP(s, 6);
                     ++wi;
                 }
                 // fused pointwise backward for the owned (unit, sequence) pairs
@@ -419,11 +450,12 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             }
             if (!ok) break;
             if (t >= 0) {
+                if (tid == 0) FLSTM_STAMP(s, 7);
                 // publish dG_t: generic-proxy stores -> visible to the other CTAs' TMA loads
                 fence_proxy_async_all();
-                __threadfence();
                 __syncwarp();
                 if (lane == 0) red_release_gpu_add(counter, 1u);
+                if (tid == 0) FLSTM_STAMP(s, 8);
             }
         }
     }
@@ -524,17 +556,26 @@ int plan_bwd(int B, int H, int sms, size_t smem_limit, BwdPlan *plan) {
     if (ngroups < 1) ngroups = 1;
     int nt = (tiles + ngroups - 1) / ngroups;
     ngroups = (tiles + nt - 1) / nt;
+    const int kc_per = kc_total / KS;
+    int ch = 4;
+    while (kc_per % ch) --ch;
     bool resident = true;
-    int stages = 8;
-    BwdSmemLayout l = bwd_smem_layout(BT, H, KS, true, stages);
-    while ((size_t)l.total > smem_limit && stages > 4) l = bwd_smem_layout(BT, H, KS, true, --stages);
-    if ((size_t)l.total > smem_limit) {
+    int stages = kc_per / ch;
+    BwdSmemLayout l = bwd_smem_layout(BT, H, KS, true, stages, ch);
+    while ((size_t)l.total > smem_limit && stages > 2) l = bwd_smem_layout(BT, H, KS, true, --stages, ch);
+    if ((size_t)l.total > smem_limit || (stages < 2 && kc_per / ch >= 2)) {
         resident = false;
-        stages = 12;
-        l = bwd_smem_layout(BT, H, KS, false, stages);
-        while ((size_t)l.total > smem_limit && stages > 2) l = bwd_smem_layout(BT, H, KS, false, --stages);
+        stages = kc_per / ch < 4 ? kc_per / ch : 4;
+        l = bwd_smem_layout(BT, H, KS, false, stages, ch);
+        while ((size_t)l.total > smem_limit && stages > 1) l = bwd_smem_layout(BT, H, KS, false, --stages, ch);
+        while ((size_t)l.total > smem_limit && ch > 1) {
+            --ch;
+            while (kc_per % ch) --ch;
+            l = bwd_smem_layout(BT, H, KS, false, stages, ch);
+        }
         if ((size_t)l.total > smem_limit) return set_error(FLSTM_ERR_UNSUPPORTED, "BPTT kernel does not fit shared memory");
     }
+    plan->ch = ch;
     plan->BT = BT;
     plan->KS = KS;
     plan->jt = jt;
@@ -564,6 +605,7 @@ int lstm_backward_persistent(int dtype, const BwdPlan &plan, const CUtensorMap &
     p.jt = plan.jt;
     p.nt = plan.nt;
     p.stages = plan.stages;
+    p.ch = plan.ch;
     p.idesc = umma_idesc_f16(64, plan.BT, bf16 ? 1 : 0, /*A MN-major*/ 1, /*B K-major*/ 0);
 #define FLSTM_BWD_CASE(BT_, KS_, RES_)                                                                         \
     if (plan.BT == BT_ && plan.KS == KS_ && plan.resident == RES_)                                             \

@@ -9,10 +9,10 @@
 //   producer warp : TMA-loads the P_t tile (input projection + bias, 16-bit), waits on the grid
 //                   barrier for h_{t-1}, then streams h_{t-1} (BT x 64 chunks) through the ring
 //   MMA warp      : tcgen05.mma M=64 (gate rows) x N=BT (batch) x K=16, accumulating over K = H into TMEM
-//   4 epilogue warps: tcgen05.ld -> + P_t -> sigmoid/tanh -> exchange through shared memory so that
-//                   one thread sees i,f,g,o of its (unit, sequence) pair -> c_t (fp32), h_t (16-bit);
-//                   the activated gates overwrite the P_t tile in shared memory and go back to the
-//                   same place in global memory with one TMA store: that is the FP16/BF16 gate cache
+//   4 epilogue warps: tcgen05.ld -> exchange through shared memory so that one thread sees all four
+//                   gate sums of its (unit, sequence) pair -> + P_t -> sigmoid/tanh -> c_t (fp32),
+//                   h_t (16-bit).  h_t is stored and published first; the cell state and the activated
+//                   gates (the FP16/BF16 gate cache, written over P_t in global memory) follow
 // Steps are separated by a per-batch-group barrier in global memory (release add / acquire poll).
 // Every wait is bounded; a timeout raises the error word and every CTA drains and returns.
 //
@@ -90,14 +90,15 @@ struct FwdSmemLayout {
     int w_bytes, ring_stage_bytes, stages, p_bytes, ex_bytes, total;
 };
 
-__host__ __device__ inline FwdSmemLayout fwd_smem_layout(int BT, int H, int rt, bool resident, int stages) {
+// One ring stage holds `ch` consecutive 64-wide K chunks of an h tile (and of W when streamed).
+__host__ __device__ inline FwdSmemLayout fwd_smem_layout(int BT, int H, int rt, bool resident, int stages, int ch) {
     FwdSmemLayout l;
     const int kc = H / 64;
     l.w_bytes = resident ? rt * kc * kChunkBytesW : 0;
-    l.ring_stage_bytes = BT * 128 + (resident ? 0 : kChunkBytesW);
+    l.ring_stage_bytes = ch * (BT * 128 + (resident ? 0 : kChunkBytesW));
     l.stages = stages;
     l.p_bytes = 2 * BT * 128;
-    l.ex_bytes = 2 * 64 * (BT + 1) * 4;
+    l.ex_bytes = 2 * 64 * (BT + 4) * 4;
     l.total = l.w_bytes + stages * l.ring_stage_bytes + l.p_bytes + l.ex_bytes + 1024 /*align*/ + 512 /*barriers*/;
     return l;
 }
@@ -108,12 +109,13 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 const __grid_constant__ CUtensorMap tm_g, FwdParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const int KC = p.H / 64;
-    const FwdSmemLayout L = fwd_smem_layout(BT, p.H, p.rt, W_RESIDENT, p.stages);
+    constexpr int EXS = BT + 4;  // row stride of the exchange buffer (floats), keeps float4 alignment
+    const int KC = p.H / 64, CH = p.ch, NLOAD = KC / CH;
+    const FwdSmemLayout L = fwd_smem_layout(BT, p.H, p.rt, W_RESIDENT, p.stages, CH);
     uint8_t *s_w = smem;                                   // resident W slice: rt*KC chunks of 8 KB
-    uint8_t *s_ring = s_w + L.w_bytes;                     // stages x [h chunk | (W chunk)]
-    uint8_t *s_p = s_ring + L.stages * L.ring_stage_bytes;  // 2 P/gate tiles, BT rows x 128 B, not swizzled
-    float *s_ex = reinterpret_cast<float *>(s_p + L.p_bytes);  // 2 x [64][BT+1] activated gates (fp32)
+    uint8_t *s_ring = s_w + L.w_bytes;                     // stages x [CH h chunks | (CH W chunks)]
+    uint8_t *s_p = s_ring + L.stages * L.ring_stage_bytes;  // 2 P tiles, BT rows x 128 B, not swizzled
+    float *s_ex = reinterpret_cast<float *>(s_p + L.p_bytes);  // 2 x [64][EXS] gate pre-activations (fp32)
     uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(s_ex) + L.ex_bytes);
     uint64_t *full = bars, *empty = bars + L.stages;
     uint64_t *tfull = empty + L.stages, *tempty = tfull + 2;
@@ -137,7 +139,7 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             mbar_init(&tfull[i], 1);
             mbar_init(&tempty[i], 4);
             mbar_init(&pfull[i], 1);
-            mbar_init(&pempty[i], 1);
+            mbar_init(&pempty[i], 4);
         }
         mbar_init(wbar, 1);
         *abort_w = 0;
@@ -157,6 +159,11 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
 
     const int nt_count = p.nt;  // batch tiles per group
     const int items_per_step = p.rt * nt_count;
+    const bool tracing = p.trace != nullptr && blockIdx.x == 0;
+#define FLSTM_STAMP(step, slot)                                                     \
+    do {                                                                            \
+        if (tracing && (step) < p.trace_steps) p.trace[(step) * 16 + (slot)] = clock64(); \
+    } while (0)
 
     if (warp == 4) {
         // ------------------------------------------------------------ producer
@@ -188,16 +195,22 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                             if (!ok) break;
                             fence_proxy_async_all();
                         }
+                        if (first) FLSTM_STAMP(t, 0);
                         first = false;
-                        for (int kc = 0; kc < KC; ++kc) {
+                        for (int ld = 0; ld < NLOAD; ++ld) {
                             ok = mbar_wait(&empty[stage], phase ^ 1, abort_w);
                             if (!ok) break;
                             uint8_t *sh = s_ring + stage * L.ring_stage_bytes;
                             mbar_expect_tx(&full[stage], (uint32_t)L.ring_stage_bytes);
-                            tma_load_3d(sh, &tm_h, kc * 64, b0, t, &full[stage]);
-                            if (!W_RESIDENT) tma_load_2d(sh + BT * 128, &tm_w, kc * 64, j * 64, &full[stage]);
+                            // CH chunks of the h tile with one copy: (x, row, chunk, step)
+                            tma_load_4d(sh, &tm_h, 0, b0, ld * CH, t, &full[stage]);
+                            if (!W_RESIDENT)
+                                for (int c = 0; c < CH; ++c)
+                                    tma_load_2d(sh + CH * BT * 128 + c * kChunkBytesW, &tm_w, (ld * CH + c) * 64, j * 64,
+                                                &full[stage]);
                             if (++stage == L.stages) { stage = 0; phase ^= 1; }
                         }
+                        FLSTM_STAMP(t, 1);
                     }
                 }
             }
@@ -209,6 +222,7 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             if (W_RESIDENT) ok = mbar_wait(wbar, 0, abort_w);
             int stage = 0;
             uint32_t phase = 0, wi = 0;
+            const uint32_t s_w_u32 = smem_u32(s_w), idesc = p.idesc;
             const uint32_t total_items = (uint32_t)p.T * items_per_step;
             for (uint32_t it = 0; it < total_items && ok; ++it, ++wi) {
                 const int r = (it % items_per_step) / nt_count;
@@ -217,21 +231,33 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 if (!ok) break;
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BT;
-                for (int kc = 0; kc < KC; ++kc) {
+                for (int ld = 0; ld < NLOAD; ++ld) {
                     ok = mbar_wait(&full[stage], phase, abort_w);
                     if (!ok) break;
+                    if (ld == 0) FLSTM_STAMP((int)(it / items_per_step), 2);
+                    if (ld == NLOAD - 1) FLSTM_STAMP((int)(it / items_per_step), 3);
                     tcgen05_fence_after();
-                    const uint32_t h_base = smem_u32(s_ring + stage * L.ring_stage_bytes);
-                    const uint32_t w_base = W_RESIDENT ? smem_u32(s_w + (r * KC + kc) * kChunkBytesW) : h_base + BT * 128;
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma_f16(d_tmem, umma_desc_kmajor_sw128(w_base + k * 32), umma_desc_kmajor_sw128(h_base + k * 32),
-                                 p.idesc, (kc | k) != 0);
+                    const uint32_t st_base = smem_u32(s_ring + stage * L.ring_stage_bytes);
+                    for (int c = 0; c < CH; ++c) {
+                        const int kc = ld * CH + c;
+                        const uint32_t h_base = st_base + c * BT * 128;
+                        const uint32_t w_base = W_RESIDENT ? s_w_u32 + (uint32_t)(r * KC + kc) * kChunkBytesW
+                                                           : st_base + CH * BT * 128 + c * kChunkBytesW;
+                        // one descriptor per chunk; the three further K steps of 16 elements advance the
+                        // start-address field by 32 bytes (2 in descriptor units)
+                        const uint64_t dw = umma_desc_kmajor_sw128(w_base), dh = umma_desc_kmajor_sw128(h_base);
+                        if (kc == 0) umma_f16_imm<false>(d_tmem, dw, dh, idesc);
+                        else umma_f16_imm<true>(d_tmem, dw, dh, idesc);
+                        umma_f16_imm<true>(d_tmem, dw + 2, dh + 2, idesc);
+                        umma_f16_imm<true>(d_tmem, dw + 4, dh + 4, idesc);
+                        umma_f16_imm<true>(d_tmem, dw + 6, dh + 6, idesc);
+                    }
                     umma_commit(&empty[stage]);
                     if (++stage == L.stages) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
                 umma_commit(&tfull[buf]);
+                FLSTM_STAMP((int)(it / items_per_step), 4);
             }
         }
     } else {
@@ -242,8 +268,10 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         float c_keep[PAIRS];
         const bool keep_c = items_per_step == 1;
         const size_t slab = (size_t)p.B * p.H;
+        const size_t G = (size_t)4 * p.H;
         uint16_t *hs = static_cast<uint16_t *>(p.hs);
         uint16_t *y = static_cast<uint16_t *>(p.y);
+        uint16_t *gates = static_cast<uint16_t *>(p.gates);
         uint32_t wi = 0;
         bool ok = true;
         for (int t = 0; t < p.T && ok; ++t) {
@@ -252,11 +280,7 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 for (int n = 0; n < nt_count && ok; ++n, ++wi) {
                     const int b0 = (ng * nt_count + n) * BT;
                     const int buf = wi & 1, pb = wi & 1;
-                    // the previous item's gate-cache store must have read its tile before the tile is reused
-                    if (tid == 0 && wi > 0) {
-                        if (p.store_gates) tma_store_wait_read<0>();
-                        mbar_arrive(&pempty[(wi - 1) & 1]);
-                    }
+                    const bool last_item = (r == p.rt - 1) && (n == nt_count - 1);
                     // cell state entering this step (own writes of the previous step, or registers)
                     float c_prev[PAIRS];
 #pragma unroll
@@ -267,65 +291,81 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     }
                     ok = mbar_wait(&tfull[buf], (wi >> 1) & 1, abort_w);
                     if (!ok) break;
+                    if (tid == 0) FLSTM_STAMP(t, 5);
                     tcgen05_fence_after();
-                    ok = mbar_wait(&pfull[pb], (wi >> 1) & 1, abort_w);
-                    if (!ok) break;
-                    uint16_t *ptile = reinterpret_cast<uint16_t *>(s_p + pb * BT * 128);
-                    float *ex = s_ex + (wi & 1) * 64 * (BT + 1);
-                    // phase A: lanes 0..15 of warp g hold gate g of units 0..15 for all BT sequences
+                    float *ex = s_ex + (wi & 1) * 64 * EXS;
+                    // phase A: lanes 0..15 of warp g hold the recurrent sums of gate g, units 0..15, all
+                    // BT sequences; they go to shared memory as they are
 #pragma unroll
                     for (int c0 = 0; c0 < BT; c0 += 32) {
                         uint32_t acc[32];
                         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BT + c0, acc);
                         tmem_ld_wait();
                         if (lane < 16) {
-                            const int col = warp * 16 + lane;
+                            float4 *dst = reinterpret_cast<float4 *>(ex + (warp * 16 + lane) * EXS + c0);
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                const int nn = c0 + i;
-                                const float pre = __uint_as_float(acc[i]) + load16<BF16>(ptile + nn * 64 + col);
-                                const float a = (warp == 2) ? tanh_fast(pre) : sigmoid_fast(pre);
-                                ptile[nn * 64 + col] = to16<BF16>(a);
-                                ex[col * (BT + 1) + nn] = a;
-                            }
+                            for (int i = 0; i < 8; ++i)
+                                dst[i] = make_float4(__uint_as_float(acc[4 * i]), __uint_as_float(acc[4 * i + 1]),
+                                                     __uint_as_float(acc[4 * i + 2]), __uint_as_float(acc[4 * i + 3]));
                         }
                     }
                     tcgen05_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&tempty[buf]);
-                    fence_proxy_async_smem();  // tile writes -> visible to the TMA store
+                    ok = mbar_wait(&pfull[pb], (wi >> 1) & 1, abort_w);
+                    if (!ok) break;
                     named_barrier_sync(1, 128);
-                    if (tid == 0 && p.store_gates) {
-                        tma_store_3d(&tm_g, ptile, j * 64, b0, t);
-                        tma_store_commit();
-                    }
-                    // phase B: one thread per (unit, sequence) pair
+                    if (tid == 0) FLSTM_STAMP(t, 6);
+                    // phase B: one thread per (unit, sequence) pair does the whole pointwise update
+                    const uint16_t *ptile = reinterpret_cast<const uint16_t *>(s_p + pb * BT * 128);
+                    float act[PAIRS][4];
+                    uint16_t h16[PAIRS];
 #pragma unroll
                     for (int i = 0; i < PAIRS; ++i) {
-                        const int nn = nb + 8 * i, b = b0 + nn;
-                        const float gi = ex[(0 * 16 + u) * (BT + 1) + nn], gf = ex[(1 * 16 + u) * (BT + 1) + nn];
-                        const float gg = ex[(2 * 16 + u) * (BT + 1) + nn], go = ex[(3 * 16 + u) * (BT + 1) + nn];
+                        const int nn = nb + 8 * i;
+                        const float ai = ex[(0 * 16 + u) * EXS + nn] + load16<BF16>(ptile + nn * 64 + 0 * 16 + u);
+                        const float af = ex[(1 * 16 + u) * EXS + nn] + load16<BF16>(ptile + nn * 64 + 1 * 16 + u);
+                        const float ag = ex[(2 * 16 + u) * EXS + nn] + load16<BF16>(ptile + nn * 64 + 2 * 16 + u);
+                        const float ao = ex[(3 * 16 + u) * EXS + nn] + load16<BF16>(ptile + nn * 64 + 3 * 16 + u);
+                        const float gi = sigmoid_fast(ai), gf = sigmoid_fast(af), gg = tanh_fast(ag), go = sigmoid_fast(ao);
                         const float c = fmaf(gf, c_prev[i], gi * gg);
                         const float h = go * tanh_fast(c);
                         c_keep[i] = c;
-                        if (b < p.B) {
-                            const size_t idx = (size_t)b * p.H + j * 16 + u;
-                            p.cs[(size_t)(t + 1) * slab + idx] = c;
-                            const uint16_t h16 = to16<BF16>(h);
-                            hs[(size_t)(t + 1) * slab + idx] = h16;
-                            if (y) y[(size_t)t * slab + idx] = h16;
+                        act[i][0] = gi; act[i][1] = gf; act[i][2] = gg; act[i][3] = go;
+                        h16[i] = to16<BF16>(h);
+                        // h_t first: it is what the other CTAs wait for
+                        if (b0 + nn < p.B) hs[(size_t)(t + 1) * slab + (size_t)(b0 + nn) * p.H + j * 16 + u] = h16[i];
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&pempty[pb]);  // this warp is done with the P tile
+                    if (last_item) {
+                        if (tid == 0) FLSTM_STAMP(t, 7);
+                        // publish h_t: generic-proxy stores -> visible to other CTAs' TMA loads; the
+                        // release is cumulative over the warp's stores ordered before it by __syncwarp
+                        fence_proxy_async_all();
+                        __syncwarp();
+                        if (lane == 0) red_release_gpu_add(counter, 1u);
+                        if (tid == 0) FLSTM_STAMP(t, 8);
+                    }
+                    // everything nobody waits for: cell state, gate cache, the caller's y
+#pragma unroll
+                    for (int i = 0; i < PAIRS; ++i) {
+                        const int b = b0 + nb + 8 * i;
+                        if (b >= p.B) continue;
+                        const size_t idx = (size_t)b * p.H + j * 16 + u;
+                        p.cs[(size_t)(t + 1) * slab + idx] = c_keep[i];
+                        if (y) y[(size_t)t * slab + idx] = h16[i];
+                        if (p.store_gates) {
+                            uint16_t *grow = gates + ((size_t)t * p.B + b) * G + (size_t)j * 64 + u;
+                            grow[0] = to16<BF16>(act[i][0]);
+                            grow[16] = to16<BF16>(act[i][1]);
+                            grow[32] = to16<BF16>(act[i][2]);
+                            grow[48] = to16<BF16>(act[i][3]);
                         }
                     }
                 }
             }
-            if (!ok) break;
-            // publish h_t: generic-proxy stores -> visible to other CTAs' TMA loads
-            fence_proxy_async_all();
-            __threadfence();
-            __syncwarp();
-            if (lane == 0) red_release_gpu_add(counter, 1u);
         }
-        if (tid == 0) tma_store_wait_all<0>();
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -371,18 +411,28 @@ int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan) {
     if (ngroups < 1) ngroups = 1;
     const int nt = (tiles + ngroups - 1) / ngroups;
     ngroups = (tiles + nt - 1) / nt;
-    // resident weights if the slice plus a useful ring fits
+    // One TMA copy brings `ch` 64-wide K chunks of an h tile; the ring holds a whole tile when it can.
+    // The W_hh slice stays resident if it fits next to a ring of at least two stages.
+    const int kc = H / 64;
+    int ch = 4;
+    while (kc % ch) --ch;
     bool resident = true;
-    int stages = 8;
-    FwdSmemLayout l = fwd_smem_layout(BT, H, rt, true, stages);
-    while ((size_t)l.total > smem_limit && stages > 4) l = fwd_smem_layout(BT, H, rt, true, --stages);
-    if ((size_t)l.total > smem_limit) {
+    int stages = kc / ch;
+    FwdSmemLayout l = fwd_smem_layout(BT, H, rt, true, stages, ch);
+    while ((size_t)l.total > smem_limit && stages > 2) l = fwd_smem_layout(BT, H, rt, true, --stages, ch);
+    if ((size_t)l.total > smem_limit || (stages < 2 && kc / ch >= 2)) {
         resident = false;
-        stages = 12;
-        l = fwd_smem_layout(BT, H, rt, false, stages);
-        while ((size_t)l.total > smem_limit && stages > 2) l = fwd_smem_layout(BT, H, rt, false, --stages);
+        stages = kc / ch < 4 ? kc / ch : 4;
+        l = fwd_smem_layout(BT, H, rt, false, stages, ch);
+        while ((size_t)l.total > smem_limit && stages > 1) l = fwd_smem_layout(BT, H, rt, false, --stages, ch);
+        while ((size_t)l.total > smem_limit && ch > 1) {
+            --ch;
+            while (kc % ch) --ch;
+            l = fwd_smem_layout(BT, H, rt, false, stages, ch);
+        }
         if ((size_t)l.total > smem_limit) return set_error(FLSTM_ERR_UNSUPPORTED, "recurrent kernel does not fit shared memory");
     }
+    plan->ch = ch;
     plan->BT = BT;
     plan->rt = rt;
     plan->cta_rows = cta_rows;
@@ -402,6 +452,7 @@ int lstm_forward_persistent(int dtype, const FwdPlan &plan, const CUtensorMap &t
     p.cta_rows = plan.cta_rows;
     p.nt = plan.nt;
     p.stages = plan.stages;
+    p.ch = plan.ch;
     p.idesc = umma_idesc_f16(64, plan.BT, bf16 ? 1 : 0, 0, 0);
 #define FLSTM_FWD_CASE(BT_, RES_)                                                                              \
     if (plan.BT == BT_ && plan.resident == RES_)                                                               \

@@ -119,6 +119,11 @@ int flstm_engine_attach_comm(flstm_engine *engine, const void *id128, int rank, 
  * out[0..5] = projection, recurrent forward, BPTT, weight-grad, input-grad, allreduce. */
 int flstm_engine_enable_timing(flstm_engine *engine, int enabled);
 int flstm_engine_phase_ms(flstm_engine *engine, float *out6);
+/* Per-time-step profiling of the persistent kernels (tensor-core backend, layer 0): CTA 0 stamps
+ * the SM clock at up to 16 points of each of the first `steps` time steps.  read_trace copies
+ * 2 x steps x 16 values (forward kernel first, then BPTT) to host memory.  steps = 0 turns it off. */
+int flstm_engine_enable_trace(flstm_engine *engine, int steps);
+int flstm_engine_read_trace(flstm_engine *engine, long long *out_host, size_t count);
 /* Number of kernels this library launched on behalf of `engine` since creation. */
 unsigned long long flstm_engine_launch_count(const flstm_engine *engine);
 
