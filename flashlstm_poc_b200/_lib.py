@@ -16,7 +16,7 @@ ENGINE_SYMBOLS = [
     "flstm_engine_backward", "flstm_engine_grad_ptrs", "flstm_engine_grad_buffer", "flstm_engine_cache_ptrs",
     "flstm_engine_set_cell_io_f32", "flstm_engine_backend", "flstm_comm_unique_id", "flstm_engine_attach_comm",
     "flstm_engine_enable_timing", "flstm_engine_phase_ms", "flstm_engine_launch_count", "flstm_tc_gemm",
-    "flstm_engine_enable_trace", "flstm_engine_read_trace",
+    "flstm_engine_enable_trace", "flstm_engine_read_trace", "flstm_bias_grad",
     "flstm_last_error",
     "flstm_version",
 ]
@@ -89,6 +89,7 @@ def load() -> ctypes.CDLL:
     lib.flstm_engine_launch_count.restype = ctypes.c_ulonglong
     lib.flstm_engine_enable_trace.argtypes = [vp, ci]
     lib.flstm_engine_read_trace.argtypes = [vp, vp, sz]
+    lib.flstm_bias_grad.argtypes = [ci, vp, sz, sz, ci, vp, vp]
     lib.flstm_tc_gemm.argtypes = [ci, ci, sz, sz, sz, vp, vp, vp, sz, vp, ci, vp]
     lib.flstm_last_error.restype = ctypes.c_char_p
     lib.flstm_version.restype = ctypes.c_char_p

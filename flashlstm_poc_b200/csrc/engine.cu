@@ -487,6 +487,24 @@ unsigned long long flstm_engine_launch_count(const flstm_engine *engine) {
     return engine ? engine->impl.launches : 0ull;
 }
 
+int flstm_bias_grad(int dtype, const void *dg, size_t rows, size_t cols, int interleaved_h, float *db, void *stream) {
+    using namespace flstm_b200;
+    if (!dg || !db) return set_error(FLSTM_ERR_INVALID, "null pointer argument");
+    if (dtype < FLSTM_DTYPE_F32 || dtype > FLSTM_DTYPE_BF16) return set_error(FLSTM_ERR_INVALID, "bad dtype %d", dtype);
+    if (interleaved_h < 0 || (interleaved_h && (size_t)interleaved_h * 4 != cols) || (interleaved_h % 16))
+        return set_error(FLSTM_ERR_INVALID, "interleaved_h must be 0 or cols/4 (a multiple of 16)");
+    if (rows == 0 || cols == 0) return FLSTM_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float *scratch = nullptr;
+    FLSTM_CUDA_TRY(cudaMalloc((void **)&scratch, (size_t)simt::column_sum_scratch_floats(cols) * sizeof(float)));
+    int st = simt::column_sum_two_pass(dtype, dg, rows, cols, scratch, db, interleaved_h, s);
+    cudaError_t e = cudaStreamSynchronize(s);
+    cudaFree(scratch);
+    if (st != FLSTM_OK) return st;
+    if (e != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "bias gradient failed: %s", cudaGetErrorString(e));
+    return FLSTM_OK;
+}
+
 const char *flstm_last_error(void) { return flstm_b200::last_error_slot().c_str(); }
 
 const char *flstm_version(void) { return "flashlstm-b200 0.1 (sm_100a)"; }

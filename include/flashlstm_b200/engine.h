@@ -140,6 +140,14 @@ unsigned long long flstm_engine_launch_count(const flstm_engine *engine);
 int flstm_tc_gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, const void *B,
                   void *D, size_t ldd, const float *bias, int layout, void *stream);
 
+/* The bias-gradient reduction of the backward pass as a stand-alone call: db[c] = sum over `rows`
+ * of dg[r][c] for a (rows, cols) matrix of dtype `dtype`, summed in a fixed order (two passes over
+ * kernel-internal partial sums, so results are run-to-run identical).  With interleaved_h = H
+ * (cols must be 4H) the columns are taken to be in the engine's tile-interleaved gate order and db
+ * is written in torch order.  Replaces the ones-vector GEMV of
+ * flashlstm_v2/src/lstm_backward.cu:1144-1156.  Allocates its scratch per call; synchronous. */
+int flstm_bias_grad(int dtype, const void *dg, size_t rows, size_t cols, int interleaved_h, float *db, void *stream);
+
 const char *flstm_last_error(void);
 const char *flstm_version(void);
 
