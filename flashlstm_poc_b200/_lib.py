@@ -17,6 +17,7 @@ ENGINE_SYMBOLS = [
     "flstm_engine_set_cell_io_f32", "flstm_engine_backend", "flstm_comm_unique_id", "flstm_engine_attach_comm",
     "flstm_engine_enable_timing", "flstm_engine_phase_ms", "flstm_engine_launch_count", "flstm_tc_gemm",
     "flstm_engine_enable_trace", "flstm_engine_read_trace", "flstm_bias_grad",
+    "flstm_bias_grad_static",
     "flstm_last_error",
     "flstm_version",
 ]
@@ -90,6 +91,7 @@ def load() -> ctypes.CDLL:
     lib.flstm_engine_enable_trace.argtypes = [vp, ci]
     lib.flstm_engine_read_trace.argtypes = [vp, vp, sz]
     lib.flstm_bias_grad.argtypes = [ci, vp, sz, sz, ci, vp, vp]
+    lib.flstm_bias_grad_static.argtypes = [ci, vp, sz, sz, ci, vp, vp]
     lib.flstm_tc_gemm.argtypes = [ci, ci, sz, sz, sz, vp, vp, vp, sz, vp, ci, vp]
     lib.flstm_last_error.restype = ctypes.c_char_p
     lib.flstm_version.restype = ctypes.c_char_p

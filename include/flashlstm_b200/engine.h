@@ -148,6 +148,23 @@ int flstm_tc_gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const 
  * flashlstm_v2/src/lstm_backward.cu:1144-1156.  Allocates its scratch per call; synchronous. */
 int flstm_bias_grad(int dtype, const void *dg, size_t rows, size_t cols, int interleaved_h, float *db, void *stream);
 
+/* flstm_bias_grad without any allocation.  This entry point has no counterpart in the reference.
+ * It is for callers that may not allocate device memory at call time: hosts that reserve all GPU
+ * memory up front and forbid cudaMalloc in their serving or real-time loop (an allocation can block
+ * or synchronise the device), code running where the CUDA allocator is off limits (during a stream
+ * capture, inside another framework's allocator hooks), and embedders that must account for every
+ * byte.  The partial sums live in a fixed 2 MiB array inside the library image, so:
+ *   - cols may be at most 16384 (4H for H = 4096); wider input is rejected with
+ *     FLSTM_ERR_UNSUPPORTED and a message naming the limit;
+ *   - every GPU that loads the library holds the array until the process exits;
+ *   - all calls share it: calls that may overlap on the GPU (different streams or threads) race and
+ *     must be serialised by the caller.  Nothing needs clearing between calls.
+ * The first call on each device looks up the array's device address (no allocation); make that
+ * first call before starting a stream capture.  Asynchronous on `stream`; calls no cudaMalloc,
+ * cudaFree or other allocating routine. */
+int flstm_bias_grad_static(int dtype, const void *dg, size_t rows, size_t cols, int interleaved_h, float *db,
+                           void *stream);
+
 const char *flstm_last_error(void);
 const char *flstm_version(void);
 
