@@ -451,8 +451,8 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             if (!ok) break;
             if (t >= 0) {
                 if (tid == 0) FLSTM_STAMP(s, 7);
-                // publish dG_t: generic-proxy stores -> visible to the other CTAs' TMA loads
-                fence_proxy_async_all();
+                // publish dG_t (release, cumulative over the warp's stores); the generic->async proxy fence
+                // is on the consumer side, after its acquire and before its TMA loads
                 __syncwarp();
                 if (lane == 0) red_release_gpu_add(counter, 1u);
                 if (tid == 0) FLSTM_STAMP(s, 8);

@@ -340,9 +340,9 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     if (lane == 0) mbar_arrive(&pempty[pb]);  // this warp is done with the P tile
                     if (last_item) {
                         if (tid == 0) FLSTM_STAMP(t, 7);
-                        // publish h_t: generic-proxy stores -> visible to other CTAs' TMA loads; the
-                        // release is cumulative over the warp's stores ordered before it by __syncwarp
-                        fence_proxy_async_all();
+                        // publish h_t: the release is cumulative over the warp's stores ordered before it
+                        // by __syncwarp.  The generic->async proxy fence sits on the consumer side, between
+                        // its acquire of the counter and its TMA loads.
                         __syncwarp();
                         if (lane == 0) red_release_gpu_add(counter, 1u);
                         if (tid == 0) FLSTM_STAMP(t, 8);

@@ -26,12 +26,12 @@ eng.forward(x,h0,c0); eng.backward(dy); torch.cuda.synchronize()
 buf = (ctypes.c_longlong * (2*N*16))()
 assert eng.lib.flstm_engine_read_trace(eng._h, buf, 2*N*16) == 0
 a = np.array(buf[:], dtype=np.int64).reshape(2, N, 16)
-names = {0:'barrier seen',1:'tma issued',2:'first chunk',3:'last chunk',4:'mma committed',5:'tfull seen',9:'partials sent',10:'reduce ready',6:'after exchange',7:'stores issued',8:'released'}
+names = {0:'barrier seen',1:'tma issued',2:'first chunk',3:'last chunk',4:'mma committed',5:'tfull seen',9:'partials sent / proxy fence done',10:'reduce ready',6:'after exchange',7:'stores issued',8:'released'}
 for d, nm in ((0,'FWD'),(1,'BWD')):
     t = a[d]
     print(nm, 'step period (clk) median:', np.median(np.diff(t[8:60,8])))
     base = t[10:60, 8][:-1]   # release of previous step
-    for k in (0,1,2,3,4,5,9,10,6,7,8):
+    for k in ((0,1,2,3,4,5,6,7,9,8) if d == 0 else (0,1,2,3,4,5,9,10,6,7,8)):
         v = t[11:60, k] - base
         if t[11:60,k].min() == 0: continue
         print(f'  {names[k]:>16}: median {np.median(v):8.0f} clk  min {v.min():8.0f} max {v.max():8.0f}')
