@@ -49,6 +49,7 @@ def parse_args():
     ap.add_argument("--backend", default="auto", choices=["auto", "simt", "tc"])
     ap.add_argument("--seq-len", type=int, default=0, help="override the workload's sequence length (profiling)")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's per-GPU batch (profiling)")
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying one captured CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -241,10 +242,29 @@ def main():
     dh0 = torch.empty(L, B, H, dtype=torch.float32, device=dev) if w.training else None
     dc0 = torch.empty(L, B, H, dtype=torch.float32, device=dev) if w.training else None
 
-    def step():
+    def eager_step():
         eng.forward_into(T, x, h0, c0, y, hn, cn)
         if w.training:
             eng.backward_into(T, dy, None, None, dx, dh0, dc0)
+
+    # the whole step (GEMMs, persistent kernels, allreduce) is captured once and replayed
+    graph, graph_note = None, "eager launches"
+    if world > 1:
+        # capturing the in-backward NCCL allreduce together with the cooperative kernels hung once at
+        # N=2; multi-GPU runs therefore launch eagerly (same kernels, same allreduce)
+        graph_note = "eager launches (graph capture is used at N=1 only)"
+    elif not args.no_graph:
+        try:
+            graph = eng.capture_step(x, h0, c0, y, hn, cn, dy, dx, dh0, dc0)
+            graph_note = "one captured CUDA graph per step"
+        except Exception as exc:  # capture is an optimisation; the eager path is the same kernels
+            graph_note = f"eager launches (graph capture failed: {type(exc).__name__})"
+            torch.cuda.synchronize()
+    step = graph.replay if graph is not None else eager_step
+    l0 = eng.launch_count
+    eager_step()
+    launches_per_step = eng.launch_count - l0
+    torch.cuda.synchronize()
 
     def barrier():
         if world > 1:
@@ -269,7 +289,7 @@ def main():
     ev1.record()
     barrier()
     total_ms = ev0.elapsed_time(ev1)
-    launches = eng.launch_count - launches0
+    launches = (eng.launch_count - launches0) if graph is None else launches_per_step * args.steps
     clocks = sampler.stop() if rank == 0 else None
     if world > 1:
         t = torch.tensor([total_ms], device=dev)
@@ -283,7 +303,7 @@ def main():
     phase_acc = {}
     reps = 3
     for _ in range(reps):
-        step()
+        eager_step()
         torch.cuda.synchronize()
         for k, v in eng.phase_ms().items():
             phase_acc[k] = phase_acc.get(k, 0.0) + v / reps
@@ -342,6 +362,7 @@ def main():
             "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
             "config": {"workload": w.name, "layers": L, "input_size": I, "hidden_size": H, "batch_per_gpu": B,
                        "global_batch": B * world, "seq_len": T, "parallelism": f"dp{world}",
+                       "launch": graph_note,
                        "l2": "working set (gate cache + dG = 512 MiB) exceeds the 126 MB L2"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline,
             "cpu_baseline": cpu_baseline, **extra,

@@ -121,6 +121,24 @@ class Engine:
         check(self.lib.flstm_engine_backward(self._h, T, dy.data_ptr(), _ptr(dhn), _ptr(dcn), _ptr(dx), _ptr(dh0),
                                              _ptr(dc0), self._stream()))
 
+    def capture_step(self, x, h0, c0, y, hn, cn, dy=None, dx=None, dh0=None, dc0=None) -> "torch.cuda.CUDAGraph":
+        """Capture one forward (+ backward when dy is given) over the given, caller-owned tensors into a
+        CUDA graph: the projection GEMM, the persistent recurrent kernels (cooperative launches), the
+        gradient GEMMs and, with a communicator attached, the per-layer allreduce all become graph nodes.
+        Replay with graph.replay(); the tensors keep their addresses, only their contents may change."""
+        T = x.shape[0]
+        # run once eagerly so lazy one-time set-up (function attributes, NCCL channels) is not captured
+        self.forward_into(T, x, h0, c0, y, hn, cn)
+        if dy is not None:
+            self.backward_into(T, dy, None, None, dx, dh0, dc0)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.forward_into(T, x, h0, c0, y, hn, cn)
+            if dy is not None:
+                self.backward_into(T, dy, None, None, dx, dh0, dc0)
+        return graph
+
     def _wrap(self, ptr: int, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         """A torch view over engine-owned device memory (valid while the engine lives)."""
         n = 1

@@ -73,6 +73,22 @@ def test_scaled_baseline_configs(name, scale):
     eng.close()
 
 
+@pytest.mark.parametrize("dtype,L,T,B,I,H,training", [
+    ("bf16", 2, 5, 32, 2048, 2048, True),    # config 3's width: W_hh slices do not fit shared memory -> streamed from L2
+    ("f16", 1, 4, 8, 4096, 4096, False),     # config 4: two row tiles per CTA, streamed weights, inference
+    ("f16", 1, 3, 1, 4096, 4096, False),     # config 4 at batch 1
+    ("bf16", 2, 4, 256, 256, 1024, True),    # several batch tiles per CTA (config 5's regime: B >> 64)
+    ("f16", 1, 6, 200, 192, 192, True),      # ragged batch tile, K chunks not a multiple of 4
+])
+def test_wide_and_large_batch_regimes(dtype, L, T, B, I, H, training):
+    w = Workload("t", dtype, L, I, H, B, T, seed=17, state_std=0.2, training=training)
+    inp = make_inputs(w)
+    got, eng = run_engine(w, inp, backend="tc")
+    ref = run_oracle(inp)
+    assert_parity(got, ref, dtype)
+    eng.close()
+
+
 def test_repeatable_and_cache_layout():
     """Two runs give bit-identical results (a race in a persistent kernel's barrier would not), and
     the gate cache read back in torch order matches the oracle's activations."""
@@ -121,4 +137,40 @@ def test_errors_are_reported():
         eng.forward(x.float())
     with pytest.raises(FlashLstmError):
         Engine("f32", 1, 2, 8, 8, 4, backend="tc", device=dev)  # tensor-core path is 16-bit only
+    eng.close()
+
+
+@pytest.mark.parametrize("dtype,L,H", [("f16", 1, 128), ("bf16", 2, 64), ("f32", 1, 32)])
+def test_whole_step_in_a_cuda_graph(dtype, L, H):
+    """Forward + backward captured once and replayed on new inputs gives what the eager calls give."""
+    from flashlstm_poc_b200.engine import TORCH_DTYPES, Engine
+
+    dev = torch.device("cuda", 0)
+    td = TORCH_DTYPES[dtype]
+    T, B, I = 9, 16, 64
+    w = Workload("g", dtype, L, I, H, B, T, seed=31, state_std=0.2)
+    inp = make_inputs(w)
+    eng = Engine(dtype, L, B, I, H, T, device=dev)
+    for l in range(L):
+        eng.set_weights(l, inp.w_ih[l].to(dev), inp.w_hh[l].to(dev), inp.b_ih[l].to(dev), inp.b_hh[l].to(dev))
+    x = torch.zeros(T, B, I, dtype=td, device=dev)
+    dy = torch.zeros(T, B, H, dtype=td, device=dev)
+    h0, c0 = inp.h0.to(dev, td), inp.c0.to(dev, td)
+    y = torch.empty(T, B, H, dtype=td, device=dev)
+    hn, cn = torch.empty(L, B, H, dtype=td, device=dev), torch.empty(L, B, H, dtype=td, device=dev)
+    dx = torch.empty(T, B, I, dtype=td, device=dev)
+    dh0, dc0 = torch.empty(L, B, H, device=dev), torch.empty(L, B, H, device=dev)
+    graph = eng.capture_step(x, h0, c0, y, hn, cn, dy, dx, dh0, dc0)
+    x.copy_(inp.x.to(dev, td))
+    dy.copy_(inp.dy.to(dev, td))
+    graph.replay()
+    torch.cuda.synchronize()
+    got = {"y": y.float().cpu().numpy(), "dx": dx.float().cpu().numpy(), "dh0": dh0.cpu().numpy(),
+           "dw_hh": [eng.grads(l)[1].cpu().numpy() for l in range(L)]}
+    ref = run_oracle(inp)
+    assert_parity(got, ref, dtype, keys=["y", "dx", "dh0", "dw_hh"])
+    y1 = y.clone()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(y, y1)
     eng.close()
