@@ -16,6 +16,8 @@
 //
 // Replaces, per step, BackwardPointwiseKernel + GemmNN (flashlstm_v2/src/lstm_backward.cu:158-227,
 // 1057-1101) and the whole recompute loop (:991-1054), which the gate cache makes unnecessary.
+#include <cstdlib>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -557,7 +559,10 @@ int plan_bwd(int B, int H, int sms, size_t smem_limit, BwdPlan *plan) {
     int nt = (tiles + ngroups - 1) / ngroups;
     ngroups = (tiles + nt - 1) / nt;
     const int kc_per = kc_total / KS;
-    int ch = 4;
+    // measured on config 2: one 64 KB copy per step beats 2, 4, 8 or 16 smaller ones (TMA issue cost
+    // outweighs the longer exposed UMMA tail), so a stage takes up to 16 chunks
+    int ch = 16;
+    if (const char *env = std::getenv("FLSTM_CH")) ch = std::atoi(env) > 0 ? std::atoi(env) : 16;
     while (kc_per % ch) --ch;
     bool resident = true;
     int stages = kc_per / ch;

@@ -19,6 +19,8 @@
 // Replaces, per step, the reference's ScaleAndPackColumnsKernel + GemmTN + ForwardPointwiseKernel
 // launches (flashlstm_v2/src/lstm_forward.cu:744-830) and v1's GEMM + lstm_pointwise_kernel pair
 // (src/lstm.cu:1241-1337, src/kernels.cu:86-164).
+#include <cstdlib>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -414,7 +416,10 @@ int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan) {
     // One TMA copy brings `ch` 64-wide K chunks of an h tile; the ring holds a whole tile when it can.
     // The W_hh slice stays resident if it fits next to a ring of at least two stages.
     const int kc = H / 64;
-    int ch = 4;
+    // measured on config 2: one 64 KB copy per step beats 2, 4, 8 or 16 smaller ones (TMA issue cost
+    // outweighs the longer exposed UMMA tail), so a stage takes up to 16 chunks
+    int ch = 16;
+    if (const char *env = std::getenv("FLSTM_CH")) ch = std::atoi(env) > 0 ? std::atoi(env) : 16;
     while (kc % ch) --ch;
     bool resident = true;
     int stages = kc / ch;
