@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(PKG, "libflashlstm_b200.so")
 # every symbol the public headers declare; tests check that each one is exported
 ENGINE_SYMBOLS = [
     "flstm_engine_create", "flstm_engine_destroy", "flstm_engine_set_weights", "flstm_engine_forward",
-    "flstm_engine_backward", "flstm_engine_grad_ptrs", "flstm_engine_grad_buffer", "flstm_engine_cache_ptrs",
+    "flstm_engine_backward", "flstm_engine_forward_range", "flstm_engine_backward_range", "flstm_engine_grad_ptrs", "flstm_engine_grad_buffer", "flstm_engine_cache_ptrs",
     "flstm_engine_set_cell_io_f32", "flstm_engine_backend", "flstm_comm_unique_id", "flstm_engine_attach_comm",
     "flstm_engine_enable_timing", "flstm_engine_phase_ms", "flstm_engine_launch_count", "flstm_tc_gemm",
     "flstm_engine_enable_trace", "flstm_engine_read_trace", "flstm_bias_grad",
@@ -76,6 +76,8 @@ def load() -> ctypes.CDLL:
     lib.flstm_engine_set_weights.argtypes = [vp, ci, vp, vp, vp, vp, vp]
     lib.flstm_engine_forward.argtypes = [vp, sz, vp, vp, vp, vp, vp, vp, vp]
     lib.flstm_engine_backward.argtypes = [vp, sz, vp, vp, vp, vp, vp, vp, vp]
+    lib.flstm_engine_forward_range.argtypes = [vp, sz, sz, sz, vp, vp, vp, vp, vp, vp, vp]
+    lib.flstm_engine_backward_range.argtypes = [vp, sz, sz, sz, vp, vp, vp, vp, vp, vp, vp]
     lib.flstm_engine_grad_ptrs.argtypes = [vp, ci, ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(vp)]
     lib.flstm_engine_grad_buffer.argtypes = [vp, ctypes.POINTER(vp), ctypes.POINTER(sz)]
     lib.flstm_engine_cache_ptrs.argtypes = [vp, ci, ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(vp),

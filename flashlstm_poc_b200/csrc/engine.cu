@@ -67,7 +67,7 @@ Engine::~Engine() {
         dev_free(l.bias);
     }
     dev_free(grads);
-    dev_free(dc);
+    dev_free(dc_layers);
     dev_free(db_part);
     dev_free(sync_words);
     dev_free(trace);
@@ -142,63 +142,99 @@ int Engine::set_weights(int layer, const float *w_ih, const float *w_hh, const f
 
 int Engine::forward(size_t T, const void *x, const void *h0, const void *c0, void *y, void *hn, void *cn,
                     cudaStream_t s) {
+    return forward_range(T, 0, T, x, h0, c0, y, hn, cn, s);
+}
+
+// Steps [t0, t1) of a T-step forward.  Ranges must be issued in ascending order starting at 0; x and
+// y are the base pointers of the whole (T, B, .) tensors.  Splitting a sequence into ranges lets a
+// caller overlap its own copies (host streaming) with the ranges already enqueued.
+int Engine::forward_range(size_t T, size_t t0, size_t t1, const void *x, const void *h0, const void *c0, void *y,
+                          void *hn, void *cn, cudaStream_t s) {
     const size_t B = cfg.batch, H = cfg.hidden_size, es = dtype_size(cfg.dtype);
     if (T == 0 || B == 0 || H == 0) return FLSTM_OK;  // zero-sized problem: silent no-op (lstm_forward.cu:493-495)
     if (!x) return set_error(FLSTM_ERR_INVALID, "x is null");
-    for (auto &l : layers)
-        if (!l.weights_set) return set_error(FLSTM_ERR_INVALID, "weights have not been set for every layer");
-    FLSTM_TRY(ensure_capacity(T));
-    timer.reset();
-    x_saved = x;
+    if (t0 >= t1 || t1 > T) return set_error(FLSTM_ERR_INVALID, "bad step range [%zu, %zu) of %zu", t0, t1, T);
     const int L = (int)layers.size();
+    const size_t slab = B * H;
+    if (t0 == 0) {
+        for (auto &l : layers)
+            if (!l.weights_set) return set_error(FLSTM_ERR_INVALID, "weights have not been set for every layer");
+        FLSTM_TRY(ensure_capacity(T));
+        timer.reset();
+        x_saved = x;
+        last_T = 0;
+        fwd_progress = 0;
+    } else if (fwd_progress != t0) {
+        return set_error(FLSTM_ERR_INVALID, "forward ranges must be contiguous and ascending (expected start %zu, got %zu)", fwd_progress, t0);
+    }
     for (int li = 0; li < L; ++li) {
         auto &l = layers[li];
-        const size_t slab = B * H;
-        // initial state -> slot 0 of the state tensors
-        if (h0) FLSTM_CUDA_TRY(cudaMemcpyAsync(l.hs, byte_ptr(h0) + li * slab * es, slab * es, cudaMemcpyDeviceToDevice, s));
-        else FLSTM_CUDA_TRY(cudaMemsetAsync(l.hs, 0, slab * es, s));
-        const size_t ces = cell_io_f32 ? sizeof(float) : es;
-        if (c0) { FLSTM_TRY(simt::convert(cell_io_f32 ? FLSTM_DTYPE_F32 : cfg.dtype, byte_ptr(c0) + li * slab * ces, FLSTM_DTYPE_F32, l.cs, slab, s)); ++launches; }
-        else FLSTM_CUDA_TRY(cudaMemsetAsync(l.cs, 0, slab * sizeof(float), s));
-
+        if (t0 == 0) {
+            // initial state -> slot 0 of the state tensors
+            if (h0) FLSTM_CUDA_TRY(cudaMemcpyAsync(l.hs, byte_ptr(h0) + li * slab * es, slab * es, cudaMemcpyDeviceToDevice, s));
+            else FLSTM_CUDA_TRY(cudaMemsetAsync(l.hs, 0, slab * es, s));
+            const size_t ces = cell_io_f32 ? sizeof(float) : es;
+            if (c0) { FLSTM_TRY(simt::convert(cell_io_f32 ? FLSTM_DTYPE_F32 : cfg.dtype, byte_ptr(c0) + li * slab * ces, FLSTM_DTYPE_F32, l.cs, slab, s)); ++launches; }
+            else FLSTM_CUDA_TRY(cudaMemsetAsync(l.cs, 0, slab * sizeof(float), s));
+        }
         const void *x_l = li == 0 ? x : byte_ptr(layers[li - 1].hs) + slab * es;
         void *y_out = (li == L - 1) ? y : nullptr;
         if (backend == FLSTM_BACKEND_TC) {
-            FLSTM_TRY(tc::forward_layer(*this, li, T, x_l, y_out, s));
+            FLSTM_TRY(tc::forward_layer(*this, li, t0, t1, x_l, y_out, s));
         } else {
-            // input projection for all steps at once: P = X W_ih^T + (b_ih + b_hh)
+            // input projection for the steps of the range at once: P = X W_ih^T + (b_ih + b_hh)
             size_t m0 = timer.mark(s);
-            FLSTM_TRY(simt::gemm(cfg.dtype, cfg.dtype, T * B, 4 * H, l.in_size, x_l, l.in_size, true, l.w_ih,
-                                 l.in_size, true, l.gates, 4 * H, l.bias, s));
+            FLSTM_TRY(simt::gemm(cfg.dtype, cfg.dtype, (t1 - t0) * B, 4 * H, l.in_size, byte_ptr(x_l) + t0 * B * l.in_size * es,
+                                 l.in_size, true, l.w_ih, l.in_size, true, byte_ptr(l.gates) + t0 * B * 4 * H * es, 4 * H,
+                                 l.bias, s));
             ++launches;
             size_t m1 = timer.mark(s);
-            for (size_t t = 0; t < T; ++t) {
+            for (size_t t = t0; t < t1; ++t) {
                 FLSTM_TRY(simt::step_forward(cfg.dtype, B, H, byte_ptr(l.hs) + t * slab * es, l.w_hh,
                                              byte_ptr(l.gates) + t * B * 4 * H * es, l.cs + t * slab,
                                              l.cs + (t + 1) * slab, byte_ptr(l.hs) + (t + 1) * slab * es,
                                              y_out ? byte_ptr(y_out) + t * slab * es : nullptr, s));
             }
-            launches += T;
+            launches += t1 - t0;
             size_t m2 = timer.mark(s);
             timer.span(PH_PROJ, m0, m1);
             timer.span(PH_RECUR_FWD, m1, m2);
         }
-        if (hn) FLSTM_CUDA_TRY(cudaMemcpyAsync(byte_ptr(hn) + li * slab * es, byte_ptr(l.hs) + T * slab * es, slab * es, cudaMemcpyDeviceToDevice, s));
-        if (cn) { FLSTM_TRY(simt::convert(FLSTM_DTYPE_F32, l.cs + T * slab, cell_io_f32 ? FLSTM_DTYPE_F32 : cfg.dtype, byte_ptr(cn) + li * slab * ces, slab, s)); ++launches; }
+        if (t1 == T) {
+            const size_t ces = cell_io_f32 ? sizeof(float) : es;
+            if (hn) FLSTM_CUDA_TRY(cudaMemcpyAsync(byte_ptr(hn) + li * slab * es, byte_ptr(l.hs) + T * slab * es, slab * es, cudaMemcpyDeviceToDevice, s));
+            if (cn) { FLSTM_TRY(simt::convert(FLSTM_DTYPE_F32, l.cs + T * slab, cell_io_f32 ? FLSTM_DTYPE_F32 : cfg.dtype, byte_ptr(cn) + li * slab * ces, slab, s)); ++launches; }
+        }
     }
-    last_T = T;
+    fwd_progress = t1;
+    if (t1 == T) {
+        last_T = T;
+        bwd_progress = T;
+    }
     return FLSTM_OK;
 }
 
 int Engine::backward(size_t T, const void *dy, const void *dhn, const void *dcn, void *dx, float *dh0,
                      float *dc0, cudaStream_t s) {
+    return backward_range(T, 0, T, dy, dhn, dcn, dx, dh0, dc0, s);
+}
+
+// Time steps [t0, t1) of the backward pass, in reverse.  Ranges must be issued in descending order,
+// the first one ending at T; dy and dx are base pointers of the whole tensors.  dX of a range is
+// complete when the range's work is; the weight and bias gradients (and their allreduce) are formed
+// by the last range (t0 == 0).
+int Engine::backward_range(size_t T, size_t t0, size_t t1, const void *dy, const void *dhn, const void *dcn, void *dx,
+                           float *dh0, float *dc0, cudaStream_t s) {
     const size_t B = cfg.batch, H = cfg.hidden_size, es = dtype_size(cfg.dtype);
     if (T == 0 || B == 0 || H == 0) return FLSTM_OK;
     if (!cfg.training) return set_error(FLSTM_ERR_INVALID, "engine was created with training = 0");
     if (last_T != T) return set_error(FLSTM_ERR_INVALID, "backward(T=%zu) does not follow a forward of the same length (last T=%zu)", T, last_T);
     if (!dy) return set_error(FLSTM_ERR_INVALID, "dy is null");
+    if (t0 >= t1 || t1 > T) return set_error(FLSTM_ERR_INVALID, "bad step range [%zu, %zu) of %zu", t0, t1, T);
+    if (bwd_progress != t1) return set_error(FLSTM_ERR_INVALID, "backward ranges must be contiguous and descending (expected end %zu, got %zu)", bwd_progress, t1);
     const int L = (int)layers.size();
     const size_t slab = B * H;
+    const size_t n = t1 - t0;  // steps in the range
     for (int li = L - 1; li >= 0; --li) {
         auto &l = layers[li];
         const void *x_l = li == 0 ? x_saved : byte_ptr(layers[li - 1].hs) + slab * es;
@@ -209,34 +245,40 @@ int Engine::backward(size_t T, const void *dy, const void *dhn, const void *dcn,
         float *dh0_l = dh0 ? dh0 + li * slab : nullptr;
         float *dc0_l = dc0 ? dc0 + li * slab : nullptr;
         if (backend == FLSTM_BACKEND_TC) {
-            FLSTM_TRY(tc::backward_layer(*this, li, T, x_l, dy_l, dhn_l, dcn_l, dx_l, dh0_l, dc0_l, s));
+            FLSTM_TRY(tc::backward_layer(*this, li, T, t0, t1, x_l, dy_l, dhn_l, dcn_l, dx_l, dh0_l, dc0_l, s));
         } else {
+            float *dc_l = dc_layers + li * slab;  // the carry survives between ranges, one per layer
             size_t m0 = timer.mark(s);
-            if (dcn_l) { FLSTM_TRY(simt::convert(cfg.dtype, dcn_l, FLSTM_DTYPE_F32, dc, slab, s)); ++launches; }
-            else FLSTM_CUDA_TRY(cudaMemsetAsync(dc, 0, slab * sizeof(float), s));
-            for (size_t step = 0; step < T; ++step) {
-                size_t t = T - 1 - step;
+            if (t1 == T) {
+                if (dcn_l) { FLSTM_TRY(simt::convert(cfg.dtype, dcn_l, FLSTM_DTYPE_F32, dc_l, slab, s)); ++launches; }
+                else FLSTM_CUDA_TRY(cudaMemsetAsync(dc_l, 0, slab * sizeof(float), s));
+            }
+            for (size_t step = 0; step < n; ++step) {
+                size_t t = t1 - 1 - step;
                 const void *dg_next = (t == T - 1) ? nullptr : byte_ptr(l.dg) + (t + 1) * B * 4 * H * es;
                 FLSTM_TRY(simt::step_backward(cfg.dtype, B, H, dg_next, l.w_hh, dhn_l,
                                               byte_ptr(dy_l) + t * slab * es,
                                               byte_ptr(l.gates) + t * B * 4 * H * es, l.cs + (t + 1) * slab,
-                                              l.cs + t * slab, dc, byte_ptr(l.dg) + t * B * 4 * H * es, s));
+                                              l.cs + t * slab, dc_l, byte_ptr(l.dg) + t * B * 4 * H * es, s));
             }
-            launches += T;
-            if (dh0_l) { FLSTM_TRY(simt::final_dh(cfg.dtype, B, H, l.dg, l.w_hh, dh0_l, s)); ++launches; }
-            if (dc0_l) FLSTM_CUDA_TRY(cudaMemcpyAsync(dc0_l, dc, slab * sizeof(float), cudaMemcpyDeviceToDevice, s));
-            size_t m1 = timer.mark(s);
-            // deferred parameter gradients over the whole sequence
-            FLSTM_TRY(simt::gemm(cfg.dtype, FLSTM_DTYPE_F32, 4 * H, l.in_size, T * B, l.dg, 4 * H, false, x_l,
-                                 l.in_size, false, l.dw_ih, l.in_size, nullptr, s));
-            FLSTM_TRY(simt::gemm(cfg.dtype, FLSTM_DTYPE_F32, 4 * H, H, T * B, l.dg, 4 * H, false, l.hs, H, false,
-                                 l.dw_hh, H, nullptr, s));
-            FLSTM_TRY(simt::column_sum(cfg.dtype, l.dg, T * B, 4 * H, l.db, s));
-            launches += 3;
-            size_t m2 = timer.mark(s);
+            launches += n;
+            size_t m1 = timer.mark(s), m2 = m1;
+            if (t0 == 0) {
+                if (dh0_l) { FLSTM_TRY(simt::final_dh(cfg.dtype, B, H, l.dg, l.w_hh, dh0_l, s)); ++launches; }
+                if (dc0_l) FLSTM_CUDA_TRY(cudaMemcpyAsync(dc0_l, dc_l, slab * sizeof(float), cudaMemcpyDeviceToDevice, s));
+                // deferred parameter gradients over the whole sequence
+                FLSTM_TRY(simt::gemm(cfg.dtype, FLSTM_DTYPE_F32, 4 * H, l.in_size, T * B, l.dg, 4 * H, false, x_l,
+                                     l.in_size, false, l.dw_ih, l.in_size, nullptr, s));
+                FLSTM_TRY(simt::gemm(cfg.dtype, FLSTM_DTYPE_F32, 4 * H, H, T * B, l.dg, 4 * H, false, l.hs, H, false,
+                                     l.dw_hh, H, nullptr, s));
+                FLSTM_TRY(simt::column_sum(cfg.dtype, l.dg, T * B, 4 * H, l.db, s));
+                launches += 3;
+                m2 = timer.mark(s);
+            }
             if (dx_l) {
-                FLSTM_TRY(simt::gemm(cfg.dtype, cfg.dtype, T * B, l.in_size, 4 * H, l.dg, 4 * H, true, l.w_ih,
-                                     l.in_size, false, dx_l, l.in_size, nullptr, s));
+                FLSTM_TRY(simt::gemm(cfg.dtype, cfg.dtype, n * B, l.in_size, 4 * H, byte_ptr(l.dg) + t0 * B * 4 * H * es, 4 * H,
+                                     true, l.w_ih, l.in_size, false, byte_ptr(dx_l) + t0 * B * l.in_size * es, l.in_size,
+                                     nullptr, s));
                 ++launches;
             }
             size_t m3 = timer.mark(s);
@@ -244,22 +286,27 @@ int Engine::backward(size_t T, const void *dy, const void *dhn, const void *dcn,
             timer.span(PH_WGRAD, m1, m2);
             timer.span(PH_XGRAD, m2, m3);
         }
-        if (comm) {
+        if (comm && t0 == 0) {
             // reduce this layer's gradients while the layers below keep back-propagating
             FLSTM_CUDA_TRY(cudaEventRecord(comm_fork, s));
             FLSTM_CUDA_TRY(cudaStreamWaitEvent(comm_stream, comm_fork, 0));
-            size_t c0 = timer.mark(comm_stream);
+            size_t c0m = timer.mark(comm_stream);
             FLSTM_TRY(comm_allreduce_sum_f32(comm, grads + l.grad_offset, l.grad_count, comm_stream));
-            size_t c1 = timer.mark(comm_stream);
-            timer.span(PH_ALLREDUCE, c0, c1);
+            size_t c1m = timer.mark(comm_stream);
+            timer.span(PH_ALLREDUCE, c0m, c1m);
         }
     }
-    if (comm) {
+    if (comm && t0 == 0) {
         FLSTM_CUDA_TRY(cudaEventRecord(comm_join, comm_stream));
         FLSTM_CUDA_TRY(cudaStreamWaitEvent(s, comm_join, 0));
     }
+    bwd_progress = t0;
     return FLSTM_OK;
 }
+
+}  // namespace flstm_b200
+
+namespace flstm_b200 {
 
 // ------------------------------------------------------------------ phase timer
 size_t PhaseTimer::mark(cudaStream_t s) {
@@ -340,8 +387,8 @@ int flstm_engine_create(const flstm_engine_config *config, flstm_engine **out) {
         if (cudaMalloc(&raw, total * sizeof(float)) != cudaSuccess) return fail(set_error(FLSTM_ERR_CUDA, "cudaMalloc of the gradient buffer failed"));
         e.grads = static_cast<float *>(raw);
         cudaMemset(raw, 0, total * sizeof(float));
-        if (cudaMalloc(&raw, B * H * sizeof(float)) != cudaSuccess) return fail(set_error(FLSTM_ERR_CUDA, "cudaMalloc failed"));
-        e.dc = static_cast<float *>(raw);
+        if (cudaMalloc(&raw, (size_t)config->layers * B * H * sizeof(float)) != cudaSuccess) return fail(set_error(FLSTM_ERR_CUDA, "cudaMalloc failed"));
+        e.dc_layers = static_cast<float *>(raw);
     }
     for (auto &l : e.layers) {
         l.dw_ih = e.grads + l.grad_offset;
@@ -389,6 +436,18 @@ int flstm_engine_backward(flstm_engine *engine, size_t seq_len, const void *dy, 
                           const void *d_cn, void *dx, float *dh0, float *dc0, void *stream) {
     if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
     return engine->impl.backward(seq_len, dy, d_hn, d_cn, dx, dh0, dc0, static_cast<cudaStream_t>(stream));
+}
+
+int flstm_engine_forward_range(flstm_engine *engine, size_t seq_len, size_t t0, size_t t1, const void *x, const void *h0,
+                               const void *c0, void *y, void *h_n, void *c_n, void *stream) {
+    if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    return engine->impl.forward_range(seq_len, t0, t1, x, h0, c0, y, h_n, c_n, static_cast<cudaStream_t>(stream));
+}
+
+int flstm_engine_backward_range(flstm_engine *engine, size_t seq_len, size_t t0, size_t t1, const void *dy,
+                                const void *d_hn, const void *d_cn, void *dx, float *dh0, float *dc0, void *stream) {
+    if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    return engine->impl.backward_range(seq_len, t0, t1, dy, d_hn, d_cn, dx, dh0, dc0, static_cast<cudaStream_t>(stream));
 }
 
 int flstm_engine_grad_ptrs(flstm_engine *engine, int layer, float **dw_ih, float **dw_hh, float **db) {

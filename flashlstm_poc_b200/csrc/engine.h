@@ -59,10 +59,12 @@ struct Engine {
     std::vector<LayerBuffers> layers;
     float *grads = nullptr;  // flat fp32: per layer [dW_ih | dW_hh | db]
     size_t grad_count = 0;
-    float *dc = nullptr;     // fp32 (B,H) cell-gradient carry
+    float *dc_layers = nullptr;  // fp32 (L,B,H) cell-gradient carry, kept between backward ranges
     float *db_part = nullptr;  // TC: per batch-tile partial bias gradients
     unsigned int *sync_words = nullptr;  // TC: grid-barrier counters + error word
-    size_t last_T = 0;       // sequence length of the last forward (0 = none)
+    size_t last_T = 0;       // sequence length of the last complete forward (0 = none)
+    size_t fwd_progress = 0; // steps of the current forward already enqueued
+    size_t bwd_progress = 0; // backward has been enqueued down to this step
     unsigned long long launches = 0;
     bool cell_io_f32 = false;       // c0 / c_n cross the API as fp32 instead of the engine dtype
     const void *x_saved = nullptr;  // layer-0 input of the last forward (caller keeps it alive)
@@ -84,6 +86,10 @@ struct Engine {
                 cudaStream_t s);
     int backward(size_t T, const void *dy, const void *dhn, const void *dcn, void *dx, float *dh0,
                  float *dc0, cudaStream_t s);
+    int forward_range(size_t T, size_t t0, size_t t1, const void *x, const void *h0, const void *c0, void *y, void *hn,
+                      void *cn, cudaStream_t s);
+    int backward_range(size_t T, size_t t0, size_t t1, const void *dy, const void *dhn, const void *dcn, void *dx,
+                       float *dh0, float *dc0, cudaStream_t s);
 };
 
 }  // namespace flstm_b200
@@ -103,9 +109,9 @@ void destroy(Engine &e);
 int on_capacity_change(Engine &e);
 int set_weights(Engine &e, int layer, const float *w_ih, const float *w_hh, const float *b_ih,
                 const float *b_hh, cudaStream_t s);
-int forward_layer(Engine &e, int layer, size_t T, const void *x_l, void *y_out, cudaStream_t s);
-int backward_layer(Engine &e, int layer, size_t T, const void *x_l, const void *dy_l, const void *dhn_l,
-                   const void *dcn_l, void *dx_l, float *dh0_l, float *dc0_l, cudaStream_t s);
+int forward_layer(Engine &e, int layer, size_t t0, size_t t1, const void *x_l, void *y_out, cudaStream_t s);
+int backward_layer(Engine &e, int layer, size_t T, size_t t0, size_t t1, const void *x_l, const void *dy_l,
+                   const void *dhn_l, const void *dcn_l, void *dx_l, float *dh0_l, float *dc0_l, cudaStream_t s);
 }  // namespace tc
 
 // Communicator (comm.cu): NCCL loaded at run time with dlopen.

@@ -191,17 +191,17 @@ static int check_async_error(Engine &e) {
 
 int poll_error(Engine &e) { return check_async_error(e); }
 
-int forward_layer(Engine &e, int li, size_t T, const void *x_l, void *y_out, cudaStream_t s) {
+int forward_layer(Engine &e, int li, size_t t0, size_t t1, const void *x_l, void *y_out, cudaStream_t s) {
     TcState *st = state(e);
     FLSTM_TRY(check_async_error(e));
     auto &l = e.layers[li];
     auto &t = st->layers[li];
-    const size_t B = e.cfg.batch, H = e.cfg.hidden_size;
+    const size_t B = e.cfg.batch, H = e.cfg.hidden_size, es = dtype_size(e.cfg.dtype), n = t1 - t0;
     unsigned int *err = e.sync_words;
     size_t m0 = e.timer.mark(s);
-    // P = X W_ih^T + (b_ih + b_hh), 16-bit, columns tile-interleaved
-    FLSTM_TRY(gemm(e.cfg.dtype, e.cfg.dtype, T * B, 4 * H, l.in_size, x_l, l.in_size, false, l.w_ih, l.in_size, false,
-                   l.gates, 4 * H, l.bias, 0, err, st->sms, s));
+    // P = X W_ih^T + (b_ih + b_hh) for the steps of the range, 16-bit, columns tile-interleaved
+    FLSTM_TRY(gemm(e.cfg.dtype, e.cfg.dtype, n * B, 4 * H, l.in_size, byte_ptr(x_l) + t0 * B * l.in_size * es, l.in_size, false,
+                   l.w_ih, l.in_size, false, byte_ptr(l.gates) + t0 * B * 4 * H * es, 4 * H, l.bias, 0, err, st->sms, s));
     size_t m1 = e.timer.mark(s);
     FLSTM_CUDA_TRY(cudaMemsetAsync(e.sync_words + 1, 0, (size_t)st->fwd.ngroups * sizeof(unsigned int), s));
     FwdParams p{};
@@ -211,11 +211,12 @@ int forward_layer(Engine &e, int li, size_t T, const void *x_l, void *y_out, cud
     p.gates = l.gates;
     p.counters = e.sync_words + 1;
     p.err = err;
-    p.T = (int)T;
+    p.T = (int)n;
+    p.t0 = (int)t0;
     p.B = (int)B;
     p.H = (int)H;
     p.store_gates = e.cfg.training ? 1 : 0;
-    p.trace = (li == 0) ? e.trace : nullptr;
+    p.trace = (li == 0 && t0 == 0) ? e.trace : nullptr;
     p.trace_steps = e.trace_steps;
     FLSTM_TRY(lstm_forward_persistent(e.cfg.dtype, st->fwd, t.tm_w, t.tm_h, t.tm_g, p, s));
     size_t m2 = e.timer.mark(s);
@@ -226,14 +227,14 @@ int forward_layer(Engine &e, int li, size_t T, const void *x_l, void *y_out, cud
     return FLSTM_OK;
 }
 
-int backward_layer(Engine &e, int li, size_t T, const void *x_l, const void *dy_l, const void *dhn_l,
+int backward_layer(Engine &e, int li, size_t T, size_t t0, size_t t1, const void *x_l, const void *dy_l, const void *dhn_l,
                    const void *dcn_l, void *dx_l, float *dh0_l, float *dc0_l, cudaStream_t s) {
     TcState *st = state(e);
     FLSTM_TRY(check_async_error(e));
     if (!st->bwd_ok) return set_error(FLSTM_ERR_UNSUPPORTED, "tensor-core backward is not planned for this engine");
     auto &l = e.layers[li];
     auto &t = st->layers[li];
-    const size_t B = e.cfg.batch, H = e.cfg.hidden_size;
+    const size_t B = e.cfg.batch, H = e.cfg.hidden_size, es = dtype_size(e.cfg.dtype), n = t1 - t0;
     unsigned int *err = e.sync_words;
     size_t m0 = e.timer.mark(s);
     FLSTM_CUDA_TRY(cudaMemsetAsync(e.sync_words + 1, 0, (size_t)st->bwd.ngroups * sizeof(unsigned int), s));
@@ -246,35 +247,41 @@ int backward_layer(Engine &e, int li, size_t T, const void *x_l, const void *dy_
     p.dcn = dcn_l;
     p.dh0 = dh0_l;
     p.dc0 = dc0_l;
-    p.dc = e.dc;
-    p.trace = (li == 0 && e.trace) ? e.trace + (size_t)e.trace_steps * 16 : nullptr;
+    p.dc = e.dc_layers + (size_t)li * B * H;
+    p.trace = (li == 0 && e.trace && t1 == T) ? e.trace + (size_t)e.trace_steps * 16 : nullptr;
     p.trace_steps = e.trace_steps;
     p.counters = e.sync_words + 1;
     p.err = err;
     p.T = (int)T;
+    p.s0 = (int)(T - t1);
+    p.s1 = (int)(T - t0) + (t0 == 0 ? 1 : 0);  // the last range also runs the iteration that writes dh0 / dc0
     p.B = (int)B;
     p.H = (int)H;
     FLSTM_TRY(lstm_backward_persistent(e.cfg.dtype, st->bwd, t.tm_w, t.tm_dg, p, s));
-    size_t m1 = e.timer.mark(s);
-    // dW = dG^T [X | H_prev]: both operands read as stored (reduction dim T*B outermost); rows of
-    // the product are written back in torch gate order
-    FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, l.in_size, T * B, l.dg, 4 * H, true, x_l, l.in_size, true,
-                   l.dw_ih, l.in_size, nullptr, (int)H, err, st->sms, s));
-    FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, H, T * B, l.dg, 4 * H, true, l.hs, H, true, l.dw_hh, H, nullptr,
-                   (int)H, err, st->sms, s));
-    FLSTM_TRY(simt::column_sum_two_pass(e.cfg.dtype, l.dg, T * B, 4 * H, e.db_part, l.db, (int)H, s));
-    size_t m2 = e.timer.mark(s);
+    size_t m1 = e.timer.mark(s), m2 = m1;
+    if (t0 == 0) {
+        // dW = dG^T [X | H_prev] over the whole sequence: both operands read as stored (reduction dim
+        // T*B outermost); rows of the product are written back in torch gate order
+        FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, l.in_size, T * B, l.dg, 4 * H, true, x_l, l.in_size, true,
+                       l.dw_ih, l.in_size, nullptr, (int)H, err, st->sms, s));
+        FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, H, T * B, l.dg, 4 * H, true, l.hs, H, true, l.dw_hh, H, nullptr,
+                       (int)H, err, st->sms, s));
+        FLSTM_TRY(simt::column_sum_two_pass(e.cfg.dtype, l.dg, T * B, 4 * H, e.db_part, l.db, (int)H, s));
+        e.launches += 4;
+        m2 = e.timer.mark(s);
+    }
     if (dx_l) {
-        // dX = dG W_ih: W_ih (rows tile-interleaved, like dG's columns) is read as stored
-        FLSTM_TRY(gemm(e.cfg.dtype, e.cfg.dtype, T * B, l.in_size, 4 * H, l.dg, 4 * H, false, l.w_ih, l.in_size, true,
-                       dx_l, l.in_size, nullptr, 0, err, st->sms, s));
+        // dX = dG W_ih for the steps of the range: W_ih (rows tile-interleaved, like dG's columns) is read as stored
+        FLSTM_TRY(gemm(e.cfg.dtype, e.cfg.dtype, n * B, l.in_size, 4 * H, byte_ptr(l.dg) + t0 * B * 4 * H * es, 4 * H, false,
+                       l.w_ih, l.in_size, true, byte_ptr(dx_l) + t0 * B * l.in_size * es, l.in_size, nullptr, 0, err, st->sms,
+                       s));
         ++e.launches;
     }
     size_t m3 = e.timer.mark(s);
     e.timer.span(PH_BPTT, m0, m1);
     e.timer.span(PH_WGRAD, m1, m2);
     e.timer.span(PH_XGRAD, m2, m3);
-    e.launches += 5;
+    e.launches += 1;
     FLSTM_CUDA_TRY(cudaMemcpyAsync(st->err_host, err, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
     return FLSTM_OK;
 }

@@ -42,7 +42,8 @@ struct FwdParams {
     void *gates;          // 16-bit (T, B, 4H): holds P on entry, the activated gates on exit
     unsigned int *counters;  // one step counter per batch group, zeroed before the launch
     unsigned int *err;    // error word: non-zero after a bounded wait expired
-    int T, B, H;
+    int T, B, H;          // T = number of steps this launch runs
+    int t0;               // first (absolute) time step of this launch; the state of step t0 is in slot t0 of hs/cs
     int store_gates;      // write the activated gates back (the gate cache)
     long long *trace;     // optional: CTA 0 stamps clock64() at 16 points of each of the first trace_steps steps
     int trace_steps;
@@ -83,7 +84,8 @@ struct BwdParams {
     unsigned int *err;
     long long *trace;     // optional per-step clock64() stamps of CTA 0 (see FwdParams)
     int trace_steps;
-    int T, B, H;
+    int T, B, H;          // T = length of the whole sequence
+    int s0, s1;           // reverse iterations [s0, s1) of this launch; iteration s is time T-1-s, s == T writes dh0/dc0
     int jt, nt, stages, ch;
     uint32_t idesc;
 };

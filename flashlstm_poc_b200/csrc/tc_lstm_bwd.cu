@@ -226,12 +226,15 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             }
             int stage = 0;
             uint32_t phase = 0;
-            for (int s = 1; s <= p.T && ok; ++s) {
+            // this launch runs reverse iterations [s0, s1); iteration s handles time t = T-1-s and, for
+            // s >= 1, first contracts dG_{t+1}, which iteration s-1 produced (in this launch: wait for
+            // the group's counter; in the previous launch: already complete)
+            for (int s = (p.s0 > 1 ? p.s0 : 1); s < p.s1 && ok; ++s) {
                 const int t_src = p.T - s;  // dG_{t+1} with t = T-1-s
-                ok = wait_counter(counter, (unsigned)(p.jt * KS * 4) * (unsigned)s, p.err, abort_w);
+                if (s > p.s0) ok = wait_counter(counter, (unsigned)(p.jt * KS * 4) * (unsigned)(s - p.s0), p.err, abort_w);
                 if (!ok) break;
                 fence_proxy_async_all();
-                FLSTM_STAMP(s, 0);
+                FLSTM_STAMP(s - p.s0, 0);
                 for (int n = 0; n < nt_count && ok; ++n) {
                     const int b0 = (ng * nt_count + n) * BT;
                     for (int ld = 0; ld < NLOAD; ++ld) {
@@ -248,7 +251,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         if (++stage == L.stages) { stage = 0; phase ^= 1; }
                     }
                 }
-                FLSTM_STAMP(s, 1);
+                FLSTM_STAMP(s - p.s0, 1);
             }
         }
     } else if (warp == 5) {
@@ -259,7 +262,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             int stage = 0;
             uint32_t phase = 0;
             const uint32_t s_w_u32 = smem_u32(s_w), idesc = p.idesc;
-            const uint32_t items = (uint32_t)p.T * nt_count;
+            const uint32_t items = (uint32_t)(p.s1 - (p.s0 > 1 ? p.s0 : 1)) * nt_count;
             for (uint32_t wi = 0; wi < items && ok; ++wi) {
                 const int buf = wi & 1;
                 ok = mbar_wait(&tempty[buf], ((wi >> 1) & 1) ^ 1, abort_w);
@@ -269,8 +272,8 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 for (int ld = 0; ld < NLOAD; ++ld) {
                     ok = mbar_wait(&full[stage], phase, abort_w);
                     if (!ok) break;
-                    if (ld == 0) FLSTM_STAMP((int)(wi / nt_count) + 1, 2);
-                    if (ld == NLOAD - 1) FLSTM_STAMP((int)(wi / nt_count) + 1, 3);
+                    if (ld == 0) FLSTM_STAMP((int)(wi / nt_count) + 1 - (p.s0 > 0 ? 1 : 0), 2);
+                    if (ld == NLOAD - 1) FLSTM_STAMP((int)(wi / nt_count) + 1 - (p.s0 > 0 ? 1 : 0), 3);
                     tcgen05_fence_after();
                     const uint32_t st_base = smem_u32(s_ring + stage * L.ring_stage_bytes);
                     for (int c = 0; c < CH; ++c) {
@@ -291,7 +294,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 }
                 if (!ok) break;
                 umma_commit(&tfull[buf]);
-                FLSTM_STAMP((int)(wi / nt_count) + 1, 4);
+                FLSTM_STAMP((int)(wi / nt_count) + 1 - (p.s0 > 0 ? 1 : 0), 4);
             }
         }
     } else {
@@ -311,7 +314,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         const uint32_t rbar_local = smem_u32(rbar);
         uint32_t wi = 0;  // MMA item counter (iterations s >= 1)
         bool ok = true;
-        for (int s = 0; s <= p.T && ok; ++s) {
+        for (int s = p.s0; s < p.s1 && ok; ++s) {
             const int t = p.T - 1 - s;  // time step whose dG is produced (t = -1: only dh0 / dc0)
             for (int n = 0; n < nt_count && ok; ++n) {
                 const int b0 = (ng * nt_count + n) * BT;
@@ -343,7 +346,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         const int b = b0 + nb + 8 * i;
                         const size_t idx = (size_t)b * p.H + unit_of(q);
                         if (s == 0) dc_in[k] = (dcn && b < p.B) ? load16<BF16>(dcn + idx) : 0.f;
-                        else if (keep_dc) dc_in[k] = dc_keep[k];
+                        else if (keep_dc && s > p.s0) dc_in[k] = dc_keep[k];
                         else dc_in[k] = (b < p.B) ? p.dc[idx] : 0.f;
                         if (PREFETCH) load_pair(q, i, in[k]);
                     }
@@ -361,7 +364,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     const int buf = wi & 1, rb = wi & 1;
                     ok = mbar_wait(&tfull[buf], (wi >> 1) & 1, abort_w);
                     if (!ok) break;
-                    if (tid == 0) FLSTM_STAMP(s, 5);
+                    if (tid == 0) FLSTM_STAMP(s - p.s0, 5);
                     tcgen05_fence_after();
                     // phase A: lanes 0..15 of warp w hold units 16w+lane of the tile, all BT sequences
 #pragma unroll
@@ -395,10 +398,10 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         if (KS > 1) mbar_arrive_cluster(map_to_rank(rbar_local + rb * 8, owner));
                         else mbar_arrive(&rbar[rb]);
                     }
-                    if (tid == 0) FLSTM_STAMP(s, 9);
+                    if (tid == 0) FLSTM_STAMP(s - p.s0, 9);
                     ok = mbar_wait_cluster(&rbar[rb], (wi >> 1) & 1, abort_w);
                     if (!ok) break;
-                    if (tid == 0) FLSTM_STAMP(s, 10);
+                    if (tid == 0) FLSTM_STAMP(s - p.s0, 10);
                     const float *red = s_red + (size_t)rb * KS * UPO * RS;
 #pragma unroll
                     for (int q = 0; q < UQ; ++q)
@@ -412,7 +415,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         }
                     // every warp has read this item's partials before any warp sends the next item's
                     named_barrier_sync(1, 128);
-                    if (tid == 0) FLSTM_STAMP(s, 6);
+                    if (tid == 0) FLSTM_STAMP(s - p.s0, 6);
                     ++wi;
                 }
                 // fused pointwise backward for the owned (unit, sequence) pairs
@@ -452,13 +455,24 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             }
             if (!ok) break;
             if (t >= 0) {
-                if (tid == 0) FLSTM_STAMP(s, 7);
+                if (tid == 0) FLSTM_STAMP(s - p.s0, 7);
                 // publish dG_t (release, cumulative over the warp's stores); the generic->async proxy fence
                 // is on the consumer side, after its acquire and before its TMA loads
                 __syncwarp();
                 if (lane == 0) red_release_gpu_add(counter, 1u);
-                if (tid == 0) FLSTM_STAMP(s, 8);
+                if (tid == 0) FLSTM_STAMP(s - p.s0, 8);
             }
+        }
+        // a later launch continues the recurrence: leave the cell-gradient carry where it will look for it
+        if (ok && keep_dc && p.s1 <= p.T) {
+            const int b0 = ng * nt_count * BT;
+#pragma unroll
+            for (int q = 0; q < UQ; ++q)
+#pragma unroll
+                for (int i = 0; i < BT / 8; ++i) {
+                    const int b = b0 + nb + 8 * i;
+                    if (b < p.B) p.dc[(size_t)b * p.H + j * 64 + kq * UPO + q * 16 + u16] = dc_keep[q * (BT / 8) + i];
+                }
         }
     }
     tcgen05_fence_before();

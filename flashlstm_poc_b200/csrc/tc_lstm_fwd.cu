@@ -179,7 +179,8 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             }
             int stage = 0;
             uint32_t phase = 0, wi = 0;
-            for (int t = 0; t < p.T && ok; ++t) {
+            for (int tt = 0; tt < p.T && ok; ++tt) {
+                const int t = p.t0 + tt;  // absolute time step; this launch runs steps [t0, t0 + T)
                 bool first = true;
                 for (int r = 0; r < p.rt && ok; ++r) {
                     const int j = jr * p.rt + r;
@@ -190,14 +191,15 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         if (!ok) break;
                         mbar_expect_tx(&pfull[pb], BT * 128);
                         tma_load_3d(s_p + pb * BT * 128, &tm_g, j * 64, b0, t, &pfull[pb]);
-                        if (first && t > 0) {
+                        if (first && tt > 0) {
                             // h_{t-1} of this batch group is complete when every CTA of the group has
-                            // arrived t times (4 epilogue warps each)
-                            ok = wait_counter(counter, (unsigned)(p.cta_rows * 4) * (unsigned)t, p.err, abort_w);
+                            // arrived tt times in this launch (4 epilogue warps each); the state a launch
+                            // starts from was completed by the previous launch
+                            ok = wait_counter(counter, (unsigned)(p.cta_rows * 4) * (unsigned)tt, p.err, abort_w);
                             if (!ok) break;
                             fence_proxy_async_all();
                         }
-                        if (first) FLSTM_STAMP(t, 0);
+                        if (first) FLSTM_STAMP(tt, 0);
                         first = false;
                         for (int ld = 0; ld < NLOAD; ++ld) {
                             ok = mbar_wait(&empty[stage], phase ^ 1, abort_w);
@@ -212,7 +214,7 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                                                 &full[stage]);
                             if (++stage == L.stages) { stage = 0; phase ^= 1; }
                         }
-                        FLSTM_STAMP(t, 1);
+                        FLSTM_STAMP(tt, 1);
                     }
                 }
             }
@@ -276,7 +278,8 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         uint16_t *gates = static_cast<uint16_t *>(p.gates);
         uint32_t wi = 0;
         bool ok = true;
-        for (int t = 0; t < p.T && ok; ++t) {
+        for (int tt = 0; tt < p.T && ok; ++tt) {
+            const int t = p.t0 + tt;
             for (int r = 0; r < p.rt && ok; ++r) {
                 const int j = jr * p.rt + r;
                 for (int n = 0; n < nt_count && ok; ++n, ++wi) {
@@ -288,12 +291,12 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
 #pragma unroll
                     for (int i = 0; i < PAIRS; ++i) {
                         const int b = b0 + nb + 8 * i;
-                        if (keep_c && t > 0) c_prev[i] = c_keep[i];
+                        if (keep_c && tt > 0) c_prev[i] = c_keep[i];
                         else c_prev[i] = (b < p.B) ? p.cs[(size_t)t * slab + (size_t)b * p.H + j * 16 + u] : 0.f;
                     }
                     ok = mbar_wait(&tfull[buf], (wi >> 1) & 1, abort_w);
                     if (!ok) break;
-                    if (tid == 0) FLSTM_STAMP(t, 5);
+                    if (tid == 0) FLSTM_STAMP(tt, 5);
                     tcgen05_fence_after();
                     float *ex = s_ex + (wi & 1) * 64 * EXS;
                     // phase A: lanes 0..15 of warp g hold the recurrent sums of gate g, units 0..15, all
@@ -317,7 +320,7 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     ok = mbar_wait(&pfull[pb], (wi >> 1) & 1, abort_w);
                     if (!ok) break;
                     named_barrier_sync(1, 128);
-                    if (tid == 0) FLSTM_STAMP(t, 6);
+                    if (tid == 0) FLSTM_STAMP(tt, 6);
                     // phase B: one thread per (unit, sequence) pair does the whole pointwise update
                     const uint16_t *ptile = reinterpret_cast<const uint16_t *>(s_p + pb * BT * 128);
                     float act[PAIRS][4];
@@ -341,13 +344,13 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&pempty[pb]);  // this warp is done with the P tile
                     if (last_item) {
-                        if (tid == 0) FLSTM_STAMP(t, 7);
+                        if (tid == 0) FLSTM_STAMP(tt, 7);
                         // publish h_t: the release is cumulative over the warp's stores ordered before it
                         // by __syncwarp.  The generic->async proxy fence sits on the consumer side, between
                         // its acquire of the counter and its TMA loads.
                         __syncwarp();
                         if (lane == 0) red_release_gpu_add(counter, 1u);
-                        if (tid == 0) FLSTM_STAMP(t, 8);
+                        if (tid == 0) FLSTM_STAMP(tt, 8);
                     }
                     // everything nobody waits for: cell state, gate cache, the caller's y
 #pragma unroll

@@ -121,6 +121,16 @@ class Engine:
         check(self.lib.flstm_engine_backward(self._h, T, dy.data_ptr(), _ptr(dhn), _ptr(dcn), _ptr(dx), _ptr(dh0),
                                              _ptr(dc0), self._stream()))
 
+    def forward_range_into(self, T: int, t0: int, t1: int, x, h0, c0, y, hn, cn) -> None:
+        """Steps [t0, t1) of a T-step forward; ranges ascending from 0 (see flstm_engine_forward_range)."""
+        check(self.lib.flstm_engine_forward_range(self._h, T, t0, t1, x.data_ptr(), _ptr(h0), _ptr(c0), _ptr(y), _ptr(hn),
+                                                  _ptr(cn), self._stream()))
+
+    def backward_range_into(self, T: int, t0: int, t1: int, dy, dhn, dcn, dx, dh0, dc0) -> None:
+        """Steps [t0, t1) of the backward pass; ranges descending from T (see flstm_engine_backward_range)."""
+        check(self.lib.flstm_engine_backward_range(self._h, T, t0, t1, dy.data_ptr(), _ptr(dhn), _ptr(dcn), _ptr(dx),
+                                                   _ptr(dh0), _ptr(dc0), self._stream()))
+
     def capture_step(self, x, h0, c0, y, hn, cn, dy=None, dx=None, dh0=None, dc0=None) -> "torch.cuda.CUDAGraph":
         """Capture one forward (+ backward when dy is given) over the given, caller-owned tensors into a
         CUDA graph: the projection GEMM, the persistent recurrent kernels (cooperative launches), the

@@ -85,6 +85,18 @@ int flstm_engine_forward(flstm_engine *engine, size_t seq_len, const void *x, co
 int flstm_engine_backward(flstm_engine *engine, size_t seq_len, const void *dy, const void *d_hn,
                           const void *d_cn, void *dx, float *dh0, float *dc0, void *stream);
 
+/* The same work split into step ranges, so that a caller can overlap its own transfers with the
+ * ranges already enqueued (what the reference's 32-step chunk pipeline does with pinned host
+ * tensors, flashlstm_v2/src/lstm_forward.cu:673-940, lstm_backward.cu:899-1213).  x / y / dy / dx
+ * are the base pointers of the WHOLE (T,B,.) tensors.  Forward ranges [t0,t1) must be contiguous and
+ * ascending from 0; h_n / c_n are written by the range that ends at seq_len.  Backward ranges must
+ * be contiguous and descending from seq_len; dX of a range is complete when the range's work is;
+ * weight / bias gradients (and their allreduce), dh0 and dc0 are produced by the range with t0 == 0. */
+int flstm_engine_forward_range(flstm_engine *engine, size_t seq_len, size_t t0, size_t t1, const void *x, const void *h0,
+                               const void *c0, void *y, void *h_n, void *c_n, void *stream);
+int flstm_engine_backward_range(flstm_engine *engine, size_t seq_len, size_t t0, size_t t1, const void *dy,
+                                const void *d_hn, const void *d_cn, void *dx, float *dh0, float *dc0, void *stream);
+
 /* Device pointers into the flat gradient buffer of one layer: dW_ih (4H,I_l), dW_hh (4H,H),
  * db (4H) (db_ih == db_hh == db, as in flashlstm_v2/src/lstm_backward.cu:1218-1231). */
 int flstm_engine_grad_ptrs(flstm_engine *engine, int layer, float **dw_ih, float **dw_hh, float **db);

@@ -174,3 +174,72 @@ def test_whole_step_in_a_cuda_graph(dtype, L, H):
     torch.cuda.synchronize()
     assert torch.equal(y, y1)
     eng.close()
+
+
+@pytest.mark.parametrize("dtype,L,H,backend", [("f16", 1, 128, "tc"), ("bf16", 2, 64, "tc"), ("f32", 2, 24, "simt"),
+                                               ("f16", 1, 1024, "tc")])
+def test_step_ranges_equal_one_call(dtype, L, H, backend):
+    """A sequence run as ascending forward ranges and descending backward ranges gives bit-identical
+    results to the single forward / backward calls (the ranges are what host streaming pipelines)."""
+    from flashlstm_poc_b200.engine import TORCH_DTYPES, Engine
+
+    dev = torch.device("cuda", 0)
+    td = TORCH_DTYPES[dtype]
+    T, B, I = 23, 16, 64
+    w = Workload("r", dtype, L, I, H, B, T, seed=41, state_std=0.2)
+    inp = make_inputs(w)
+    torch.manual_seed(3)
+    dhn = torch.randn(L, B, H).to(td).to(dev)
+    dcn = torch.randn(L, B, H).to(td).to(dev)
+
+    def run(cuts):
+        eng = Engine(dtype, L, B, I, H, T, device=dev, backend=backend)
+        for l in range(L):
+            eng.set_weights(l, inp.w_ih[l].to(dev), inp.w_hh[l].to(dev), inp.b_ih[l].to(dev), inp.b_hh[l].to(dev))
+        x, dy = inp.x.to(dev, td), inp.dy.to(dev, td)
+        h0, c0 = inp.h0.to(dev, td), inp.c0.to(dev, td)
+        y = torch.zeros(T, B, H, dtype=td, device=dev)
+        hn, cn = torch.zeros(L, B, H, dtype=td, device=dev), torch.zeros(L, B, H, dtype=td, device=dev)
+        dx = torch.zeros(T, B, I, dtype=td, device=dev)
+        dh0, dc0 = torch.zeros(L, B, H, device=dev), torch.zeros(L, B, H, device=dev)
+        edges = [0] + cuts + [T]
+        for a, b in zip(edges[:-1], edges[1:]):
+            eng.forward_range_into(T, a, b, x, h0, c0, y, hn, cn)
+        for a, b in reversed(list(zip(edges[:-1], edges[1:]))):
+            eng.backward_range_into(T, a, b, dy, dhn, dcn, dx, dh0, dc0)
+        torch.cuda.synchronize()
+        out = [y, hn, cn, dx, dh0, dc0] + [g.clone() for l in range(L) for g in eng.grads(l)]
+        out = [o.clone() for o in out]
+        eng.close()
+        return out
+
+    whole = run([])
+    for cuts in ([8, 16], [1, 2, 22], [11]):
+        parts = run(cuts)
+        for a, b in zip(whole, parts):
+            assert torch.equal(a, b), cuts
+    ref = run_oracle(inp, dhn.float().cpu(), dcn.float().cpu())
+    got = {"y": whole[0].float().cpu().numpy(), "dx": whole[3].float().cpu().numpy(), "dh0": whole[4].cpu().numpy()}
+    assert_parity(got, ref, dtype, keys=["y", "dx", "dh0"])
+
+
+def test_step_ranges_must_be_in_order():
+    from flashlstm_poc_b200._lib import FlashLstmError
+    from flashlstm_poc_b200.engine import Engine
+
+    dev = torch.device("cuda", 0)
+    w = Workload("r", "f16", 1, 64, 64, 8, 8, seed=1)
+    inp = make_inputs(w)
+    eng = Engine("f16", 1, 8, 64, 64, 8, device=dev)
+    eng.set_weights(0, inp.w_ih[0].to(dev), inp.w_hh[0].to(dev), inp.b_ih[0].to(dev), inp.b_hh[0].to(dev))
+    x = inp.x.to(dev, torch.float16)
+    y = torch.empty(8, 8, 64, dtype=torch.float16, device=dev)
+    eng.forward_range_into(8, 0, 4, x, None, None, y, None, None)
+    with pytest.raises(FlashLstmError, match="contiguous"):
+        eng.forward_range_into(8, 5, 8, x, None, None, y, None, None)
+    with pytest.raises(FlashLstmError, match="does not follow"):
+        eng.backward_range_into(8, 4, 8, y, None, None, None, None, None)  # the forward is not complete yet
+    eng.forward_range_into(8, 4, 8, x, None, None, y, None, None)
+    with pytest.raises(FlashLstmError, match="descending"):
+        eng.backward_range_into(8, 0, 4, y, None, None, None, None, None)
+    eng.close()
