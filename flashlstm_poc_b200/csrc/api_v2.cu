@@ -7,8 +7,12 @@
 //
 // Behind the boundary the design differs on purpose:
 //  * the sequence is device resident (the largest benchmark configuration's activations fit
-//    HBM many times over); host tensors are moved with one asynchronous copy each on the
-//    h2d / d2h streams, ordered against the compute stream with events;
+//    HBM many times over); host tensors move in chunks of whole time steps (about eight per
+//    sequence) on the h2d / d2h streams, ordered against the compute stream with per-chunk events,
+//    so that x / dY of the next chunk and y / checkpoints / dx of the previous chunk are in flight
+//    while the projection GEMM and the persistent recurrence of the current chunk run (the role of
+//    the reference's double-buffered 32-step chunk pipeline, lstm_forward.cu:673-940,
+//    lstm_backward.cu:899-1213);
 //  * a context per (device, B, I, H) owns the engine and the staging buffers, so a call
 //    allocates nothing once the context exists (the reference cudaMallocs ~25 buffers and
 //    registers the host tensors on every call, lstm_forward.cu:525-645);
@@ -17,10 +21,12 @@
 //    rebuilt by running the forward recurrence again from x, h0, c0.  The cell state is never
 //    reconstructed from y and o (the reference does, lstm_backward.cu:188-197).
 #include <cstdio>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <stdexcept>
 #include <tuple>
+#include <vector>
 
 #include "common.cuh"
 #include "engine.h"
@@ -37,6 +43,7 @@ struct V2Context {
     void *x = nullptr, *y = nullptr, *dy = nullptr, *dx = nullptr;  // fp16 (T,B,.)
     void *chk_h = nullptr, *chk_c = nullptr;                        // up to fp32 (T,B,H)
     cudaEvent_t ev_in = nullptr, ev_compute = nullptr;
+    std::vector<cudaEvent_t> ev_pool;  // per-chunk "input landed" / "compute done" events of the pipeline
     // identity of the forward whose cache the engine holds
     const void *fwd_y = nullptr;
     size_t fwd_T = 0;
@@ -47,6 +54,17 @@ struct V2Context {
         release();
         if (ev_in) cudaEventDestroy(ev_in);
         if (ev_compute) cudaEventDestroy(ev_compute);
+        for (auto e : ev_pool) cudaEventDestroy(e);
+    }
+    int event(size_t i, cudaEvent_t *out) {
+        while (ev_pool.size() <= i) {
+            cudaEvent_t e;
+            if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess)
+                return set_error(FLSTM_ERR_CUDA, "event creation failed");
+            ev_pool.push_back(e);
+        }
+        *out = ev_pool[i];
+        return FLSTM_OK;
     }
     void release() {
         for (void **p : {&x, &y, &dy, &dx, &chk_h, &chk_c}) {
@@ -113,6 +131,19 @@ int get_context(size_t T, size_t B, size_t I, size_t H, V2Context **out) {
     return FLSTM_OK;
 }
 
+// Host tensors move in chunks of whole time steps so that copies overlap the recurrence: about eight
+// chunks per sequence, at least 16 steps each (the reference uses fixed 32-step chunks,
+// flashlstm_v2/src/lstm_forward.cu:515).  FLSTM_STREAM_CHUNK overrides the number of steps.
+size_t chunk_steps(size_t T) {
+    if (const char *env = std::getenv("FLSTM_STREAM_CHUNK")) {
+        const long v = std::atol(env);
+        if (v > 0) return (size_t)v < T ? (size_t)v : T;
+    }
+    size_t n = (T + 7) / 8;
+    if (n < 16) n = 16;
+    return n < T ? n : T;
+}
+
 bool is_device_pointer(const void *p) {
     cudaPointerAttributes a{};
     if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
@@ -147,32 +178,70 @@ int forward_impl(size_t T, size_t B, size_t I, size_t H, size_t R, const __half 
     FLSTM_TRY(get_context(T, B, I, H, &c));
     c->cache_valid = false;
     const size_t slab = B * H;
-    const void *x_dev = nullptr;
-    FLSTM_TRY(stage_in(x_host, c->x, T * B * I * 2, sh, &x_dev));
-    FLSTM_CUDA_TRY(cudaEventRecord(c->ev_in, sh));
-    FLSTM_TRY(flstm_engine_set_weights(c->engine, 0, w_ih, w_hh, b_ih, b_hh, sc));
-    FLSTM_CUDA_TRY(cudaStreamWaitEvent(sc, c->ev_in, 0));
-    const bool y_on_device = is_device_pointer(y_host);
+    const bool x_on_device = is_device_pointer(x_host), y_on_device = is_device_pointer(y_host);
+    const void *x_dev = x_on_device ? (const void *)x_host : c->x;
     void *y_dev = y_on_device ? (void *)y_host : c->y;
-    FLSTM_TRY(flstm_engine_forward(c->engine, T, x_dev, h0, c0, y_dev, hy, cy, sc));
-    // checkpoints: entry k = state entering step k*R (entry 0 = h0 / c0)
     const size_t nchk = (T + R - 1) / R;
-    void *hs = nullptr;
-    float *cs = nullptr;
-    FLSTM_TRY(flstm_engine_cache_ptrs(c->engine, 0, nullptr, &cs, &hs, nullptr));
     const int hd = opt.h_dtype == FLSTM_GATE_CACHE_FLOAT16 ? FLSTM_DTYPE_F16 : FLSTM_DTYPE_F32;
     const int cd = opt.c_dtype == FLSTM_GATE_CACHE_FLOAT16 ? FLSTM_DTYPE_F16 : FLSTM_DTYPE_F32;
     const bool ch_dev = cache.h_ptr && is_device_pointer(cache.h_ptr);
     const bool cc_dev = cache.c_ptr && is_device_pointer(cache.c_ptr);
-    if (cache.h_ptr) FLSTM_TRY(simt::gather_slabs(FLSTM_DTYPE_F16, hs, slab, R, nchk, hd, ch_dev ? cache.h_ptr : c->chk_h, sc));
-    if (cache.c_ptr) FLSTM_TRY(simt::gather_slabs(FLSTM_DTYPE_F32, cs, slab, R, nchk, cd, cc_dev ? cache.c_ptr : c->chk_c, sc));
-    FLSTM_CUDA_TRY(cudaEventRecord(c->ev_compute, sc));
-    FLSTM_CUDA_TRY(cudaStreamWaitEvent(sd, c->ev_compute, 0));
-    if (!y_on_device) FLSTM_CUDA_TRY(cudaMemcpyAsync(y_host, c->y, T * slab * 2, cudaMemcpyDeviceToHost, sd));
-    if (cache.h_ptr && !ch_dev)
-        FLSTM_CUDA_TRY(cudaMemcpyAsync(cache.h_ptr, c->chk_h, nchk * slab * dtype_size(hd), cudaMemcpyDeviceToHost, sd));
-    if (cache.c_ptr && !cc_dev)
-        FLSTM_CUDA_TRY(cudaMemcpyAsync(cache.c_ptr, c->chk_c, nchk * slab * dtype_size(cd), cudaMemcpyDeviceToHost, sd));
+    char *chk_h_dev = static_cast<char *>(ch_dev ? cache.h_ptr : c->chk_h);
+    char *chk_c_dev = static_cast<char *>(cc_dev ? cache.c_ptr : c->chk_c);
+    void *hs = nullptr;
+    float *cs = nullptr;
+    FLSTM_TRY(flstm_engine_cache_ptrs(c->engine, 0, nullptr, &cs, &hs, nullptr));
+    FLSTM_TRY(flstm_engine_set_weights(c->engine, 0, w_ih, w_hh, b_ih, b_hh, sc));
+
+    // Chunk pipeline over the caller's three streams: x chunk k+1 travels host->device while chunk k
+    // runs (projection GEMM + persistent recurrence over the chunk's steps), and y / checkpoint rows
+    // of chunk k travel device->host while chunk k+1 runs.
+    const size_t cs_steps = chunk_steps(T), nchunks = (T + cs_steps - 1) / cs_steps;
+    if (!x_on_device) {
+        for (size_t k = 0; k < nchunks; ++k) {
+            const size_t t0 = k * cs_steps, t1 = (t0 + cs_steps < T) ? t0 + cs_steps : T;
+            FLSTM_CUDA_TRY(cudaMemcpyAsync(static_cast<char *>(c->x) + t0 * B * I * 2,
+                                           reinterpret_cast<const char *>(x_host) + t0 * B * I * 2, (t1 - t0) * B * I * 2,
+                                           cudaMemcpyHostToDevice, sh));
+            cudaEvent_t ev;
+            FLSTM_TRY(c->event(2 * k, &ev));
+            FLSTM_CUDA_TRY(cudaEventRecord(ev, sh));
+        }
+    }
+    for (size_t k = 0; k < nchunks; ++k) {
+        const size_t t0 = k * cs_steps, t1 = (t0 + cs_steps < T) ? t0 + cs_steps : T;
+        cudaEvent_t ev_x, ev_done;
+        FLSTM_TRY(c->event(2 * k, &ev_x));
+        FLSTM_TRY(c->event(2 * k + 1, &ev_done));
+        if (!x_on_device) FLSTM_CUDA_TRY(cudaStreamWaitEvent(sc, ev_x, 0));
+        FLSTM_TRY(flstm_engine_forward_range(c->engine, T, t0, t1, x_dev, h0, c0, y_dev, hy, cy, sc));
+        // checkpoints: entry e = state entering step e*R (entry 0 = h0 / c0); this chunk owns the
+        // entries whose step lies in [t0, t1)
+        const size_t e0 = (t0 + R - 1) / R, e1 = (t1 + R - 1) / R < nchk ? (t1 + R - 1) / R : nchk;
+        if (e1 > e0) {
+            if (cache.h_ptr)
+                FLSTM_TRY(simt::gather_slabs(FLSTM_DTYPE_F16, static_cast<char *>(hs) + e0 * R * slab * 2, slab, R, e1 - e0, hd,
+                                             chk_h_dev + e0 * slab * dtype_size(hd), sc));
+            if (cache.c_ptr)
+                FLSTM_TRY(simt::gather_slabs(FLSTM_DTYPE_F32, cs + e0 * R * slab, slab, R, e1 - e0, cd,
+                                             chk_c_dev + e0 * slab * dtype_size(cd), sc));
+        }
+        FLSTM_CUDA_TRY(cudaEventRecord(ev_done, sc));
+        FLSTM_CUDA_TRY(cudaStreamWaitEvent(sd, ev_done, 0));
+        if (!y_on_device)
+            FLSTM_CUDA_TRY(cudaMemcpyAsync(reinterpret_cast<char *>(y_host) + t0 * slab * 2, static_cast<char *>(c->y) + t0 * slab * 2,
+                                           (t1 - t0) * slab * 2, cudaMemcpyDeviceToHost, sd));
+        if (e1 > e0) {
+            if (cache.h_ptr && !ch_dev)
+                FLSTM_CUDA_TRY(cudaMemcpyAsync(static_cast<char *>(cache.h_ptr) + e0 * slab * dtype_size(hd),
+                                               chk_h_dev + e0 * slab * dtype_size(hd), (e1 - e0) * slab * dtype_size(hd),
+                                               cudaMemcpyDeviceToHost, sd));
+            if (cache.c_ptr && !cc_dev)
+                FLSTM_CUDA_TRY(cudaMemcpyAsync(static_cast<char *>(cache.c_ptr) + e0 * slab * dtype_size(cd),
+                                               chk_c_dev + e0 * slab * dtype_size(cd), (e1 - e0) * slab * dtype_size(cd),
+                                               cudaMemcpyDeviceToHost, sd));
+        }
+    }
     FLSTM_CUDA_TRY(cudaStreamSynchronize(sh));
     FLSTM_CUDA_TRY(cudaStreamSynchronize(sc));
     FLSTM_CUDA_TRY(cudaStreamSynchronize(sd));
@@ -200,31 +269,60 @@ int backward_impl(size_t T, size_t B, size_t I, size_t H, size_t R, const __half
     V2Context *c = nullptr;
     FLSTM_TRY(get_context(T, B, I, H, &c));
     const size_t slab = B * H;
-    const void *x_dev = nullptr, *dy_dev = nullptr;
     const bool have_cache = c->cache_valid && c->fwd_y == y_host && c->fwd_T == T;
-    // with a live cache the forward's device copy of x is still in place and is reused
-    if (!have_cache) FLSTM_TRY(stage_in(x_host, c->x, T * B * I * 2, sh, &x_dev));
-    FLSTM_TRY(stage_in(dy_host, c->dy, T * slab * 2, sh, &dy_dev));
-    FLSTM_CUDA_TRY(cudaEventRecord(c->ev_in, sh));
-    FLSTM_CUDA_TRY(cudaStreamWaitEvent(sc, c->ev_in, 0));
+    const bool dy_on_device = is_device_pointer(dy_host), dx_on_device = is_device_pointer(dx_host);
+    const void *dy_dev = dy_on_device ? (const void *)dy_host : c->dy;
+    void *dx_dev = dx_on_device ? (void *)dx_host : c->dx;
+    const size_t cs_steps = chunk_steps(T), nchunks = (T + cs_steps - 1) / cs_steps;
+    // dY chunks travel host->device in the order the reverse recurrence consumes them: last chunk first
+    if (!dy_on_device) {
+        for (size_t r = 0; r < nchunks; ++r) {
+            const size_t k = nchunks - 1 - r;
+            const size_t t0 = k * cs_steps, t1 = (t0 + cs_steps < T) ? t0 + cs_steps : T;
+            FLSTM_CUDA_TRY(cudaMemcpyAsync(static_cast<char *>(c->dy) + t0 * slab * 2,
+                                           reinterpret_cast<const char *>(dy_host) + t0 * slab * 2, (t1 - t0) * slab * 2,
+                                           cudaMemcpyHostToDevice, sh));
+            cudaEvent_t ev;
+            FLSTM_TRY(c->event(2 * k, &ev));
+            FLSTM_CUDA_TRY(cudaEventRecord(ev, sh));
+        }
+    }
     if (!have_cache) {
-        // stateless call: rebuild the gate cache by running the recurrence again
+        // stateless call (another forward ran in between, or none did): rebuild the gate cache by
+        // running the recurrence again from x, h0, c0.  With a live cache the forward's device copy
+        // of x is still in place and nothing is recomputed.
         if (!c0) return set_error(FLSTM_ERR_INVALID, "c0 is null");
+        const void *x_dev = nullptr;
+        FLSTM_TRY(stage_in(x_host, c->x, T * B * I * 2, sh, &x_dev));
+        FLSTM_CUDA_TRY(cudaEventRecord(c->ev_in, sh));
+        FLSTM_CUDA_TRY(cudaStreamWaitEvent(sc, c->ev_in, 0));
         FLSTM_TRY(flstm_engine_set_weights(c->engine, 0, w_ih, w_hh, b_ih, b_hh, sc));
         FLSTM_TRY(flstm_engine_forward(c->engine, T, x_dev, h0, c0, nullptr, nullptr, nullptr, sc));
     }
-    const bool dx_on_device = is_device_pointer(dx_host);
-    void *dx_dev = dx_on_device ? (void *)dx_host : c->dx;
-    FLSTM_TRY(flstm_engine_backward(c->engine, T, dy_dev, d_hn, d_cn, dx_dev, dh0, dc0, sc));
+    // reverse chunk pipeline: BPTT + dX GEMM of chunk k run while dY of chunk k-1 arrives and dX of
+    // chunk k+1 leaves; the weight / bias gradients are formed over the whole sequence by the last chunk
+    for (size_t r = 0; r < nchunks; ++r) {
+        const size_t k = nchunks - 1 - r;
+        const size_t t0 = k * cs_steps, t1 = (t0 + cs_steps < T) ? t0 + cs_steps : T;
+        cudaEvent_t ev_dy, ev_done;
+        FLSTM_TRY(c->event(2 * k, &ev_dy));
+        FLSTM_TRY(c->event(2 * k + 1, &ev_done));
+        if (!dy_on_device) FLSTM_CUDA_TRY(cudaStreamWaitEvent(sc, ev_dy, 0));
+        FLSTM_TRY(flstm_engine_backward_range(c->engine, T, t0, t1, dy_dev, d_hn, d_cn, dx_dev, dh0, dc0, sc));
+        FLSTM_CUDA_TRY(cudaEventRecord(ev_done, sc));
+        if (!dx_on_device) {
+            FLSTM_CUDA_TRY(cudaStreamWaitEvent(sd, ev_done, 0));
+            FLSTM_CUDA_TRY(cudaMemcpyAsync(reinterpret_cast<char *>(dx_host) + t0 * B * I * 2,
+                                           static_cast<char *>(c->dx) + t0 * B * I * 2, (t1 - t0) * B * I * 2,
+                                           cudaMemcpyDeviceToHost, sd));
+        }
+    }
     float *g_ih = nullptr, *g_hh = nullptr, *g_b = nullptr;
     FLSTM_TRY(flstm_engine_grad_ptrs(c->engine, 0, &g_ih, &g_hh, &g_b));
     FLSTM_CUDA_TRY(cudaMemcpyAsync(dw_ih, g_ih, 4 * H * I * sizeof(float), cudaMemcpyDeviceToDevice, sc));
     FLSTM_CUDA_TRY(cudaMemcpyAsync(dw_hh, g_hh, 4 * H * H * sizeof(float), cudaMemcpyDeviceToDevice, sc));
     FLSTM_CUDA_TRY(cudaMemcpyAsync(db_ih, g_b, 4 * H * sizeof(float), cudaMemcpyDeviceToDevice, sc));
     FLSTM_CUDA_TRY(cudaMemcpyAsync(db_hh, g_b, 4 * H * sizeof(float), cudaMemcpyDeviceToDevice, sc));
-    FLSTM_CUDA_TRY(cudaEventRecord(c->ev_compute, sc));
-    FLSTM_CUDA_TRY(cudaStreamWaitEvent(sd, c->ev_compute, 0));
-    if (!dx_on_device) FLSTM_CUDA_TRY(cudaMemcpyAsync(dx_host, c->dx, T * B * I * 2, cudaMemcpyDeviceToHost, sd));
     FLSTM_CUDA_TRY(cudaStreamSynchronize(sh));
     FLSTM_CUDA_TRY(cudaStreamSynchronize(sc));
     FLSTM_CUDA_TRY(cudaStreamSynchronize(sd));
