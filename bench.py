@@ -52,6 +52,7 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying one captured CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cudnn", action="store_true")
     return ap.parse_args()
 
 
@@ -344,6 +345,16 @@ def main():
     if not args.no_e2e and w.layers == 1 and w.dtype == "f16" and w.training:
         e2e = run_e2e(args, w, inp, base, dev, world, rank)
 
+    # on-GPU comparison: cuDNN through torch.nn.LSTM in the config's dtype (what the reference's own
+    # benchmark compares itself with, python/benchmark_lstm.py:304-328); test/baseline code only
+    cudnn = None
+    if rank == 0 and world == 1 and not args.no_cudnn:
+        try:
+            cudnn = cudnn_tokens_per_sec(w, base, inp, dev, td)
+        except Exception as exc:
+            cudnn = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+    extra["cudnn_torch_nn_lstm"] = cudnn
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cores = os.cpu_count() or 1
@@ -373,6 +384,48 @@ def main():
         dist.barrier()
         dist.destroy_process_group()
     return 0
+
+
+def cudnn_tokens_per_sec(w, base, inp, dev, td, iters=5):
+    """torch.nn.LSTM on the same device (cuDNN), same weights / inputs / dtype, forward + backward."""
+    import torch
+
+    m = torch.nn.LSTM(w.input_size, w.hidden_size, num_layers=w.layers).to(dev, td)
+    with torch.no_grad():
+        for l in range(w.layers):
+            getattr(m, f"weight_ih_l{l}").copy_(base.w_ih[l])
+            getattr(m, f"weight_hh_l{l}").copy_(base.w_hh[l])
+            getattr(m, f"bias_ih_l{l}").copy_(base.b_ih[l])
+            getattr(m, f"bias_hh_l{l}").copy_(base.b_hh[l])
+    x = inp.x.to(dev, td).requires_grad_(w.training)
+    L, B, H = w.layers, w.batch, w.hidden_size
+    h0 = (torch.zeros(L, B, H) if inp.h0 is None else inp.h0).to(dev, td)
+    c0 = (torch.zeros(L, B, H) if inp.c0 is None else inp.c0).to(dev, td)
+    dy = inp.dy.to(dev, td) if w.training else None
+
+    def step():
+        if w.training:
+            m.zero_grad(set_to_none=True)
+            x.grad = None
+            y, _ = m(x, (h0, c0))
+            y.backward(dy)
+        else:
+            with torch.no_grad():
+                m(x, (h0, c0))
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    return {"value": w.batch * w.seq_len / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms,
+            "note": "torch.nn.LSTM (cuDNN) on the same GPU, same dtype, fwd+bwd" if w.training else
+                    "torch.nn.LSTM (cuDNN) on the same GPU, same dtype, forward only"}
 
 
 def run_e2e(args, w, inp, base, dev, world, rank):

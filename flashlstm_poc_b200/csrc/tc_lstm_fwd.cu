@@ -421,8 +421,12 @@ int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan) {
     const int kc = H / 64;
     // measured on config 2: one 64 KB copy per step beats 2, 4, 8 or 16 smaller ones (TMA issue cost
     // outweighs the longer exposed UMMA tail), so a stage takes up to 16 chunks
-    int ch = 16;
-    if (const char *env = std::getenv("FLSTM_CH")) ch = std::atoi(env) > 0 ? std::atoi(env) : 16;
+    // (measured: the streamed-weight and multi-tile regimes need several smaller stages in flight instead)
+    int ch16 = 16;
+    while (kc % ch16) --ch16;
+    const bool one_tile_resident = nt == 1 && (size_t)fwd_smem_layout(BT, H, rt, true, kc / ch16, ch16).total <= smem_limit;
+    int ch = one_tile_resident ? 16 : 4;
+    if (const char *env = std::getenv("FLSTM_CH")) ch = std::atoi(env) > 0 ? std::atoi(env) : ch;
     while (kc % ch) --ch;
     bool resident = true;
     int stages = kc / ch;
