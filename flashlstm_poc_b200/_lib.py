@@ -16,7 +16,7 @@ ENGINE_SYMBOLS = [
     "flstm_engine_backward", "flstm_engine_forward_range", "flstm_engine_backward_range", "flstm_engine_grad_ptrs", "flstm_engine_grad_buffer", "flstm_engine_cache_ptrs",
     "flstm_engine_set_cell_io_f32", "flstm_engine_backend", "flstm_comm_unique_id", "flstm_engine_attach_comm",
     "flstm_engine_enable_timing", "flstm_engine_phase_ms", "flstm_engine_launch_count", "flstm_tc_gemm",
-    "flstm_engine_enable_trace", "flstm_engine_read_trace", "flstm_bias_grad",
+    "flstm_engine_enable_trace", "flstm_engine_read_trace", "flstm_bias_grad", "flstm_tc_plan",
     "flstm_bias_grad_static",
     "flstm_last_error",
     "flstm_version",
@@ -37,6 +37,15 @@ class EngineConfig(ctypes.Structure):
         ("input_size", ctypes.c_size_t), ("hidden_size", ctypes.c_size_t), ("max_seq_len", ctypes.c_size_t),
         ("training", ctypes.c_int), ("backend", ctypes.c_int),
     ]
+
+
+class TcPlanInfo(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in (
+        "fwd_batch_tile", "fwd_row_tiles_per_cta", "fwd_grid", "fwd_batch_groups", "fwd_tiles_per_group",
+        "fwd_stages", "fwd_chunks_per_stage", "fwd_weights_resident", "fwd_smem_bytes",
+        "bwd_batch_tile", "bwd_cluster_size", "bwd_grid", "bwd_batch_groups", "bwd_tiles_per_group",
+        "bwd_stages", "bwd_chunks_per_stage", "bwd_weights_resident", "bwd_smem_bytes",
+        "step_path", "step_bn_fwd", "step_bn_bwd", "step_splits")]
 
 
 class LstmBuffers(ctypes.Structure):
@@ -92,6 +101,7 @@ def load() -> ctypes.CDLL:
     lib.flstm_engine_launch_count.restype = ctypes.c_ulonglong
     lib.flstm_engine_enable_trace.argtypes = [vp, ci]
     lib.flstm_engine_read_trace.argtypes = [vp, vp, sz]
+    lib.flstm_tc_plan.argtypes = [sz, sz, ci, ci, sz, ctypes.POINTER(TcPlanInfo)]
     lib.flstm_bias_grad.argtypes = [ci, vp, sz, sz, ci, vp, vp]
     lib.flstm_bias_grad_static.argtypes = [ci, vp, sz, sz, ci, vp, vp]
     lib.flstm_tc_gemm.argtypes = [ci, ci, sz, sz, sz, vp, vp, vp, sz, vp, ci, vp]

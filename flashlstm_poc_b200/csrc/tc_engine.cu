@@ -25,6 +25,10 @@ struct TcLayer {
     CUtensorMap tm_h;   // hs (Tcap+1, B, H), 1 x BT x 64 boxes, 128B swizzle
     CUtensorMap tm_g;   // gates (Tcap, B, 4H), 1 x BT x 64 boxes, no swizzle
     CUtensorMap tm_dg;  // dG (Tcap, B, 4H), 1 x BT x 64 boxes, 128B swizzle (BPTT operand)
+    // wide-batch path (one GEMM launch per step)
+    CUtensorMap tm_hs3;    // hs (Tcap+1, B, H), 1 x 128 x 64 boxes, 128B swizzle
+    CUtensorMap tm_wstep;  // w_hh (4H, H), bn_fwd x 64 boxes, 128B swizzle
+    CUtensorMap tm_dg3;    // dG (Tcap, B, 4H), 1 x 128 x 64 boxes, 128B swizzle
 };
 
 struct TcState {
@@ -33,6 +37,8 @@ struct TcState {
     FwdPlan fwd{};
     BwdPlan bwd{};
     bool bwd_ok = false;
+    StepPlan step{};
+    float *dh_parts = nullptr;  // wide-batch path: fp32 (L, splits, B, H) partial sums of dG_t W_hh
     std::vector<TcLayer> layers;
     unsigned int *err_host = nullptr;  // pinned mirror of the device error word
 };
@@ -107,6 +113,8 @@ bool supported(const flstm_engine_config &cfg) {
     if (cudaGetDevice(&dev) != cudaSuccess) return false;
     cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
     if (major != 10) return false;
+    StepPlan sp;
+    if (plan_step((int)cfg.batch, (int)cfg.hidden_size, device_sm_count(), &sp) == FLSTM_OK && sp.use) return true;
     FwdPlan fp;
     int optin = 0;
     cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
@@ -125,13 +133,23 @@ int init(Engine &e) {
     int optin = 0;
     FLSTM_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, e.device));
     st->smem_limit = (size_t)optin;
-    FLSTM_TRY(plan_fwd((int)e.cfg.batch, (int)e.cfg.hidden_size, st->sms, st->smem_limit, &st->fwd));
-    if (e.cfg.training) {
-        FLSTM_TRY(plan_bwd((int)e.cfg.batch, (int)e.cfg.hidden_size, st->sms, st->smem_limit, &st->bwd));
-        st->bwd_ok = true;
+    FLSTM_TRY(plan_step((int)e.cfg.batch, (int)e.cfg.hidden_size, st->sms, &st->step));
+    void *raw = nullptr;
+    if (st->step.use) {
+        st->bwd_ok = e.cfg.training != 0;
+        if (e.cfg.training) {
+            const size_t n = e.layers.size() * (size_t)st->step.splits * e.cfg.batch * e.cfg.hidden_size;
+            FLSTM_CUDA_TRY(cudaMalloc(&raw, n * sizeof(float)));
+            st->dh_parts = static_cast<float *>(raw);
+        }
+    } else {
+        FLSTM_TRY(plan_fwd((int)e.cfg.batch, (int)e.cfg.hidden_size, st->sms, st->smem_limit, &st->fwd));
+        if (e.cfg.training) {
+            FLSTM_TRY(plan_bwd((int)e.cfg.batch, (int)e.cfg.hidden_size, st->sms, st->smem_limit, &st->bwd));
+            st->bwd_ok = true;
+        }
     }
     st->layers.resize(e.layers.size());
-    void *raw = nullptr;
     FLSTM_CUDA_TRY(cudaMalloc(&raw, 1024 * sizeof(unsigned int)));
     e.sync_words = static_cast<unsigned int *>(raw);
     FLSTM_CUDA_TRY(cudaMemset(raw, 0, 1024 * sizeof(unsigned int)));
@@ -147,6 +165,7 @@ void destroy(Engine &e) {
     TcState *st = state(e);
     if (!st) return;
     if (st->err_host) cudaFreeHost(st->err_host);
+    if (st->dh_parts) cudaFree(st->dh_parts);
     delete st;
     e.tc_state = nullptr;
 }
@@ -158,6 +177,13 @@ int on_capacity_change(Engine &e) {
         auto &l = e.layers[li];
         auto &t = st->layers[li];
         FLSTM_TRY(make_tensor_map_2d(&t.tm_w, l.w_hh, 4 * H, H, H, 64, 64, true));
+        if (st->step.use) {
+            FLSTM_TRY(make_tensor_map_3d(&t.tm_hs3, l.hs, cap + 1, B, H, H, B * H, 128, 64, true));
+            FLSTM_TRY(make_tensor_map_2d(&t.tm_wstep, l.w_hh, 4 * H, H, H, st->step.bn_fwd, 64, true));
+            if (e.cfg.training && l.dg)
+                FLSTM_TRY(make_tensor_map_3d(&t.tm_dg3, l.dg, cap, B, 4 * H, 4 * H, B * 4 * H, 128, 64, true));
+            continue;
+        }
         FLSTM_TRY(make_tensor_map_chunked(&t.tm_h, l.hs, cap + 1, B, H, st->fwd.BT, st->fwd.ch));
         FLSTM_TRY(make_tensor_map_3d(&t.tm_g, l.gates, cap, B, 4 * H, 4 * H, B * 4 * H, st->fwd.BT, 64, false));
         if (e.cfg.training && l.dg)
@@ -203,6 +229,29 @@ int forward_layer(Engine &e, int li, size_t t0, size_t t1, const void *x_l, void
     FLSTM_TRY(gemm(e.cfg.dtype, e.cfg.dtype, n * B, 4 * H, l.in_size, byte_ptr(x_l) + t0 * B * l.in_size * es, l.in_size, false,
                    l.w_ih, l.in_size, false, byte_ptr(l.gates) + t0 * B * 4 * H * es, 4 * H, l.bias, 0, err, st->sms, s));
     size_t m1 = e.timer.mark(s);
+    if (st->step.use) {
+        const size_t slab = B * H;
+        for (size_t step = t0; step < t1; ++step) {
+            StepFwdParams sp{};
+            sp.gates_t = byte_ptr(l.gates) + step * B * 4 * H * es;
+            sp.c_prev = l.cs + step * slab;
+            sp.c_out = l.cs + (step + 1) * slab;
+            sp.h_out = byte_ptr(l.hs) + (step + 1) * slab * es;
+            sp.y_out = y_out ? byte_ptr(y_out) + step * slab * es : nullptr;
+            sp.err = err;
+            sp.t = (int)step;
+            sp.B = (int)B;
+            sp.H = (int)H;
+            sp.store_gates = e.cfg.training ? 1 : 0;
+            FLSTM_TRY(lstm_step_forward(e.cfg.dtype, st->step, t.tm_hs3, t.tm_wstep, sp, st->sms, s));
+        }
+        size_t m2 = e.timer.mark(s);
+        e.timer.span(PH_PROJ, m0, m1);
+        e.timer.span(PH_RECUR_FWD, m1, m2);
+        e.launches += 1 + n;
+        FLSTM_CUDA_TRY(cudaMemcpyAsync(st->err_host, err, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
+        return FLSTM_OK;
+    }
     FLSTM_CUDA_TRY(cudaMemsetAsync(e.sync_words + 1, 0, (size_t)st->fwd.ngroups * sizeof(unsigned int), s));
     FwdParams p{};
     p.cs = l.cs;
@@ -227,6 +276,43 @@ int forward_layer(Engine &e, int li, size_t t0, size_t t1, const void *x_l, void
     return FLSTM_OK;
 }
 
+// Wide-batch BPTT over the steps [t0, t1), descending: per step one pointwise kernel (dG_t, cell-gradient
+// carry) and one split-K GEMM (the fp32 partial sums of dG_t W_hh that step t-1 adds to its dy).
+static int backward_steps(Engine &e, int li, size_t T, size_t t0, size_t t1, const void *dy_l, const void *dhn_l,
+                          const void *dcn_l, float *dh0_l, float *dc0_l, cudaStream_t s) {
+    TcState *st = state(e);
+    auto &l = e.layers[li];
+    auto &t = st->layers[li];
+    const size_t B = e.cfg.batch, H = e.cfg.hidden_size, es = dtype_size(e.cfg.dtype), slab = B * H;
+    const int splits = st->step.splits;
+    float *parts = st->dh_parts + (size_t)li * splits * slab;
+    float *dc = e.dc_layers + (size_t)li * slab;
+    if (t1 == T) {
+        // gradients entering the last step: dh_n in partial buffer 0, dc_n in the carry
+        if (dhn_l) { FLSTM_TRY(simt::convert(e.cfg.dtype, dhn_l, FLSTM_DTYPE_F32, parts, slab, s)); ++e.launches; }
+        else FLSTM_CUDA_TRY(cudaMemsetAsync(parts, 0, slab * sizeof(float), s));
+        if (dcn_l) { FLSTM_TRY(simt::convert(e.cfg.dtype, dcn_l, FLSTM_DTYPE_F32, dc, slab, s)); ++e.launches; }
+        else FLSTM_CUDA_TRY(cudaMemsetAsync(dc, 0, slab * sizeof(float), s));
+    }
+    for (size_t step = t1; step-- > t0;) {
+        const int nparts = (step == T - 1) ? 1 : splits;
+        FLSTM_TRY(lstm_step_backward_pointwise(e.cfg.dtype, byte_ptr(l.gates) + step * B * 4 * H * es, l.cs + (step + 1) * slab,
+                                               l.cs + step * slab, byte_ptr(dy_l) + step * slab * es, parts, nparts, dc,
+                                               byte_ptr(l.dg) + step * B * 4 * H * es, (int)B, (int)H, s));
+        ++e.launches;
+        if (step > 0 || dh0_l) {
+            FLSTM_TRY(lstm_step_backward_gemm(e.cfg.dtype, st->step, t.tm_dg3, t.tm_w, (int)step, (int)B, (int)H, parts,
+                                              e.sync_words, st->sms, s));
+            ++e.launches;
+        }
+    }
+    if (t0 == 0) {
+        if (dh0_l) { FLSTM_TRY(sum_parts(parts, splits, slab, dh0_l, s)); ++e.launches; }
+        if (dc0_l) FLSTM_CUDA_TRY(cudaMemcpyAsync(dc0_l, dc, slab * sizeof(float), cudaMemcpyDeviceToDevice, s));
+    }
+    return FLSTM_OK;
+}
+
 int backward_layer(Engine &e, int li, size_t T, size_t t0, size_t t1, const void *x_l, const void *dy_l, const void *dhn_l,
                    const void *dcn_l, void *dx_l, float *dh0_l, float *dc0_l, cudaStream_t s) {
     TcState *st = state(e);
@@ -237,6 +323,8 @@ int backward_layer(Engine &e, int li, size_t T, size_t t0, size_t t1, const void
     const size_t B = e.cfg.batch, H = e.cfg.hidden_size, es = dtype_size(e.cfg.dtype), n = t1 - t0;
     unsigned int *err = e.sync_words;
     size_t m0 = e.timer.mark(s);
+    if (st->step.use) FLSTM_TRY(backward_steps(e, li, T, t0, t1, dy_l, dhn_l, dcn_l, dh0_l, dc0_l, s));
+    else {
     FLSTM_CUDA_TRY(cudaMemsetAsync(e.sync_words + 1, 0, (size_t)st->bwd.ngroups * sizeof(unsigned int), s));
     BwdParams p{};
     p.cs = l.cs;
@@ -258,6 +346,8 @@ int backward_layer(Engine &e, int li, size_t T, size_t t0, size_t t1, const void
     p.B = (int)B;
     p.H = (int)H;
     FLSTM_TRY(lstm_backward_persistent(e.cfg.dtype, st->bwd, t.tm_w, t.tm_dg, p, s));
+    e.launches += 1;
+    }
     size_t m1 = e.timer.mark(s), m2 = m1;
     if (t0 == 0) {
         // dW = dG^T [X | H_prev] over the whole sequence: both operands read as stored (reduction dim
@@ -281,7 +371,6 @@ int backward_layer(Engine &e, int li, size_t T, size_t t0, size_t t1, const void
     e.timer.span(PH_BPTT, m0, m1);
     e.timer.span(PH_WGRAD, m1, m2);
     e.timer.span(PH_XGRAD, m2, m3);
-    e.launches += 1;
     FLSTM_CUDA_TRY(cudaMemcpyAsync(st->err_host, err, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
     return FLSTM_OK;
 }
@@ -308,6 +397,45 @@ int device_sm_count() {
 
 }  // namespace tc
 }  // namespace flstm_b200
+
+extern "C" int flstm_tc_plan(size_t batch, size_t hidden_size, int training, int sm_count, size_t smem_limit,
+                             flstm_tc_plan_info *out) {
+    using namespace flstm_b200;
+    if (!out || sm_count < 1) return set_error(FLSTM_ERR_INVALID, "bad argument");
+    *out = flstm_tc_plan_info{};
+    tc::StepPlan sp{};
+    FLSTM_TRY(tc::plan_step((int)batch, (int)hidden_size, sm_count, &sp));
+    out->step_path = sp.use ? 1 : 0;
+    out->step_bn_fwd = sp.bn_fwd;
+    out->step_bn_bwd = sp.bn_bwd;
+    out->step_splits = sp.splits;
+    if (sp.use) return FLSTM_OK;
+    tc::FwdPlan f{};
+    FLSTM_TRY(tc::plan_fwd((int)batch, (int)hidden_size, sm_count, smem_limit, &f));
+    out->fwd_batch_tile = f.BT;
+    out->fwd_row_tiles_per_cta = f.rt;
+    out->fwd_grid = f.grid;
+    out->fwd_batch_groups = f.ngroups;
+    out->fwd_tiles_per_group = f.nt;
+    out->fwd_stages = f.stages;
+    out->fwd_chunks_per_stage = f.ch;
+    out->fwd_weights_resident = f.resident ? 1 : 0;
+    out->fwd_smem_bytes = f.smem_bytes;
+    if (training) {
+        tc::BwdPlan b{};
+        FLSTM_TRY(tc::plan_bwd((int)batch, (int)hidden_size, sm_count, smem_limit, &b));
+        out->bwd_batch_tile = b.BT;
+        out->bwd_cluster_size = b.KS;
+        out->bwd_grid = b.grid;
+        out->bwd_batch_groups = b.ngroups;
+        out->bwd_tiles_per_group = b.nt;
+        out->bwd_stages = b.stages;
+        out->bwd_chunks_per_stage = b.ch;
+        out->bwd_weights_resident = b.resident ? 1 : 0;
+        out->bwd_smem_bytes = b.smem_bytes;
+    }
+    return FLSTM_OK;
+}
 
 extern "C" int flstm_tc_gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, const void *B,
                              void *D, size_t ldd, const float *bias, int layout, void *stream) {

@@ -97,6 +97,40 @@ int plan_bwd(int B, int H, int sms, size_t smem_limit, BwdPlan *plan);
 int lstm_backward_persistent(int dtype, const BwdPlan &plan, const CUtensorMap &tm_w, const CUtensorMap &tm_dg,
                              BwdParams p, cudaStream_t s);
 
+// ------------------------------------------------------------------ wide-batch path: one GEMM launch per step
+struct StepPlan {
+    bool use;     // the engine takes this path instead of the persistent kernels
+    int bn_fwd;   // output-tile width of the forward step GEMM (gate columns): 128 or 256
+    int bn_bwd;   // output-tile width of the backward step GEMM (hidden units): 128 or 256
+    int splits;   // K = 4H splits of the backward step GEMM (fp32 partial sums, added by the pointwise kernel)
+};
+
+struct StepFwdParams {
+    void *gates_t;        // 16-bit (B,4H) at step t: projection in, activated gates out
+    const float *c_prev;  // fp32 (B,H) cell state entering the step
+    float *c_out;         // fp32 (B,H)
+    void *h_out;          // 16-bit (B,H): slot t+1 of the hidden states
+    void *y_out;          // optional 16-bit (B,H) copy for the caller
+    unsigned int *err;
+    int t;                // slot of h_{t-1} in the hidden-state tensor map (= absolute step)
+    int B, H;
+    int store_gates;
+};
+
+int plan_step(int B, int H, int sms, StepPlan *plan);
+// tm_hs: hidden states (T+1, B, H) as a 3-D map, box 1 x 128 x 64, 128B swizzle.  tm_w: W_hh rows
+// tile-interleaved (4H, H), box plan.bn_fwd x 64, 128B swizzle.
+int lstm_step_forward(int dtype, const StepPlan &plan, const CUtensorMap &tm_hs, const CUtensorMap &tm_w,
+                      const StepFwdParams &p, int sms, cudaStream_t s);
+// parts[s] (B,H) fp32 = dG_t[:, K slice s] W_hh[K slice s, :].  tm_dg: dG (T, B, 4H) as a 3-D map, box
+// 1 x 128 x 64, 128B swizzle.  tm_w64: W_hh (4H, H) with 64 x 64 boxes (read as an MN-major operand).
+int lstm_step_backward_gemm(int dtype, const StepPlan &plan, const CUtensorMap &tm_dg, const CUtensorMap &tm_w64, int t,
+                            int B, int H, float *parts, unsigned int *err, int sms, cudaStream_t s);
+// dG_t and the cell-gradient carry from dh = dy_t + sum(parts[0..nparts)), the gate cache and the cell states.
+int lstm_step_backward_pointwise(int dtype, const void *gates_t, const float *c_t, const float *c_prev, const void *dy_t,
+                                 const float *parts, int nparts, float *dc, void *dg_t, int B, int H, cudaStream_t s);
+int sum_parts(const float *parts, int nparts, size_t n, float *out, cudaStream_t s);
+
 // fp32 (4H, K) torch-ordered rows -> 16-bit tile-interleaved rows; bias likewise (b_ih + b_hh)
 int pack_weights_interleaved(int dtype, const float *w, size_t H, size_t K, void *out, cudaStream_t s);
 int pack_bias_interleaved(const float *b_ih, const float *b_hh, size_t H, float *out, cudaStream_t s);

@@ -139,6 +139,22 @@ int flstm_engine_read_trace(flstm_engine *engine, long long *out_host, size_t co
 /* Number of kernels this library launched on behalf of `engine` since creation. */
 unsigned long long flstm_engine_launch_count(const flstm_engine *engine);
 
+/* How the tensor-core backend would lay a problem out on a GPU with `sm_count` SMs and `smem_limit`
+ * bytes of opt-in shared memory per CTA (B200: 148, 232448): grids of the two persistent kernels,
+ * batch tiling, TMA ring shape, whether the W_hh slices stay resident in shared memory; or, for wide
+ * batches, the tile widths and K splits of the per-step GEMM launches.  Pure host
+ * arithmetic (needs no device); FLSTM_ERR_UNSUPPORTED when the shape cannot be tiled. */
+typedef struct {
+    int fwd_batch_tile, fwd_row_tiles_per_cta, fwd_grid, fwd_batch_groups, fwd_tiles_per_group;
+    int fwd_stages, fwd_chunks_per_stage, fwd_weights_resident, fwd_smem_bytes;
+    int bwd_batch_tile, bwd_cluster_size, bwd_grid, bwd_batch_groups, bwd_tiles_per_group;
+    int bwd_stages, bwd_chunks_per_stage, bwd_weights_resident, bwd_smem_bytes;
+    /* wide batches run one GEMM launch per time step instead (then the fields above are zero) */
+    int step_path, step_bn_fwd, step_bn_bwd, step_splits;
+} flstm_tc_plan_info;
+int flstm_tc_plan(size_t batch, size_t hidden_size, int training, int sm_count, size_t smem_limit,
+                  flstm_tc_plan_info *out);
+
 /* The dense-contraction building block of the path on the tcgen05 tensor cores, exported for
  * unit tests and profiling: D[M,N] = A B^T (+ bias[N]) with f16/bf16 operands (`dtype`) and fp32
  * accumulation; D has dtype `out_dtype` (the operand dtype or FLSTM_DTYPE_F32) and row pitch ldd.

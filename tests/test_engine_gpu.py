@@ -77,10 +77,16 @@ def test_scaled_baseline_configs(name, scale):
     ("bf16", 2, 5, 32, 2048, 2048, True),    # config 3's width: W_hh slices do not fit shared memory -> streamed from L2
     ("f16", 1, 4, 8, 4096, 4096, False),     # config 4: two row tiles per CTA, streamed weights, inference
     ("f16", 1, 3, 1, 4096, 4096, False),     # config 4 at batch 1
-    ("bf16", 2, 4, 256, 256, 1024, True),    # several batch tiles per CTA (config 5's regime: B >> 64)
+    ("bf16", 2, 4, 256, 256, 1024, True),    # wide batch (config 5's regime): one GEMM launch per step, no K split
+    ("f16", 1, 5, 300, 128, 256, True),      # wide batch, ragged last 128-row tile, backward K split 8 ways
+    ("bf16", 1, 3, 256, 128, 512, False),    # wide batch, inference
     ("f16", 1, 6, 200, 192, 192, True),      # ragged batch tile, K chunks not a multiple of 4
+    ("bf16", 2, 4, 256, 256, 1024, "persistent"),  # the persistent kernels with several batch tiles per CTA
 ])
-def test_wide_and_large_batch_regimes(dtype, L, T, B, I, H, training):
+def test_wide_and_large_batch_regimes(dtype, L, T, B, I, H, training, monkeypatch):
+    if training == "persistent":
+        monkeypatch.setenv("FLSTM_STEP_MIN_BATCH", "0")  # keep wide batches on the persistent kernels
+        training = True
     w = Workload("t", dtype, L, I, H, B, T, seed=17, state_std=0.2, training=training)
     inp = make_inputs(w)
     got, eng = run_engine(w, inp, backend="tc")
@@ -178,14 +184,14 @@ def test_whole_step_in_a_cuda_graph(dtype, L, H):
 
 @pytest.mark.parametrize("dtype,L,H,backend", [("f16", 1, 128, "tc"), ("bf16", 2, 64, "tc"), ("f32", 2, 24, "simt"),
                                                ("f16", 1, 1024, "tc")])
-def test_step_ranges_equal_one_call(dtype, L, H, backend):
+def test_step_ranges_equal_one_call(dtype, L, H, backend, B=16):
     """A sequence run as ascending forward ranges and descending backward ranges gives bit-identical
     results to the single forward / backward calls (the ranges are what host streaming pipelines)."""
     from flashlstm_poc_b200.engine import TORCH_DTYPES, Engine
 
     dev = torch.device("cuda", 0)
     td = TORCH_DTYPES[dtype]
-    T, B, I = 23, 16, 64
+    T, I = 23, 64
     w = Workload("r", dtype, L, I, H, B, T, seed=41, state_std=0.2)
     inp = make_inputs(w)
     torch.manual_seed(3)
@@ -221,6 +227,11 @@ def test_step_ranges_equal_one_call(dtype, L, H, backend):
     ref = run_oracle(inp, dhn.float().cpu(), dcn.float().cpu())
     got = {"y": whole[0].float().cpu().numpy(), "dx": whole[3].float().cpu().numpy(), "dh0": whole[4].cpu().numpy()}
     assert_parity(got, ref, dtype, keys=["y", "dx", "dh0"])
+
+
+def test_step_ranges_wide_batch():
+    """The same for the wide-batch path, whose fp32 partial sums of dh carry over between ranges."""
+    test_step_ranges_equal_one_call("bf16", 2, 128, "tc", B=256)
 
 
 def test_step_ranges_must_be_in_order():

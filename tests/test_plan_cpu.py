@@ -1,0 +1,76 @@
+"""Host logic of the tensor-core backend's planner (no GPU needed): for a sweep of shapes the
+persistent grids fit the machine, shared memory stays under the limit, and the tiling covers the
+problem exactly."""
+import ctypes
+
+import pytest
+
+from flashlstm_poc_b200 import _build, _lib
+
+SMS, SMEM = 148, 232448  # B200
+
+
+@pytest.fixture(scope="module")
+def lib():
+    _build.build()
+    return _lib.load()
+
+
+def plan(lib, B, H, training=1, sms=SMS, smem=SMEM):
+    info = _lib.TcPlanInfo()
+    st = lib.flstm_tc_plan(B, H, training, sms, smem, ctypes.byref(info))
+    return st, info
+
+
+@pytest.mark.parametrize("H", [64, 128, 192, 256, 512, 768, 1024, 2048, 4096])
+@pytest.mark.parametrize("B", [1, 8, 32, 64, 200, 256, 2048])
+def test_plans_fit_the_machine(lib, B, H):
+    st, p = plan(lib, B, H, training=1 if H <= 2048 else 0)
+    assert st == 0, lib.flstm_last_error()
+    if B >= 256 and H % 128 == 0:
+        # wide batches: one output-tiled GEMM launch per step; K = 4H split while tiles are scarce
+        assert p.step_path == 1 and p.fwd_grid == 0
+        assert p.step_bn_fwd in (128, 256) and p.step_bn_bwd in (128, 256) and (4 * H) % p.step_bn_fwd == 0
+        assert H % p.step_bn_bwd == 0 and p.step_splits in (1, 2, 4, 8) and (4 * H // 64) % p.step_splits == 0
+        return
+    assert p.step_path == 0
+    # forward: co-resident grid, covers all row tiles and all sequences
+    assert 1 <= p.fwd_grid <= SMS and p.fwd_smem_bytes <= SMEM
+    cta_rows = p.fwd_grid // p.fwd_batch_groups
+    assert cta_rows * p.fwd_row_tiles_per_cta == H // 16
+    assert p.fwd_batch_groups * p.fwd_tiles_per_group * p.fwd_batch_tile >= B
+    assert (H // 64) % p.fwd_chunks_per_stage == 0 and p.fwd_stages >= 1
+    if not p.fwd_weights_resident:
+        assert H >= 2048 or B >= 128  # small batches keep their W_hh slice in shared memory up to H = 1024
+    if H <= 2048:
+        assert 1 <= p.bwd_grid <= SMS and p.bwd_smem_bytes <= SMEM
+        assert p.bwd_cluster_size in (1, 2, 4) and p.bwd_grid % p.bwd_cluster_size == 0
+        assert p.bwd_grid == (H // 64) * p.bwd_cluster_size * p.bwd_batch_groups
+        assert ((H // 16) // p.bwd_cluster_size) % p.bwd_chunks_per_stage == 0
+        assert p.bwd_batch_groups * p.bwd_tiles_per_group * p.bwd_batch_tile >= B
+
+
+def test_benchmark_configuration_plan(lib):
+    """Config 2 (H=1024, B=64): 64 row tiles x 2 batch halves, resident weights, one whole-tile copy per
+    step; BPTT as 32 clusters of 4."""
+    st, p = plan(lib, 64, 1024)
+    assert st == 0
+    assert (p.fwd_grid, p.fwd_batch_tile, p.fwd_batch_groups, p.fwd_tiles_per_group) == (128, 32, 2, 1)
+    assert p.fwd_weights_resident == 1 and p.fwd_chunks_per_stage == 16 and p.fwd_stages == 1
+    assert (p.bwd_grid, p.bwd_cluster_size, p.bwd_weights_resident) == (128, 4, 1)
+
+
+def test_wide_batch_plans(lib):
+    """Config 3 (B=256, H=2048): 128 forward tiles of 128 x 128, backward K split 4 ways.
+    Config 5 (B=2048, H=1024): 256-wide forward tiles, no K split."""
+    st, p = plan(lib, 256, 2048)
+    assert st == 0 and (p.step_path, p.step_bn_fwd, p.step_splits) == (1, 128, 4)
+    st, p = plan(lib, 2048, 1024)
+    assert st == 0 and (p.step_path, p.step_bn_fwd, p.step_splits) == (1, 256, 1)
+
+
+def test_unsupported_shapes_are_reported(lib):
+    st, _ = plan(lib, 8, 100)
+    assert st == 4 and b"multiple of 64" in lib.flstm_last_error()
+    st, _ = plan(lib, 8, 1024, smem=16 * 1024)  # a machine with too little shared memory
+    assert st == 4
