@@ -256,6 +256,11 @@ int make_tensor_map_2d(CUtensorMap *out, const void *base, uint64_t rows, uint64
 int make_tensor_map_3d(CUtensorMap *out, const void *base, uint64_t d2, uint64_t rows, uint64_t cols,
                        uint64_t row_pitch_elems, uint64_t d2_pitch_elems, uint32_t box_rows, uint32_t box_cols,
                        bool swizzle128);
+// Dense (d2, rows, cols) tensor of 2- or 4-byte elements, box 1 x box_rows x box_cols whose rows are 32, 64
+// or 128 bytes; swizzle span = the row size, so row r of the tile sits at r * row_bytes in shared memory
+// with its 16-byte chunk index XOR-ed by address bits 7.. (the staging tiles of the step epilogue).
+int make_tensor_map_3d_tile(CUtensorMap *out, const void *base, int elem_bytes, uint64_t d2, uint64_t rows, uint64_t cols,
+                            uint32_t box_rows, uint32_t box_cols);
 // A (steps, rows, width) 16-bit tensor seen as (steps, width/64, rows, 64): one box of
 // 1 x chunks x box_rows x 64 lands in shared memory as `chunks` consecutive [box_rows x 128 B]
 // swizzled K-major UMMA operand tiles, so one copy brings several 64-wide K chunks of a tile.

@@ -29,6 +29,7 @@ struct TcLayer {
     CUtensorMap tm_hs3;    // hs (Tcap+1, B, H), 1 x 128 x 64 boxes, 128B swizzle
     CUtensorMap tm_wstep;  // w_hh (4H, H), bn_fwd x 64 boxes, 128B swizzle
     CUtensorMap tm_dg3;    // dG (Tcap, B, 4H), 1 x 128 x 64 boxes, 128B swizzle
+    CUtensorMap tm_g_ep, tm_c_ep, tm_h_ep;  // 32-row epilogue tiles of gates / cs / hs
 };
 
 struct TcState {
@@ -180,6 +181,9 @@ int on_capacity_change(Engine &e) {
         if (st->step.use) {
             FLSTM_TRY(make_tensor_map_3d(&t.tm_hs3, l.hs, cap + 1, B, H, H, B * H, 128, 64, true));
             FLSTM_TRY(make_tensor_map_2d(&t.tm_wstep, l.w_hh, 4 * H, H, H, st->step.bn_fwd, 64, true));
+            FLSTM_TRY(make_tensor_map_3d_tile(&t.tm_g_ep, l.gates, 2, cap, B, 4 * H, 32, 64));
+            FLSTM_TRY(make_tensor_map_3d_tile(&t.tm_c_ep, l.cs, 4, cap + 1, B, H, 32, 16));
+            FLSTM_TRY(make_tensor_map_3d_tile(&t.tm_h_ep, l.hs, 2, cap + 1, B, H, 32, 16));
             if (e.cfg.training && l.dg)
                 FLSTM_TRY(make_tensor_map_3d(&t.tm_dg3, l.dg, cap, B, 4 * H, 4 * H, B * 4 * H, 128, 64, true));
             continue;
@@ -230,20 +234,17 @@ int forward_layer(Engine &e, int li, size_t t0, size_t t1, const void *x_l, void
                    l.w_ih, l.in_size, false, byte_ptr(l.gates) + t0 * B * 4 * H * es, 4 * H, l.bias, 0, err, st->sms, s));
     size_t m1 = e.timer.mark(s);
     if (st->step.use) {
-        const size_t slab = B * H;
+        CUtensorMap tm_y;
+        if (y_out) FLSTM_TRY(make_tensor_map_3d_tile(&tm_y, y_out, 2, t1, B, H, 32, 16));
+        const StepFwdMaps maps{&t.tm_hs3, &t.tm_wstep, &t.tm_g_ep, &t.tm_c_ep, &t.tm_h_ep, y_out ? &tm_y : nullptr};
         for (size_t step = t0; step < t1; ++step) {
             StepFwdParams sp{};
-            sp.gates_t = byte_ptr(l.gates) + step * B * 4 * H * es;
-            sp.c_prev = l.cs + step * slab;
-            sp.c_out = l.cs + (step + 1) * slab;
-            sp.h_out = byte_ptr(l.hs) + (step + 1) * slab * es;
-            sp.y_out = y_out ? byte_ptr(y_out) + step * slab * es : nullptr;
             sp.err = err;
             sp.t = (int)step;
             sp.B = (int)B;
             sp.H = (int)H;
             sp.store_gates = e.cfg.training ? 1 : 0;
-            FLSTM_TRY(lstm_step_forward(e.cfg.dtype, st->step, t.tm_hs3, t.tm_wstep, sp, st->sms, s));
+            FLSTM_TRY(lstm_step_forward(e.cfg.dtype, st->step, maps, sp, st->sms, s));
         }
         size_t m2 = e.timer.mark(s);
         e.timer.span(PH_PROJ, m0, m1);

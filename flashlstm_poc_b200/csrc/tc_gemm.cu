@@ -377,6 +377,26 @@ int make_tensor_map_3d(CUtensorMap *out, const void *base, uint64_t d2, uint64_t
     return FLSTM_OK;
 }
 
+int make_tensor_map_3d_tile(CUtensorMap *out, const void *base, int elem_bytes, uint64_t d2, uint64_t rows, uint64_t cols,
+                            uint32_t box_rows, uint32_t box_cols) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return set_error(FLSTM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const uint32_t inner = box_cols * elem_bytes;
+    if (elem_bytes != 2 && elem_bytes != 4) return set_error(FLSTM_ERR_INVALID, "tensor map element size must be 2 or 4");
+    if (inner != 32 && inner != 64 && inner != 128) return set_error(FLSTM_ERR_INVALID, "tile rows must be 32, 64 or 128 bytes");
+    cuuint64_t dims[3] = {cols, rows, d2};
+    cuuint64_t strides[2] = {cols * elem_bytes, rows * cols * elem_bytes};
+    cuuint32_t box[3] = {box_cols, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    const CUtensorMapSwizzle sw = inner == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : inner == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+    CUresult r = fn(out, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(FLSTM_ERR_CUDA, "cuTensorMapEncodeTiled (3-D tile) failed (%d)", (int)r);
+    return FLSTM_OK;
+}
+
 int make_tensor_map_chunked(CUtensorMap *out, const void *base, uint64_t steps, uint64_t rows, uint64_t width,
                             uint32_t box_rows, uint32_t chunks) {
     EncodeTiledFn fn = encode_fn();

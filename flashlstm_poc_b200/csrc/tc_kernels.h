@@ -106,22 +106,23 @@ struct StepPlan {
 };
 
 struct StepFwdParams {
-    void *gates_t;        // 16-bit (B,4H) at step t: projection in, activated gates out
-    const float *c_prev;  // fp32 (B,H) cell state entering the step
-    float *c_out;         // fp32 (B,H)
-    void *h_out;          // 16-bit (B,H): slot t+1 of the hidden states
-    void *y_out;          // optional 16-bit (B,H) copy for the caller
     unsigned int *err;
-    int t;                // slot of h_{t-1} in the hidden-state tensor map (= absolute step)
+    int t;            // absolute time step: h_{t-1} / c_{t-1} in slot t of the state tensors, results in slot t+1
     int B, H;
-    int store_gates;
+    int store_gates;  // overwrite the projection with the activated gates (the gate cache)
+};
+
+// Tensor maps of the forward step kernel.  Operands: hs (T+1, B, H) as a 3-D map with 1 x 128 x 64 boxes and
+// W_hh (rows tile-interleaved, (4H, H)) with plan.bn_fwd x 64 boxes, both 128B-swizzled.  Epilogue tiles
+// (make_tensor_map_3d_tile, 32-row boxes): gates (T, B, 4H) 64 columns wide, cs (T+1, B, H) fp32 16 wide,
+// hs_out (T+1, B, H) 16 wide, y = the caller's (T, B, H) output 16 wide or null.
+struct StepFwdMaps {
+    const CUtensorMap *hs, *w, *gates, *cs, *hs_out, *y;
 };
 
 int plan_step(int B, int H, int sms, StepPlan *plan);
-// tm_hs: hidden states (T+1, B, H) as a 3-D map, box 1 x 128 x 64, 128B swizzle.  tm_w: W_hh rows
-// tile-interleaved (4H, H), box plan.bn_fwd x 64, 128B swizzle.
-int lstm_step_forward(int dtype, const StepPlan &plan, const CUtensorMap &tm_hs, const CUtensorMap &tm_w,
-                      const StepFwdParams &p, int sms, cudaStream_t s);
+int lstm_step_forward(int dtype, const StepPlan &plan, const StepFwdMaps &m, const StepFwdParams &p, int sms,
+                      cudaStream_t s);
 // parts[s] (B,H) fp32 = dG_t[:, K slice s] W_hh[K slice s, :].  tm_dg: dG (T, B, 4H) as a 3-D map, box
 // 1 x 128 x 64, 128B swizzle.  tm_w64: W_hh (4H, H) with 64 x 64 boxes (read as an MN-major operand).
 int lstm_step_backward_gemm(int dtype, const StepPlan &plan, const CUtensorMap &tm_dg, const CUtensorMap &tm_w64, int t,

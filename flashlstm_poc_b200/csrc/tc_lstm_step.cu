@@ -34,17 +34,24 @@ namespace {
 constexpr int BM = 128, BK = 64;
 constexpr int kStepThreads = 192;
 
-template <int BN>
+enum Epilogue { EPI_LSTM_FWD = 0, EPI_F32_PARTS = 1 };
+
+// Staging tiles of one forward-epilogue warp (32 sequences x one group of 16 hidden units), all filled and
+// drained by TMA: 2 x [32 x 128 B] projection in / gates out, 2 x [32 x 64 B] cell state in / out,
+// [32 x 32 B] hidden state out.
+constexpr int kEpiPBytes = 32 * 128, kEpiCBytes = 32 * 64, kEpiHBytes = 32 * 32;
+constexpr int kEpiWarpBytes = 2 * kEpiPBytes + 2 * kEpiCBytes + kEpiHBytes;  // 13312, a multiple of 1024
+
+template <int BN, int EPI>
 struct StepShape {
-    static constexpr int kStages = (BN == 256) ? 4 : 6;
+    static constexpr int kStages = (EPI == EPI_LSTM_FWD) ? ((BN == 256) ? 3 : 5) : ((BN == 256) ? 4 : 6);
     static constexpr int kABytes = BM * BK * 2;
     static constexpr int kBBytes = BN * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kEpiBytes = (EPI == EPI_LSTM_FWD) ? 4 * kEpiWarpBytes : 0;
     static constexpr int kTmemCols = 2 * BN;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
-
-enum Epilogue { EPI_LSTM_FWD = 0, EPI_F32_PARTS = 1 };
 
 struct StepArgs {
     int M, N, K;       // M = batch, N = output columns, K = contraction length
@@ -54,14 +61,10 @@ struct StepArgs {
     unsigned int *err;
     // EPI_F32_PARTS
     float *parts;
-    // EPI_LSTM_FWD: all pointers already at time step t
-    void *gates_t;        // 16-bit (B,4H): projection in, activated gates out
-    const float *c_prev;  // fp32 (B,H)
-    float *c_out;         // fp32 (B,H)
-    void *h_out;          // 16-bit (B,H)
-    void *y_out;          // 16-bit (B,H) or null
-    int H;
-    int store_gates;
+    // EPI_LSTM_FWD
+    int t;             // time step: projection / gate cache and y at slot t, states read at slot t, written at t+1
+    int has_y;         // also store h_t into the caller's y
+    int store_gates;   // write the activated gates back (the gate cache)
 };
 
 template <bool BF16>
@@ -79,20 +82,23 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
-// The LSTM cell update of 16 hidden units of one sequence.  acc[0..63]: recurrent sums, gate-major
-// (i,f,g,o) x 16 units, exactly the 64 columns of one unit group.
+// The LSTM cell update of 16 hidden units of one sequence from the staged tiles.  acc[0..63]: recurrent
+// sums, gate-major (i,f,g,o) x 16 units (the 64 columns of one unit group).  r: row of the warp's
+// 32-sequence block.  TMA wrote the tiles with the swizzle of their row size: 16-byte chunk j of row r sits at
+// chunk j ^ (r & 7) (128 B rows), j ^ ((r >> 1) & 3) (64 B rows), j ^ ((r >> 2) & 1) (32 B rows).
+// Outputs overwrite the inputs in place (gates over the projection, c_t over c_{t-1}).
 template <bool BF16>
-__device__ __forceinline__ void lstm_cell_16(const uint32_t (&acc)[64], const StepArgs &a, int b, int group) {
-    const size_t G = (size_t)4 * a.H;
-    uint16_t *grow = static_cast<uint16_t *>(a.gates_t) + (size_t)b * G + (size_t)group * 64;
-    const size_t sidx = (size_t)b * a.H + (size_t)group * 16;
+__device__ __forceinline__ void lstm_cell_16(const uint32_t (&acc)[64], uint8_t *sP, uint8_t *sC, uint8_t *sH, int r,
+                                             int store_gates) {
+    uint8_t *prow = sP + r * 128, *crow = sC + r * 64, *hrow = sH + r * 32;
+    const int xp = r & 7, xc = (r >> 1) & 3, xh = (r >> 2) & 1;
 #pragma unroll
     for (int ub = 0; ub < 2; ++ub) {  // 8 units at a time
         uint4 pv[4];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) pv[g] = *reinterpret_cast<const uint4 *>(grow + g * 16 + ub * 8);
-        const float4 c0 = *reinterpret_cast<const float4 *>(a.c_prev + sidx + ub * 8);
-        const float4 c1 = *reinterpret_cast<const float4 *>(a.c_prev + sidx + ub * 8 + 4);
+        for (int g = 0; g < 4; ++g) pv[g] = *reinterpret_cast<const uint4 *>(prow + (((g * 2 + ub) ^ xp) << 4));
+        const float4 c0 = *reinterpret_cast<const float4 *>(crow + (((ub * 2) ^ xc) << 4));
+        const float4 c1 = *reinterpret_cast<const float4 *>(crow + (((ub * 2 + 1) ^ xc) << 4));
         const float cp[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
         float cn[8], hn[8], act[4][8];
 #pragma unroll
@@ -114,16 +120,14 @@ __device__ __forceinline__ void lstm_cell_16(const uint32_t (&acc)[64], const St
             hn[u] = go * tanh_fast(c);
             act[0][u] = gi; act[1][u] = gf; act[2][u] = gg; act[3][u] = go;
         }
-        const uint4 hv = make_uint4(pack2<BF16>(hn[0], hn[1]), pack2<BF16>(hn[2], hn[3]), pack2<BF16>(hn[4], hn[5]),
-                                    pack2<BF16>(hn[6], hn[7]));
-        *reinterpret_cast<uint4 *>(static_cast<uint16_t *>(a.h_out) + sidx + ub * 8) = hv;
-        if (a.y_out) *reinterpret_cast<uint4 *>(static_cast<uint16_t *>(a.y_out) + sidx + ub * 8) = hv;
-        *reinterpret_cast<float4 *>(a.c_out + sidx + ub * 8) = make_float4(cn[0], cn[1], cn[2], cn[3]);
-        *reinterpret_cast<float4 *>(a.c_out + sidx + ub * 8 + 4) = make_float4(cn[4], cn[5], cn[6], cn[7]);
-        if (a.store_gates) {
+        *reinterpret_cast<uint4 *>(hrow + ((ub ^ xh) << 4)) =
+            make_uint4(pack2<BF16>(hn[0], hn[1]), pack2<BF16>(hn[2], hn[3]), pack2<BF16>(hn[4], hn[5]), pack2<BF16>(hn[6], hn[7]));
+        *reinterpret_cast<float4 *>(crow + (((ub * 2) ^ xc) << 4)) = make_float4(cn[0], cn[1], cn[2], cn[3]);
+        *reinterpret_cast<float4 *>(crow + (((ub * 2 + 1) ^ xc) << 4)) = make_float4(cn[4], cn[5], cn[6], cn[7]);
+        if (store_gates) {
 #pragma unroll
             for (int g = 0; g < 4; ++g)
-                *reinterpret_cast<uint4 *>(grow + g * 16 + ub * 8) =
+                *reinterpret_cast<uint4 *>(prow + (((g * 2 + ub) ^ xp) << 4)) =
                     make_uint4(pack2<BF16>(act[g][0], act[g][1]), pack2<BF16>(act[g][2], act[g][3]),
                                pack2<BF16>(act[g][4], act[g][5]), pack2<BF16>(act[g][6], act[g][7]));
         }
@@ -132,16 +136,22 @@ __device__ __forceinline__ void lstm_cell_16(const uint32_t (&acc)[64], const St
 
 // A: (steps, M, K) K-major through a 3-D map with 128 x 64 boxes.  B: K-major (N, K) with BN x 64 boxes
 // (forward: W_hh rows = gate columns) or MN-major, stored (K, N), 64 x 64 boxes (backward: W_hh as stored).
+// Forward epilogue maps (make_tensor_map_3d_tile, 32-row boxes): tm_g gates (T,B,4H) 64 columns wide, tm_c cell
+// states (T+1,B,H) fp32 16 wide, tm_h hidden states (T+1,B,H) 16 wide, tm_y the caller's y (T,B,H) 16 wide.
 template <int BN, int EPI, bool B_MN, bool BF16>
 __global__ void __launch_bounds__(kStepThreads, 1)
-step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const StepArgs a) {
-    using S = StepShape<BN>;
+step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+            const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_c,
+            const __grid_constant__ CUtensorMap tm_h, const __grid_constant__ CUtensorMap tm_y, const StepArgs a) {
+    using S = StepShape<BN, EPI>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::kStages * S::kStageBytes);
+    uint8_t *epi = smem + S::kStages * S::kStageBytes;  // 1024-aligned: stage sizes are multiples of 1024
+    uint64_t *bars = reinterpret_cast<uint64_t *>(epi + S::kEpiBytes);
     uint64_t *full = bars, *empty = bars + S::kStages;
     uint64_t *tfull = bars + 2 * S::kStages, *tempty = tfull + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty + 2);
+    uint64_t *ldbars = tempty + 2;  // 2 per epilogue warp
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(ldbars + 8);
     volatile uint32_t *abort_w = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -154,10 +164,16 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             mbar_init(&tfull[i], 1);
             mbar_init(&tempty[i], 4);
         }
+        for (int i = 0; i < 8; ++i) mbar_init(&ldbars[i], 1);
         *abort_w = 0;
         fence_barrier_init();
         tma_prefetch_desc(&tm_a);
         tma_prefetch_desc(&tm_b);
+        if (EPI == EPI_LSTM_FWD) {
+            tma_prefetch_desc(&tm_g);
+            tma_prefetch_desc(&tm_c);
+            tma_prefetch_desc(&tm_h);
+        }
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, S::kTmemCols);
@@ -231,26 +247,85 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
     } else {
         const int q = warp & 3;  // TMEM lane quadrant this warp may access
-        int it = 0;
-        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
-            const int buf = it & 1;
-            const uint32_t bphase = (it >> 1) & 1;
-            const int ks = tile / (num_m * num_n), mn = tile % (num_m * num_n);
-            const int m0 = (mn / num_n) * BM, n0 = (mn % num_n) * BN;
-            if (!mbar_wait(&tfull[buf], bphase, abort_w)) break;
-            tcgen05_fence_after();
-            const int row = m0 + q * 32 + lane;  // sequence index
-            const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
-            if (EPI == EPI_LSTM_FWD) {
+        if (EPI == EPI_LSTM_FWD) {
+            // Items = (tile, 64-column unit group) pairs in order.  Lane 0 keeps the loads of the next item in
+            // flight while the warp works on the current one; outputs leave through TMA stores from the same tiles.
+            constexpr int kGroups = BN / 64;
+            uint8_t *wb = epi + q * kEpiWarpBytes;
+            uint8_t *sH = wb + 2 * kEpiPBytes + 2 * kEpiCBytes;
+            uint64_t *ldbar = ldbars + q * 2;
+            const int my_tiles = (tiles > (int)blockIdx.x) ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+            const int items = my_tiles * kGroups;
+            auto item_coords = [&](int idx, int &row0, int &col0) {
+                const int tl = blockIdx.x + (idx / kGroups) * gridDim.x;
+                row0 = (tl / num_n) * BM + q * 32;
+                col0 = (tl % num_n) * BN + (idx % kGroups) * 64;
+            };
+            auto issue_loads = [&](int idx) {  // one lane
+                int row0, col0;
+                item_coords(idx, row0, col0);
+                if (row0 >= a.M) return;  // nothing of this block is a real sequence
+                const int buf = idx & 1;
+                mbar_expect_tx(&ldbar[buf], kEpiPBytes + kEpiCBytes);
+                tma_load_3d(wb + buf * kEpiPBytes, &tm_g, col0, row0, a.t, &ldbar[buf]);
+                tma_load_3d(wb + 2 * kEpiPBytes + buf * kEpiCBytes, &tm_c, col0 >> 2, row0, a.t, &ldbar[buf]);
+            };
+            if (lane == 0 && items > 0) issue_loads(0);
+            uint32_t ldphase = 0;  // bit b: parity of the next completion of ldbar[b]
+            int item = 0, it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++it) {
+                const int tbuf = it & 1;
+                if (!mbar_wait(&tfull[tbuf], (it >> 1) & 1, abort_w)) break;
+                tcgen05_fence_after();
+                const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + tbuf * BN;
 #pragma unroll 1
-                for (int c = 0; c < BN; c += 64) {
+                for (int g = 0; g < kGroups; ++g, ++item) {
+                    const int buf = item & 1;
+                    int row0, col0;
+                    item_coords(item, row0, col0);
+                    if (lane == 0) {
+                        tma_store_wait_read<0>();  // earlier stores have read the other buffers and sH
+                        if (item + 1 < items) issue_loads(item + 1);
+                    }
+                    __syncwarp();
                     uint32_t acc[64];
-                    tmem_ld_32x32b_x32(t_row + c, *reinterpret_cast<uint32_t(*)[32]>(&acc[0]));
-                    tmem_ld_32x32b_x32(t_row + c + 32, *reinterpret_cast<uint32_t(*)[32]>(&acc[32]));
+                    tmem_ld_32x32b_x32(t_row + g * 64, *reinterpret_cast<uint32_t(*)[32]>(&acc[0]));
+                    tmem_ld_32x32b_x32(t_row + g * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&acc[32]));
                     tmem_ld_wait();
-                    if (row < a.M) lstm_cell_16<BF16>(acc, a, row, (n0 + c) >> 6);
+                    if (g == kGroups - 1) {  // the accumulator is in registers: hand it back to the UMMA warp
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tempty[tbuf]);
+                    }
+                    if (row0 >= a.M) continue;
+                    ok = mbar_wait(&ldbar[buf], (ldphase >> buf) & 1u, abort_w);
+                    if (!ok) break;
+                    ldphase ^= 1u << buf;
+                    uint8_t *sP = wb + buf * kEpiPBytes, *sC = wb + 2 * kEpiPBytes + buf * kEpiCBytes;
+                    lstm_cell_16<BF16>(acc, sP, sC, sH, lane, a.store_gates);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (a.store_gates) tma_store_3d(&tm_g, sP, col0, row0, a.t);
+                        tma_store_3d(&tm_c, sC, col0 >> 2, row0, a.t + 1);
+                        tma_store_3d(&tm_h, sH, col0 >> 2, row0, a.t + 1);
+                        if (a.has_y) tma_store_3d(&tm_y, sH, col0 >> 2, row0, a.t);
+                        tma_store_commit();
+                    }
                 }
-            } else {
+            }
+            if (lane == 0) tma_store_wait_all<0>();
+        } else {
+            int it = 0;
+            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+                const int buf = it & 1;
+                const int ks = tile / (num_m * num_n), mn = tile % (num_m * num_n);
+                const int m0 = (mn / num_n) * BM, n0 = (mn % num_n) * BN;
+                if (!mbar_wait(&tfull[buf], (it >> 1) & 1, abort_w)) break;
+                tcgen05_fence_after();
+                const int row = m0 + q * 32 + lane;  // sequence index
+                const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
                 float *dst = a.parts + ((size_t)ks * a.M + row) * a.N + n0;
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 32) {
@@ -265,10 +340,10 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                                             __uint_as_float(acc[4 * i + 2]), __uint_as_float(acc[4 * i + 3]));
                     }
                 }
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tempty[buf]);
             }
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&tempty[buf]);
         }
     }
     tcgen05_fence_before();
@@ -368,9 +443,14 @@ __global__ void sum_parts_kernel(const float *__restrict__ parts, int nparts, si
     }
 }
 
+struct EpilogueMaps {
+    const CUtensorMap *g, *c, *h, *y;
+};
+
 template <int BN, int EPI, bool B_MN, bool BF16>
-int launch_step(const CUtensorMap &ta, const CUtensorMap &tb, const StepArgs &a, int sms, cudaStream_t s) {
-    using S = StepShape<BN>;
+int launch_step(const CUtensorMap &ta, const CUtensorMap &tb, const EpilogueMaps &em, const StepArgs &a, int sms,
+                cudaStream_t s) {
+    using S = StepShape<BN, EPI>;
     auto kern = step_kernel<BN, EPI, B_MN, BF16>;
     static bool configured = false;  // per instantiation
     if (!configured) {
@@ -379,7 +459,7 @@ int launch_step(const CUtensorMap &ta, const CUtensorMap &tb, const StepArgs &a,
     }
     const int tiles = ((a.M + BM - 1) / BM) * (a.N / BN) * a.splits;
     const int grid = tiles < sms ? tiles : sms;
-    kern<<<grid, kStepThreads, S::kSmemBytes, s>>>(ta, tb, a);
+    kern<<<grid, kStepThreads, S::kSmemBytes, s>>>(ta, tb, *em.g, *em.c, *em.h, *em.y, a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "step kernel launch failed: %s", cudaGetErrorString(e));
     return FLSTM_OK;
@@ -412,8 +492,8 @@ int plan_step(int B, int H, int sms, StepPlan *plan) {
     return FLSTM_OK;
 }
 
-int lstm_step_forward(int dtype, const StepPlan &plan, const CUtensorMap &tm_hs, const CUtensorMap &tm_w,
-                      const StepFwdParams &p, int sms, cudaStream_t s) {
+int lstm_step_forward(int dtype, const StepPlan &plan, const StepFwdMaps &m, const StepFwdParams &p, int sms,
+                      cudaStream_t s) {
     const bool bf16 = dtype == FLSTM_DTYPE_BF16;
     StepArgs a{};
     a.M = p.B;
@@ -423,18 +503,15 @@ int lstm_step_forward(int dtype, const StepPlan &plan, const CUtensorMap &tm_hs,
     a.splits = 1;
     a.idesc = umma_idesc_f16(BM, plan.bn_fwd, bf16 ? 1 : 0, 0, 0);
     a.err = p.err;
-    a.gates_t = p.gates_t;
-    a.c_prev = p.c_prev;
-    a.c_out = p.c_out;
-    a.h_out = p.h_out;
-    a.y_out = p.y_out;
-    a.H = p.H;
+    a.t = p.t;
+    a.has_y = m.y ? 1 : 0;
     a.store_gates = p.store_gates;
+    const EpilogueMaps em{m.gates, m.cs, m.hs_out, m.y ? m.y : m.hs_out};
     if (plan.bn_fwd == 256)
-        return bf16 ? launch_step<256, EPI_LSTM_FWD, false, true>(tm_hs, tm_w, a, sms, s)
-                    : launch_step<256, EPI_LSTM_FWD, false, false>(tm_hs, tm_w, a, sms, s);
-    return bf16 ? launch_step<128, EPI_LSTM_FWD, false, true>(tm_hs, tm_w, a, sms, s)
-                : launch_step<128, EPI_LSTM_FWD, false, false>(tm_hs, tm_w, a, sms, s);
+        return bf16 ? launch_step<256, EPI_LSTM_FWD, false, true>(*m.hs, *m.w, em, a, sms, s)
+                    : launch_step<256, EPI_LSTM_FWD, false, false>(*m.hs, *m.w, em, a, sms, s);
+    return bf16 ? launch_step<128, EPI_LSTM_FWD, false, true>(*m.hs, *m.w, em, a, sms, s)
+                : launch_step<128, EPI_LSTM_FWD, false, false>(*m.hs, *m.w, em, a, sms, s);
 }
 
 int lstm_step_backward_gemm(int dtype, const StepPlan &plan, const CUtensorMap &tm_dg, const CUtensorMap &tm_w64, int t,
@@ -449,9 +526,9 @@ int lstm_step_backward_gemm(int dtype, const StepPlan &plan, const CUtensorMap &
     a.idesc = umma_idesc_f16(BM, plan.bn_bwd, bf16 ? 1 : 0, 0, 1);
     a.err = err;
     a.parts = parts;
-    a.H = H;
-    if (plan.bn_bwd == 256) return launch_step<256, EPI_F32_PARTS, true, false>(tm_dg, tm_w64, a, sms, s);
-    return launch_step<128, EPI_F32_PARTS, true, false>(tm_dg, tm_w64, a, sms, s);
+    const EpilogueMaps em{&tm_dg, &tm_dg, &tm_dg, &tm_dg};  // unused by this epilogue
+    if (plan.bn_bwd == 256) return launch_step<256, EPI_F32_PARTS, true, false>(tm_dg, tm_w64, em, a, sms, s);
+    return launch_step<128, EPI_F32_PARTS, true, false>(tm_dg, tm_w64, em, a, sms, s);
 }
 
 int lstm_step_backward_pointwise(int dtype, const void *gates_t, const float *c_t, const float *c_prev, const void *dy_t,
