@@ -18,6 +18,7 @@
 // Replaces, for large batches, the same reference code as the persistent kernels: the per-step
 // recurrent launches of flashlstm_v2/src/lstm_forward.cu:744-830 and lstm_backward.cu:806-1110.
 #include <cstdlib>
+#include <utility>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -66,6 +67,35 @@ struct StepArgs {
     int has_y;         // also store h_t into the caller's y
     int store_gates;   // write the activated gates back (the gate cache)
 };
+
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Kernels of the per-step chain start while the previous one drains (programmatic dependent launch); each
+// waits for its predecessor with griddepcontrol.wait before touching global memory.  FLSTM_PDL=0 turns it off.
+bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char *env = std::getenv("FLSTM_PDL");
+        on = (env && env[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_chained(void (*kern)(KArgs...), int grid, int block, size_t smem, cudaStream_t s, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
 
 template <bool BF16>
 __device__ __forceinline__ float2 unpack2(uint32_t w) {
@@ -155,6 +185,9 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     volatile uint32_t *abort_w = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // The next kernel of the chain may be scheduled as soon as CTAs of this grid retire (it is never
+    // co-resident with one: both need most of the SM's shared memory); it still waits for this whole grid.
+    grid_launch_dependents();
     if (threadIdx.x == 0) {
         for (int i = 0; i < S::kStages; ++i) {
             mbar_init(&full[i], 1);
@@ -183,6 +216,9 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Launched with programmatic stream serialization: everything above overlapped the tail of the previous
+    // step's kernel; its results (h, c, dG, partial sums) may be touched only from here on.
+    grid_dependency_wait();
 
     const int num_m = (a.M + BM - 1) / BM, num_n = a.N / BN;
     const int kblocks = a.K / BK, kper = kblocks / a.splits;
@@ -362,6 +398,7 @@ step_bwd_pointwise_kernel(const uint16_t *__restrict__ gates_t, const float *__r
                           uint16_t *__restrict__ dg_t, int B, int H) {
     const int octets = H >> 3;
     const size_t total = (size_t)B * octets, slab = (size_t)B * H;
+    grid_dependency_wait();
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int b = (int)(i / octets), U0 = (int)(i % octets) * 8;
         const size_t sidx = (size_t)b * H + U0;
@@ -459,8 +496,7 @@ int launch_step(const CUtensorMap &ta, const CUtensorMap &tb, const EpilogueMaps
     }
     const int tiles = ((a.M + BM - 1) / BM) * (a.N / BN) * a.splits;
     const int grid = tiles < sms ? tiles : sms;
-    kern<<<grid, kStepThreads, S::kSmemBytes, s>>>(ta, tb, *em.g, *em.c, *em.h, *em.y, a);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_chained(kern, grid, kStepThreads, S::kSmemBytes, s, ta, tb, *em.g, *em.c, *em.h, *em.y, a);
     if (e != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "step kernel launch failed: %s", cudaGetErrorString(e));
     return FLSTM_OK;
 }
@@ -536,15 +572,11 @@ int lstm_step_backward_pointwise(int dtype, const void *gates_t, const float *c_
     const size_t total = (size_t)B * (H / 8);
     int grid = (int)((total + 255) / 256);
     if (grid > 148 * 8) grid = 148 * 8;
-    if (dtype == FLSTM_DTYPE_BF16)
-        step_bwd_pointwise_kernel<true><<<grid, 256, 0, s>>>(static_cast<const uint16_t *>(gates_t), c_t, c_prev,
-                                                             static_cast<const uint16_t *>(dy_t), parts, nparts, dc,
-                                                             static_cast<uint16_t *>(dg_t), B, H);
-    else
-        step_bwd_pointwise_kernel<false><<<grid, 256, 0, s>>>(static_cast<const uint16_t *>(gates_t), c_t, c_prev,
-                                                              static_cast<const uint16_t *>(dy_t), parts, nparts, dc,
-                                                              static_cast<uint16_t *>(dg_t), B, H);
-    cudaError_t e = cudaGetLastError();
+    const uint16_t *g16 = static_cast<const uint16_t *>(gates_t), *dy16 = static_cast<const uint16_t *>(dy_t);
+    uint16_t *dg16 = static_cast<uint16_t *>(dg_t);
+    cudaError_t e = dtype == FLSTM_DTYPE_BF16
+                        ? launch_chained(step_bwd_pointwise_kernel<true>, grid, 256, 0, s, g16, c_t, c_prev, dy16, parts, nparts, dc, dg16, B, H)
+                        : launch_chained(step_bwd_pointwise_kernel<false>, grid, 256, 0, s, g16, c_t, c_prev, dy16, parts, nparts, dc, dg16, B, H);
     if (e != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "step pointwise launch failed: %s", cudaGetErrorString(e));
     return FLSTM_OK;
 }
