@@ -17,6 +17,8 @@
 // These replace the reference's CUTLASS mma.sync instantiations (src/lstm_internal.h:48-68,
 // flashlstm_v2/src/gemm.cu:208-359) and its per-32-step chunked dW/dX GEMMs with beta=1
 // (flashlstm_v2/src/lstm_backward.cu:1112-1171).
+#include <cstdlib>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -39,7 +41,10 @@ struct GemmShape {
     static constexpr int kBBytes = BN * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTmemCols = 2 * BN;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    // 16-bit outputs leave through TMA: each epilogue warp stages [32 rows x 128 B] tiles, double-buffered
+    static constexpr int kOutTileBytes = 32 * 128;
+    static constexpr int kOutBytes = 4 * 2 * kOutTileBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 enum OutMode { OUT_F16 = 0, OUT_BF16 = 1, OUT_F32 = 2 };
@@ -89,6 +94,44 @@ __device__ __forceinline__ void store_row32(void *dst_row, int col0, const uint3
     }
 }
 
+// 64 accumulator columns of one output row -> 16-bit, into row r of a [32 x 128 B] staging tile laid out
+// the way a 128B-swizzled TMA store expects it (16-byte chunk j of row r at chunk j ^ (r & 7)).
+template <int MODE>
+__device__ __forceinline__ void stage_row64(uint8_t *tile, int r, const uint32_t (&acc)[64], const float *bias, int col0,
+                                            int n_valid) {
+    uint8_t *row = tile + r * 128;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(acc[8 * j + i]);
+        if (bias) {
+            if (n_valid >= 64) {
+                const float4 b0 = __ldg(reinterpret_cast<const float4 *>(bias + col0 + 8 * j));
+                const float4 b1 = __ldg(reinterpret_cast<const float4 *>(bias + col0 + 8 * j + 4));
+                v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (8 * j + i < n_valid) v[i] += __ldg(bias + col0 + 8 * j + i);
+            }
+        }
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (MODE == OUT_F16) {
+                __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+                w[i] = *reinterpret_cast<uint32_t *>(&h);
+            } else {
+                __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                w[i] = *reinterpret_cast<uint32_t *>(&h);
+            }
+        }
+        *reinterpret_cast<uint4 *>(row + ((j ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
 // Output rows may be written through the inverse of the tile-interleaved gate order: row
 // r' = ((u/16)*4 + g)*16 + u%16 of the product goes to row g*H + u of D (unperm_h = H, else 0).
 __device__ __forceinline__ int unpermute_gate_row(int r, int H) {
@@ -96,15 +139,18 @@ __device__ __forceinline__ int unpermute_gate_row(int r, int H) {
     return g * H + tile * 16 + u;
 }
 
-template <int BN, int MODE, bool HAS_BIAS, bool A_MN, bool B_MN>
+// TMA_OUT (16-bit outputs with a 16-byte aligned D and row pitch): tm_d maps D as (M, N) with 32 x 64 boxes.
+template <int BN, int MODE, bool HAS_BIAS, bool A_MN, bool B_MN, bool TMA_OUT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, void *__restrict__ D,
+gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+            const __grid_constant__ CUtensorMap tm_d, void *__restrict__ D,
             size_t ldd, const float *__restrict__ bias, int M, int N, int K, uint32_t idesc, int unperm_h,
             unsigned int *__restrict__ err_word) {
     using S = GemmShape<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::kStages * S::kStageBytes);
+    uint8_t *s_out = smem + S::kStages * S::kStageBytes;  // 1024-aligned: stage sizes are multiples of 1024
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_out + S::kOutBytes);
     uint64_t *full = bars, *empty = bars + S::kStages;
     uint64_t *tfull = bars + 2 * S::kStages, *tempty = tfull + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty + 2);
@@ -112,6 +158,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
+        if (TMA_OUT) tma_prefetch_desc(&tm_d);
         for (int i = 0; i < S::kStages; ++i) {
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], 1);
@@ -200,7 +247,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
     } else {
         const int q = warp & 3;  // TMEM lane quadrant this warp may access
-        int it = 0;
+        int it = 0, out_idx = 0;
         for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
             const int buf = it & 1;
             const uint32_t bphase = (it >> 1) & 1;
@@ -208,6 +255,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             if (!mbar_wait(&tfull[buf], bphase, abort_w)) break;
             tcgen05_fence_after();
             const int row = m0 + q * 32 + lane;
+            if (TMA_OUT) {
+                const int row0 = m0 + q * 32;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 64) {
+                    uint32_t acc[64];
+                    tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c, *reinterpret_cast<uint32_t(*)[32]>(&acc[0]));
+                    tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c + 32, *reinterpret_cast<uint32_t(*)[32]>(&acc[32]));
+                    tmem_ld_wait();
+                    if (c + 64 >= BN) {  // accumulator drained: the UMMA warp may start the tile after next
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tempty[buf]);
+                    }
+                    const int n_valid = N - (n0 + c);
+                    if (row0 >= M || n_valid <= 0) continue;
+                    uint8_t *tile = s_out + (q * 2 + (out_idx & 1)) * S::kOutTileBytes;
+                    if (lane == 0) tma_store_wait_read<1>();  // the store that last used this buffer has read it
+                    __syncwarp();
+                    stage_row64<MODE>(tile, lane, acc, HAS_BIAS ? bias : nullptr, n0 + c, n_valid);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tm_d, tile, n0 + c, row0);
+                        tma_store_commit();
+                    }
+                    ++out_idx;
+                }
+                continue;
+            }
             const size_t esz = (MODE == OUT_F32) ? 4 : 2;
             const int out_row = (unperm_h && row < M) ? unpermute_gate_row(row, unperm_h) : row;
             char *dst_row = static_cast<char *>(D) + (size_t)out_row * ldd * esz;
@@ -223,6 +299,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             __syncwarp();
             if (lane == 0) mbar_arrive(&tempty[buf]);
         }
+        if (TMA_OUT && lane == 0) tma_store_wait_all<0>();
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -231,7 +308,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 }
 
 struct GemmArgs {
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, td;
+    bool tma_out;
     void *D;
     size_t ldd;
     const float *bias;
@@ -243,10 +321,10 @@ struct GemmArgs {
     cudaStream_t s;
 };
 
-template <int BN, int MODE, bool HAS_BIAS, bool A_MN, bool B_MN>
-int launch(const GemmArgs &g) {
+template <int BN, int MODE, bool HAS_BIAS, bool A_MN, bool B_MN, bool TMA_OUT>
+int launch_one(const GemmArgs &g) {
     using S = GemmShape<BN>;
-    auto kern = gemm_kernel<BN, MODE, HAS_BIAS, A_MN, B_MN>;
+    auto kern = gemm_kernel<BN, MODE, HAS_BIAS, A_MN, B_MN, TMA_OUT>;
     static bool configured = false;  // per instantiation
     if (!configured) {
         FLSTM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes));
@@ -254,11 +332,17 @@ int launch(const GemmArgs &g) {
     }
     const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
     const int grid = tiles < g.sms ? tiles : g.sms;
-    kern<<<grid, kGemmThreads, S::kSmemBytes, g.s>>>(g.ta, g.tb, g.D, g.ldd, g.bias, g.M, g.N, g.K, g.idesc, g.unperm_h,
-                                                    g.err);
+    kern<<<grid, kGemmThreads, S::kSmemBytes, g.s>>>(g.ta, g.tb, g.td, g.D, g.ldd, g.bias, g.M, g.N, g.K, g.idesc,
+                                                    g.unperm_h, g.err);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "tc gemm launch failed: %s", cudaGetErrorString(e));
     return FLSTM_OK;
+}
+
+template <int BN, int MODE, bool HAS_BIAS, bool A_MN, bool B_MN>
+int launch(const GemmArgs &g) {
+    if (MODE != OUT_F32 && g.tma_out) return launch_one<BN, MODE, HAS_BIAS, A_MN, B_MN, (MODE != OUT_F32)>(g);
+    return launch_one<BN, MODE, HAS_BIAS, A_MN, B_MN, false>(g);
 }
 
 template <int BN>
@@ -308,6 +392,12 @@ int gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, 
     else FLSTM_TRY(make_tensor_map_2d(&g.ta, A, K, M, lda, BK, 64, true));
     if (!b_mn) FLSTM_TRY(make_tensor_map_2d(&g.tb, B, N, K, ldb, BN, BK, true));
     else FLSTM_TRY(make_tensor_map_2d(&g.tb, B, K, N, ldb, BK, 64, true));
+    // 16-bit outputs go out through TMA when D can be described by a tensor map
+    g.tma_out = out_dtype != FLSTM_DTYPE_F32 && unperm_h == 0 && N >= 64 && (ldd % 8) == 0 &&
+                (reinterpret_cast<uintptr_t>(D) & 15) == 0 && (reinterpret_cast<uintptr_t>(bias) & 15) == 0;
+    if (const char *env = std::getenv("FLSTM_GEMM_TMA_OUT")) g.tma_out = g.tma_out && env[0] != '0';
+    if (g.tma_out) FLSTM_TRY(make_tensor_map_2d(&g.td, D, M, N, ldd, 32, 64, true));
+    else g.td = g.ta;  // unused
     g.D = D;
     g.ldd = ldd;
     g.bias = bias;
