@@ -331,6 +331,15 @@ def main():
         "us_per_timestep": dom_ms * 1e3 / steps_seq,
         "algorithmic_bytes_per_timestep": dom_bytes,
     }
+    if tc and w.name.startswith("c2_fp16_h1024"):
+        # DRAM bytes of the persistent forward kernel from its ncu capture (1.20 MB per time step at T=128, scaled
+        # by T: the traffic is per step); the BPTT kernel cannot be replayed by ncu (cooperative + cluster launch)
+        fwd_traffic = 1.20e6 * T
+        if dom == "recurrent_fwd":
+            roofline["traffic"] = fwd_traffic
+        else:
+            roofline["traffic_recurrent_fwd_kernel"] = fwd_traffic
+            roofline["traffic_note"] = "no ncu capture of the BPTT kernel exists (ncu cannot replay its launch)"
     gemm_flops = w.flops() * (2.0 / 3.0 if w.training else 0.5)
     gemm_ms = phase_acc.get("projection", 0.0) + phase_acc.get("weight_grad", 0.0) + phase_acc.get("input_grad", 0.0)
     extra = {
@@ -366,6 +375,10 @@ def main():
                         "sample": f"all {sample_T} time steps at full batch/width, fwd+bwd, best of 2 passes "
                                   f"({sec:.2f} s each); numpy restatement of the reference's CPU playground"}
 
+    es = 4 if w.dtype == "f32" else 2
+    ws_mib = (2 if w.training else 1) * L * T * B * 4 * H * es / 2**20
+    l2_note = (f"working set (gate cache{' + dG' if w.training else ''} = {ws_mib:.0f} MiB) "
+               + ("exceeds the 126 MB L2" if ws_mib > 126 else "fits the 126 MB L2 (diagnostic size, not a bench configuration)"))
     if rank == 0:
         line = {
             "metric": METRIC, "value": tokens_per_s, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -374,7 +387,7 @@ def main():
             "config": {"workload": w.name, "layers": L, "input_size": I, "hidden_size": H, "batch_per_gpu": B,
                        "global_batch": B * world, "seq_len": T, "parallelism": f"dp{world}",
                        "launch": graph_note,
-                       "l2": "working set (gate cache + dG = 512 MiB) exceeds the 126 MB L2"},
+                       "l2": l2_note},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline,
             "cpu_baseline": cpu_baseline, **extra,
         }
