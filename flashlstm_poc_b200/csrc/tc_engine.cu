@@ -114,11 +114,11 @@ bool supported(const flstm_engine_config &cfg) {
     if (cudaGetDevice(&dev) != cudaSuccess) return false;
     cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
     if (major != 10) return false;
-    StepPlan sp;
-    if (plan_step((int)cfg.batch, (int)cfg.hidden_size, device_sm_count(), &sp) == FLSTM_OK && sp.use) return true;
-    FwdPlan fp;
     int optin = 0;
     cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    StepPlan sp;
+    if (plan_step((int)cfg.batch, (int)cfg.hidden_size, device_sm_count(), (size_t)optin, &sp) == FLSTM_OK && sp.use) return true;
+    FwdPlan fp;
     if (plan_fwd((int)cfg.batch, (int)cfg.hidden_size, device_sm_count(), (size_t)optin, &fp) != FLSTM_OK) return false;
     if (cfg.training) {
         BwdPlan bp;
@@ -134,7 +134,7 @@ int init(Engine &e) {
     int optin = 0;
     FLSTM_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, e.device));
     st->smem_limit = (size_t)optin;
-    FLSTM_TRY(plan_step((int)e.cfg.batch, (int)e.cfg.hidden_size, st->sms, &st->step));
+    FLSTM_TRY(plan_step((int)e.cfg.batch, (int)e.cfg.hidden_size, st->sms, st->smem_limit, &st->step));
     void *raw = nullptr;
     if (st->step.use) {
         st->bwd_ok = e.cfg.training != 0;
@@ -405,7 +405,7 @@ extern "C" int flstm_tc_plan(size_t batch, size_t hidden_size, int training, int
     if (!out || sm_count < 1) return set_error(FLSTM_ERR_INVALID, "bad argument");
     *out = flstm_tc_plan_info{};
     tc::StepPlan sp{};
-    FLSTM_TRY(tc::plan_step((int)batch, (int)hidden_size, sm_count, &sp));
+    FLSTM_TRY(tc::plan_step((int)batch, (int)hidden_size, sm_count, smem_limit, &sp));
     out->step_path = sp.use ? 1 : 0;
     out->step_bn_fwd = sp.bn_fwd;
     out->step_bn_bwd = sp.bn_bwd;

@@ -120,7 +120,7 @@ struct StepFwdMaps {
     const CUtensorMap *hs, *w, *gates, *cs, *hs_out, *y;
 };
 
-int plan_step(int B, int H, int sms, StepPlan *plan);
+int plan_step(int B, int H, int sms, size_t smem_limit, StepPlan *plan);
 int lstm_step_forward(int dtype, const StepPlan &plan, const StepFwdMaps &m, const StepFwdParams &p, int sms,
                       cudaStream_t s);
 // parts[s] (B,H) fp32 = dG_t[:, K slice s] W_hh[K slice s, :].  tm_dg: dG (T, B, 4H) as a 3-D map, box

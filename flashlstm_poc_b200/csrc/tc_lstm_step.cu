@@ -512,12 +512,21 @@ int pick_bn(int m_tiles, int N, int splits, int sms) {
 
 }  // namespace
 
-int plan_step(int B, int H, int sms, StepPlan *plan) {
+int plan_step(int B, int H, int sms, size_t smem_limit, StepPlan *plan) {
     *plan = StepPlan{};
     if (H % 64 != 0 || H < 64) return set_error(FLSTM_ERR_UNSUPPORTED, "hidden size must be a multiple of 64");
-    int min_batch = 256;
-    if (const char *env = std::getenv("FLSTM_STEP_MIN_BATCH")) min_batch = std::atoi(env);
-    plan->use = min_batch > 0 && B >= min_batch && H % 128 == 0;  // the backward tiles are 128 or 256 units wide
+    // Measured crossover (H = 1024 / 2048 / 4096, B = 8..2048): the persistent kernels win exactly while every
+    // CTA has a single batch tile per step; with two or more tiles per CTA the per-step GEMM launches win.
+    // FLSTM_STEP_MIN_BATCH=n replaces the rule by "B >= n" (0: never).
+    bool use;
+    if (const char *env = std::getenv("FLSTM_STEP_MIN_BATCH")) {
+        const int min_batch = std::atoi(env);
+        use = min_batch > 0 && B >= min_batch;
+    } else {
+        FwdPlan fp{};
+        use = plan_fwd(B, H, sms, smem_limit, &fp) != FLSTM_OK || fp.nt > 1;
+    }
+    plan->use = use && H % 128 == 0;  // the backward tiles are 128 or 256 units wide
     const int m_tiles = (B + BM - 1) / BM;
     plan->bn_fwd = pick_bn(m_tiles, 4 * H, 1, sms);
     // backward: K = 4H is long and N = H short; split K until the tiles fill the machine
@@ -525,6 +534,9 @@ int plan_step(int B, int H, int sms, StepPlan *plan) {
     while (splits < 8 && m_tiles * (H / 128) * splits * 2 <= sms && ((4 * H / BK) % (splits * 2)) == 0) splits *= 2;
     plan->splits = splits;
     plan->bn_bwd = pick_bn(m_tiles, H, splits, sms);
+    const size_t need_fwd = plan->bn_fwd == 256 ? StepShape<256, EPI_LSTM_FWD>::kSmemBytes : StepShape<128, EPI_LSTM_FWD>::kSmemBytes;
+    const size_t need_bwd = plan->bn_bwd == 256 ? StepShape<256, EPI_F32_PARTS>::kSmemBytes : StepShape<128, EPI_F32_PARTS>::kSmemBytes;
+    if (need_fwd > smem_limit || need_bwd > smem_limit) plan->use = false;  // the step kernels do not fit this device
     return FLSTM_OK;
 }
 

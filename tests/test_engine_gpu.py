@@ -73,20 +73,23 @@ def test_scaled_baseline_configs(name, scale):
     eng.close()
 
 
-@pytest.mark.parametrize("dtype,L,T,B,I,H,training", [
-    ("bf16", 2, 5, 32, 2048, 2048, True),    # config 3's width: W_hh slices do not fit shared memory -> streamed from L2
-    ("f16", 1, 4, 8, 4096, 4096, False),     # config 4: two row tiles per CTA, streamed weights, inference
-    ("f16", 1, 3, 1, 4096, 4096, False),     # config 4 at batch 1
-    ("bf16", 2, 4, 256, 256, 1024, True),    # wide batch (config 5's regime): one GEMM launch per step, no K split
-    ("f16", 1, 5, 300, 128, 256, True),      # wide batch, ragged last 128-row tile, backward K split 8 ways
-    ("bf16", 1, 3, 256, 128, 512, False),    # wide batch, inference
-    ("f16", 1, 6, 200, 192, 192, True),      # ragged batch tile, K chunks not a multiple of 4
-    ("bf16", 2, 4, 256, 256, 1024, "persistent"),  # the persistent kernels with several batch tiles per CTA
+@pytest.mark.parametrize("dtype,L,T,B,I,H,training,path", [
+    ("bf16", 2, 5, 32, 2048, 2048, True, "auto"),    # config 3's width: W_hh slices do not fit shared memory -> streamed from L2
+    ("f16", 1, 4, 8, 4096, 4096, False, "auto"),     # config 4: two row tiles per CTA, streamed weights, inference
+    ("f16", 1, 3, 1, 4096, 4096, False, "auto"),     # config 4 at batch 1
+    ("bf16", 2, 4, 256, 256, 1024, True, "auto"),    # wide batch (config 5's regime): one GEMM launch per step, no K split
+    ("bf16", 1, 3, 64, 256, 2048, True, "auto"),     # two batch tiles per CTA at H=2048: the planner takes the per-step path
+    ("f16", 1, 5, 300, 128, 256, True, "step"),      # per-step path, ragged last 128-row tile, backward K split 8 ways
+    ("bf16", 1, 3, 256, 128, 512, False, "step"),    # per-step path, inference
+    ("f16", 1, 4, 40, 128, 128, True, "step"),       # per-step path with a single, mostly empty 128-row tile
+    ("f16", 1, 6, 200, 192, 192, True, "auto"),      # ragged batch tile, K chunks not a multiple of 4
+    ("bf16", 2, 4, 256, 256, 1024, True, "persistent"),  # the persistent kernels with several batch tiles per CTA
 ])
-def test_wide_and_large_batch_regimes(dtype, L, T, B, I, H, training, monkeypatch):
-    if training == "persistent":
+def test_wide_and_large_batch_regimes(dtype, L, T, B, I, H, training, path, monkeypatch):
+    if path == "persistent":
         monkeypatch.setenv("FLSTM_STEP_MIN_BATCH", "0")  # keep wide batches on the persistent kernels
-        training = True
+    elif path == "step":
+        monkeypatch.setenv("FLSTM_STEP_MIN_BATCH", "1")  # per-step GEMM launches whatever the planner would pick
     w = Workload("t", dtype, L, I, H, B, T, seed=17, state_std=0.2, training=training)
     inp = make_inputs(w)
     got, eng = run_engine(w, inp, backend="tc")
@@ -231,7 +234,13 @@ def test_step_ranges_equal_one_call(dtype, L, H, backend, B=16):
 
 def test_step_ranges_wide_batch():
     """The same for the wide-batch path, whose fp32 partial sums of dh carry over between ranges."""
-    test_step_ranges_equal_one_call("bf16", 2, 128, "tc", B=256)
+    import os
+
+    os.environ["FLSTM_STEP_MIN_BATCH"] = "1"
+    try:
+        test_step_ranges_equal_one_call("bf16", 2, 128, "tc", B=256)
+    finally:
+        del os.environ["FLSTM_STEP_MIN_BATCH"]
 
 
 def test_step_ranges_must_be_in_order():

@@ -27,13 +27,13 @@ def plan(lib, B, H, training=1, sms=SMS, smem=SMEM):
 def test_plans_fit_the_machine(lib, B, H):
     st, p = plan(lib, B, H, training=1 if H <= 2048 else 0)
     assert st == 0, lib.flstm_last_error()
-    if B >= 256 and H % 128 == 0:
-        # wide batches: one output-tiled GEMM launch per step; K = 4H split while tiles are scarce
-        assert p.step_path == 1 and p.fwd_grid == 0
+    if p.step_path:
+        # one output-tiled GEMM launch per step; K = 4H split while tiles are scarce
+        assert H % 128 == 0 and p.fwd_grid == 0
         assert p.step_bn_fwd in (128, 256) and p.step_bn_bwd in (128, 256) and (4 * H) % p.step_bn_fwd == 0
         assert H % p.step_bn_bwd == 0 and p.step_splits in (1, 2, 4, 8) and (4 * H // 64) % p.step_splits == 0
         return
-    assert p.step_path == 0
+    assert p.fwd_tiles_per_group == 1 or H % 128 != 0  # the persistent kernels keep the single-tile shapes
     # forward: co-resident grid, covers all row tiles and all sequences
     assert 1 <= p.fwd_grid <= SMS and p.fwd_smem_bytes <= SMEM
     cta_rows = p.fwd_grid // p.fwd_batch_groups
@@ -58,6 +58,15 @@ def test_benchmark_configuration_plan(lib):
     assert (p.fwd_grid, p.fwd_batch_tile, p.fwd_batch_groups, p.fwd_tiles_per_group) == (128, 32, 2, 1)
     assert p.fwd_weights_resident == 1 and p.fwd_chunks_per_stage == 16 and p.fwd_stages == 1
     assert (p.bwd_grid, p.bwd_cluster_size, p.bwd_weights_resident) == (128, 4, 1)
+
+
+@pytest.mark.parametrize("B,H,step", [(64, 1024, 0), (96, 1024, 1), (128, 1024, 0), (160, 1024, 1), (2048, 1024, 1),
+                                      (32, 2048, 0), (64, 2048, 1), (256, 2048, 1), (8, 4096, 0), (64, 4096, 1)])
+def test_path_choice_follows_the_measured_crossover(lib, B, H, step):
+    """Measured on B200: the persistent kernels win while a CTA has one batch tile per step, the per-step GEMM
+    launches win from two tiles per CTA on (these ten shapes were timed both ways)."""
+    st, p = plan(lib, B, H, training=0 if H == 4096 else 1)
+    assert st == 0 and p.step_path == step
 
 
 def test_wide_batch_plans(lib):
