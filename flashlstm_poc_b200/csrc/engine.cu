@@ -71,10 +71,33 @@ Engine::~Engine() {
     dev_free(db_part);
     dev_free(sync_words);
     dev_free(trace);
+    for (size_t i = 1; i < lanes.size(); ++i)
+        if (lanes[i]) cudaStreamDestroy(lanes[i]);
+    for (auto ev : lane_events) cudaEventDestroy(ev);
     if (comm) comm_destroy(comm);
     if (comm_stream) cudaStreamDestroy(comm_stream);
     if (comm_fork) cudaEventDestroy(comm_fork);
     if (comm_join) cudaEventDestroy(comm_join);
+}
+
+int Engine::ensure_lanes(cudaStream_t s) {
+    if (lanes.size() != layers.size()) {
+        lanes.assign(layers.size(), nullptr);
+        for (size_t i = 1; i < lanes.size(); ++i)
+            FLSTM_CUDA_TRY(cudaStreamCreateWithFlags(&lanes[i], cudaStreamNonBlocking));
+    }
+    lanes[0] = s;
+    lane_events_used = 0;
+    return FLSTM_OK;
+}
+
+cudaEvent_t Engine::next_lane_event() {
+    if (lane_events_used == lane_events.size()) {
+        cudaEvent_t ev = nullptr;
+        if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        lane_events.push_back(ev);
+    }
+    return lane_events[lane_events_used++];
 }
 
 void Engine::release_time_buffers() {
@@ -167,41 +190,72 @@ int Engine::forward_range(size_t T, size_t t0, size_t t1, const void *x, const v
     } else if (fwd_progress != t0) {
         return set_error(FLSTM_ERR_INVALID, "forward ranges must be contiguous and ascending (expected start %zu, got %zu)", fwd_progress, t0);
     }
-    for (int li = 0; li < L; ++li) {
-        auto &l = layers[li];
-        if (t0 == 0) {
-            // initial state -> slot 0 of the state tensors
+    if (t0 == 0) {
+        // initial state -> slot 0 of the state tensors
+        for (int li = 0; li < L; ++li) {
+            auto &l = layers[li];
             if (h0) FLSTM_CUDA_TRY(cudaMemcpyAsync(l.hs, byte_ptr(h0) + li * slab * es, slab * es, cudaMemcpyDeviceToDevice, s));
             else FLSTM_CUDA_TRY(cudaMemsetAsync(l.hs, 0, slab * es, s));
             const size_t ces = cell_io_f32 ? sizeof(float) : es;
             if (c0) { FLSTM_TRY(simt::convert(cell_io_f32 ? FLSTM_DTYPE_F32 : cfg.dtype, byte_ptr(c0) + li * slab * ces, FLSTM_DTYPE_F32, l.cs, slab, s)); ++launches; }
             else FLSTM_CUDA_TRY(cudaMemsetAsync(l.cs, 0, slab * sizeof(float), s));
         }
-        const void *x_l = li == 0 ? x : byte_ptr(layers[li - 1].hs) + slab * es;
-        void *y_out = (li == L - 1) ? y : nullptr;
-        if (backend == FLSTM_BACKEND_TC) {
-            FLSTM_TRY(tc::forward_layer(*this, li, t0, t1, x_l, y_out, s));
-        } else {
-            // input projection for the steps of the range at once: P = X W_ih^T + (b_ih + b_hh)
-            size_t m0 = timer.mark(s);
-            FLSTM_TRY(simt::gemm(cfg.dtype, cfg.dtype, (t1 - t0) * B, 4 * H, l.in_size, byte_ptr(x_l) + t0 * B * l.in_size * es,
-                                 l.in_size, true, l.w_ih, l.in_size, true, byte_ptr(l.gates) + t0 * B * 4 * H * es, 4 * H,
-                                 l.bias, s));
-            ++launches;
-            size_t m1 = timer.mark(s);
-            for (size_t t = t0; t < t1; ++t) {
-                FLSTM_TRY(simt::step_forward(cfg.dtype, B, H, byte_ptr(l.hs) + t * slab * es, l.w_hh,
-                                             byte_ptr(l.gates) + t * B * 4 * H * es, l.cs + t * slab,
-                                             l.cs + (t + 1) * slab, byte_ptr(l.hs) + (t + 1) * slab * es,
-                                             y_out ? byte_ptr(y_out) + t * slab * es : nullptr, s));
+    }
+    const size_t wave = backend == FLSTM_BACKEND_TC ? tc::wavefront_chunk(*this, t1 - t0) : 0;
+    if (wave) {
+        // Cross-layer wavefront: layer l works on time chunk k while layer l-1 is already on chunk k+1.
+        FLSTM_TRY(ensure_lanes(s));
+        cudaEvent_t fork = next_lane_event();
+        if (!fork) return set_error(FLSTM_ERR_CUDA, "cudaEventCreate failed");
+        FLSTM_CUDA_TRY(cudaEventRecord(fork, s));
+        for (int li = 1; li < L; ++li) FLSTM_CUDA_TRY(cudaStreamWaitEvent(lanes[li], fork, 0));
+        for (size_t c0s = t0; c0s < t1; c0s += wave) {
+            const size_t c1s = c0s + wave < t1 ? c0s + wave : t1;
+            cudaEvent_t prev = nullptr;
+            for (int li = 0; li < L; ++li) {
+                if (prev) FLSTM_CUDA_TRY(cudaStreamWaitEvent(lanes[li], prev, 0));
+                const void *x_l = li == 0 ? x : byte_ptr(layers[li - 1].hs) + slab * es;
+                FLSTM_TRY(tc::forward_layer(*this, li, c0s, c1s, x_l, (li == L - 1) ? y : nullptr, lanes[li]));
+                if (li + 1 < L || c1s == t1) {
+                    prev = next_lane_event();
+                    if (!prev) return set_error(FLSTM_ERR_CUDA, "cudaEventCreate failed");
+                    FLSTM_CUDA_TRY(cudaEventRecord(prev, lanes[li]));
+                    if (c1s == t1 && li > 0) FLSTM_CUDA_TRY(cudaStreamWaitEvent(s, prev, 0));  // join
+                }
             }
-            launches += t1 - t0;
-            size_t m2 = timer.mark(s);
-            timer.span(PH_PROJ, m0, m1);
-            timer.span(PH_RECUR_FWD, m1, m2);
         }
-        if (t1 == T) {
-            const size_t ces = cell_io_f32 ? sizeof(float) : es;
+    } else {
+        for (int li = 0; li < L; ++li) {
+            auto &l = layers[li];
+            const void *x_l = li == 0 ? x : byte_ptr(layers[li - 1].hs) + slab * es;
+            void *y_out = (li == L - 1) ? y : nullptr;
+            if (backend == FLSTM_BACKEND_TC) {
+                FLSTM_TRY(tc::forward_layer(*this, li, t0, t1, x_l, y_out, s));
+            } else {
+                // input projection for the steps of the range at once: P = X W_ih^T + (b_ih + b_hh)
+                size_t m0 = timer.mark(s);
+                FLSTM_TRY(simt::gemm(cfg.dtype, cfg.dtype, (t1 - t0) * B, 4 * H, l.in_size, byte_ptr(x_l) + t0 * B * l.in_size * es,
+                                     l.in_size, true, l.w_ih, l.in_size, true, byte_ptr(l.gates) + t0 * B * 4 * H * es, 4 * H,
+                                     l.bias, s));
+                ++launches;
+                size_t m1 = timer.mark(s);
+                for (size_t t = t0; t < t1; ++t) {
+                    FLSTM_TRY(simt::step_forward(cfg.dtype, B, H, byte_ptr(l.hs) + t * slab * es, l.w_hh,
+                                                 byte_ptr(l.gates) + t * B * 4 * H * es, l.cs + t * slab,
+                                                 l.cs + (t + 1) * slab, byte_ptr(l.hs) + (t + 1) * slab * es,
+                                                 y_out ? byte_ptr(y_out) + t * slab * es : nullptr, s));
+                }
+                launches += t1 - t0;
+                size_t m2 = timer.mark(s);
+                timer.span(PH_PROJ, m0, m1);
+                timer.span(PH_RECUR_FWD, m1, m2);
+            }
+        }
+    }
+    if (t1 == T) {
+        const size_t ces = cell_io_f32 ? sizeof(float) : es;
+        for (int li = 0; li < L; ++li) {
+            auto &l = layers[li];
             if (hn) FLSTM_CUDA_TRY(cudaMemcpyAsync(byte_ptr(hn) + li * slab * es, byte_ptr(l.hs) + T * slab * es, slab * es, cudaMemcpyDeviceToDevice, s));
             if (cn) { FLSTM_TRY(simt::convert(FLSTM_DTYPE_F32, l.cs + T * slab, cell_io_f32 ? FLSTM_DTYPE_F32 : cfg.dtype, byte_ptr(cn) + li * slab * ces, slab, s)); ++launches; }
         }
@@ -235,6 +289,55 @@ int Engine::backward_range(size_t T, size_t t0, size_t t1, const void *dy, const
     const int L = (int)layers.size();
     const size_t slab = B * H;
     const size_t n = t1 - t0;  // steps in the range
+    const size_t wave = backend == FLSTM_BACKEND_TC ? tc::wavefront_chunk(*this, n) : 0;
+    if (wave) {
+        // Cross-layer wavefront, descending in time: layer l takes chunk k as soon as layer l+1 has produced
+        // its dX for that chunk; weight gradients of a layer follow its last chunk on the layer's own lane.
+        FLSTM_TRY(ensure_lanes(s));
+        cudaEvent_t fork = next_lane_event();
+        if (!fork) return set_error(FLSTM_ERR_CUDA, "cudaEventCreate failed");
+        FLSTM_CUDA_TRY(cudaEventRecord(fork, s));
+        for (int li = 1; li < L; ++li) FLSTM_CUDA_TRY(cudaStreamWaitEvent(lanes[li], fork, 0));
+        for (size_t c1s = t1; c1s > t0;) {
+            const size_t c0s = (c1s - t0 > wave) ? c1s - wave : t0;
+            cudaEvent_t above = nullptr;  // dX of this chunk from the layer above
+            for (int li = L - 1; li >= 0; --li) {
+                auto &l = layers[li];
+                if (above) FLSTM_CUDA_TRY(cudaStreamWaitEvent(lanes[li], above, 0));
+                const void *x_l = li == 0 ? x_saved : byte_ptr(layers[li - 1].hs) + slab * es;
+                const void *dy_l = (li == L - 1) ? dy : layers[li + 1].dx;
+                void *dx_l = li == 0 ? dx : l.dx;
+                cudaEvent_t ready = nullptr;
+                if (li > 0) {
+                    ready = next_lane_event();
+                    if (!ready) return set_error(FLSTM_ERR_CUDA, "cudaEventCreate failed");
+                }
+                FLSTM_TRY(tc::backward_layer(*this, li, T, c0s, c1s, x_l, dy_l, dhn ? byte_ptr(dhn) + li * slab * es : nullptr,
+                                             dcn ? byte_ptr(dcn) + li * slab * es : nullptr, dx_l, dh0 ? dh0 + li * slab : nullptr,
+                                             dc0 ? dc0 + li * slab : nullptr, lanes[li], ready));
+                above = ready;
+                if (c0s == 0 && comm) {
+                    // reduce this layer's gradients while the layers below keep back-propagating
+                    FLSTM_CUDA_TRY(cudaEventRecord(comm_fork, lanes[li]));
+                    FLSTM_CUDA_TRY(cudaStreamWaitEvent(comm_stream, comm_fork, 0));
+                    FLSTM_TRY(comm_allreduce_sum_f32(comm, grads + l.grad_offset, l.grad_count, comm_stream));
+                }
+                if (c0s == t0 && li > 0) {  // join the lane after its last chunk of the range
+                    cudaEvent_t done = next_lane_event();
+                    if (!done) return set_error(FLSTM_ERR_CUDA, "cudaEventCreate failed");
+                    FLSTM_CUDA_TRY(cudaEventRecord(done, lanes[li]));
+                    FLSTM_CUDA_TRY(cudaStreamWaitEvent(s, done, 0));
+                }
+            }
+            c1s = c0s;
+        }
+        if (comm && t0 == 0) {
+            FLSTM_CUDA_TRY(cudaEventRecord(comm_join, comm_stream));
+            FLSTM_CUDA_TRY(cudaStreamWaitEvent(s, comm_join, 0));
+        }
+        bwd_progress = t0;
+        return FLSTM_OK;
+    }
     for (int li = L - 1; li >= 0; --li) {
         auto &l = layers[li];
         const void *x_l = li == 0 ? x_saved : byte_ptr(layers[li - 1].hs) + slab * es;

@@ -75,6 +75,13 @@ struct Engine {
     long long *trace = nullptr;  // device: [2 (fwd,bwd)][trace_steps][16] clock stamps of CTA 0
     int trace_steps = 0;
     void *tc_state = nullptr;  // tensor-core path: cached tensor maps etc. (tc_engine.cu)
+    // Cross-layer wavefront (wide-batch path with stacked layers): layer l > 0 runs its time chunks on
+    // lanes[l] one chunk behind layer l-1, so independent per-step kernels of different layers share the GPU.
+    std::vector<cudaStream_t> lanes;        // lanes[0] is the caller's stream (not owned)
+    std::vector<cudaEvent_t> lane_events;   // pool, reused call after call in stream order
+    size_t lane_events_used = 0;
+    int ensure_lanes(cudaStream_t s);
+    cudaEvent_t next_lane_event();
 
     ~Engine();
     int allocate(size_t t_cap);
@@ -110,8 +117,12 @@ int on_capacity_change(Engine &e);
 int set_weights(Engine &e, int layer, const float *w_ih, const float *w_hh, const float *b_ih,
                 const float *b_hh, cudaStream_t s);
 int forward_layer(Engine &e, int layer, size_t t0, size_t t1, const void *x_l, void *y_out, cudaStream_t s);
+// `dx_ready` (optional) is recorded on `s` once dx_l of the range is complete, before the weight gradients
 int backward_layer(Engine &e, int layer, size_t T, size_t t0, size_t t1, const void *x_l, const void *dy_l,
-                   const void *dhn_l, const void *dcn_l, void *dx_l, float *dh0_l, float *dc0_l, cudaStream_t s);
+                   const void *dhn_l, const void *dcn_l, void *dx_l, float *dh0_l, float *dc0_l, cudaStream_t s,
+                   cudaEvent_t dx_ready = nullptr);
+// steps per wavefront chunk for a range of n steps; 0 = no cross-layer wavefront for this engine
+size_t wavefront_chunk(const Engine &e, size_t n);
 }  // namespace tc
 
 // Communicator (comm.cu): NCCL loaded at run time with dlopen.

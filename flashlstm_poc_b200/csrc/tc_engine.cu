@@ -154,7 +154,8 @@ int init(Engine &e) {
     FLSTM_CUDA_TRY(cudaMalloc(&raw, 1024 * sizeof(unsigned int)));
     e.sync_words = static_cast<unsigned int *>(raw);
     FLSTM_CUDA_TRY(cudaMemset(raw, 0, 1024 * sizeof(unsigned int)));
-    FLSTM_CUDA_TRY(cudaMalloc(&raw, (size_t)simt::column_sum_scratch_floats(4 * e.cfg.hidden_size) * sizeof(float)));
+    // one bias-gradient scratch per layer: with the cross-layer wavefront two layers may reduce at once
+    FLSTM_CUDA_TRY(cudaMalloc(&raw, e.layers.size() * (size_t)simt::column_sum_scratch_floats(4 * e.cfg.hidden_size) * sizeof(float)));
     e.db_part = static_cast<float *>(raw);
     FLSTM_CUDA_TRY(cudaMallocHost(&raw, sizeof(unsigned int)));
     st->err_host = static_cast<unsigned int *>(raw);
@@ -314,8 +315,21 @@ static int backward_steps(Engine &e, int li, size_t T, size_t t0, size_t t1, con
     return FLSTM_OK;
 }
 
+// Opt-in (FLSTM_WAVE_CHUNK=<steps per chunk>): measured neutral on configs 3 and 5, which already run at the
+// board's power cap -- the overlap only lowers the SM clock (1.9 -> 1.6 GHz) -- so the default stays the
+// layer-by-layer schedule.
+size_t wavefront_chunk(const Engine &e, size_t n) {
+    TcState *st = static_cast<TcState *>(e.tc_state);
+    if (!st || !st->step.use || e.layers.size() < 2 || e.timer.enabled) return 0;
+    const char *env = std::getenv("FLSTM_WAVE_CHUNK");
+    if (!env) return 0;
+    const long v = std::atol(env);
+    if (v <= 0) return 0;
+    return (size_t)v < n ? (size_t)v : 0;  // a single chunk is the plain layer-by-layer schedule
+}
+
 int backward_layer(Engine &e, int li, size_t T, size_t t0, size_t t1, const void *x_l, const void *dy_l, const void *dhn_l,
-                   const void *dcn_l, void *dx_l, float *dh0_l, float *dc0_l, cudaStream_t s) {
+                   const void *dcn_l, void *dx_l, float *dh0_l, float *dc0_l, cudaStream_t s, cudaEvent_t dx_ready) {
     TcState *st = state(e);
     FLSTM_TRY(check_async_error(e));
     if (!st->bwd_ok) return set_error(FLSTM_ERR_UNSUPPORTED, "tensor-core backward is not planned for this engine");
@@ -350,6 +364,16 @@ int backward_layer(Engine &e, int li, size_t T, size_t t0, size_t t1, const void
     e.launches += 1;
     }
     size_t m1 = e.timer.mark(s), m2 = m1;
+    if (dx_l) {
+        // dX = dG W_ih for the steps of the range: W_ih (rows tile-interleaved, like dG's columns) is read as stored
+        FLSTM_TRY(gemm(e.cfg.dtype, e.cfg.dtype, n * B, l.in_size, 4 * H, byte_ptr(l.dg) + t0 * B * 4 * H * es, 4 * H, false,
+                       l.w_ih, l.in_size, true, byte_ptr(dx_l) + t0 * B * l.in_size * es, l.in_size, nullptr, 0, err, st->sms,
+                       s));
+        ++e.launches;
+        m2 = e.timer.mark(s);
+    }
+    if (dx_ready) FLSTM_CUDA_TRY(cudaEventRecord(dx_ready, s));  // the layer below may start on this range
+    size_t m3 = m2;
     if (t0 == 0) {
         // dW = dG^T [X | H_prev] over the whole sequence: both operands read as stored (reduction dim
         // T*B outermost); rows of the product are written back in torch gate order
@@ -357,21 +381,14 @@ int backward_layer(Engine &e, int li, size_t T, size_t t0, size_t t1, const void
                        l.dw_ih, l.in_size, nullptr, (int)H, err, st->sms, s));
         FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, H, T * B, l.dg, 4 * H, true, l.hs, H, true, l.dw_hh, H, nullptr,
                        (int)H, err, st->sms, s));
-        FLSTM_TRY(simt::column_sum_two_pass(e.cfg.dtype, l.dg, T * B, 4 * H, e.db_part, l.db, (int)H, s));
+        FLSTM_TRY(simt::column_sum_two_pass(e.cfg.dtype, l.dg, T * B, 4 * H,
+                                            e.db_part + (size_t)li * simt::column_sum_scratch_floats(4 * H), l.db, (int)H, s));
         e.launches += 4;
-        m2 = e.timer.mark(s);
+        m3 = e.timer.mark(s);
     }
-    if (dx_l) {
-        // dX = dG W_ih for the steps of the range: W_ih (rows tile-interleaved, like dG's columns) is read as stored
-        FLSTM_TRY(gemm(e.cfg.dtype, e.cfg.dtype, n * B, l.in_size, 4 * H, byte_ptr(l.dg) + t0 * B * 4 * H * es, 4 * H, false,
-                       l.w_ih, l.in_size, true, byte_ptr(dx_l) + t0 * B * l.in_size * es, l.in_size, nullptr, 0, err, st->sms,
-                       s));
-        ++e.launches;
-    }
-    size_t m3 = e.timer.mark(s);
     e.timer.span(PH_BPTT, m0, m1);
-    e.timer.span(PH_WGRAD, m1, m2);
-    e.timer.span(PH_XGRAD, m2, m3);
+    e.timer.span(PH_XGRAD, m1, m2);
+    e.timer.span(PH_WGRAD, m2, m3);
     FLSTM_CUDA_TRY(cudaMemcpyAsync(st->err_host, err, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
     return FLSTM_OK;
 }
