@@ -16,7 +16,7 @@ ENGINE_SYMBOLS = [
     "flstm_engine_backward", "flstm_engine_forward_range", "flstm_engine_backward_range", "flstm_engine_grad_ptrs", "flstm_engine_grad_buffer", "flstm_engine_cache_ptrs",
     "flstm_engine_set_cell_io_f32", "flstm_engine_backend", "flstm_comm_unique_id", "flstm_engine_attach_comm",
     "flstm_engine_enable_timing", "flstm_engine_phase_ms", "flstm_engine_launch_count", "flstm_tc_gemm",
-    "flstm_engine_enable_trace", "flstm_engine_read_trace", "flstm_bias_grad", "flstm_tc_plan",
+    "flstm_engine_enable_trace", "flstm_engine_read_trace", "flstm_bias_grad", "flstm_tc_plan", "flstm_engine_wait", "flstm_engine_abort_comm",
     "flstm_bias_grad_static",
     "flstm_last_error",
     "flstm_version",
@@ -102,6 +102,8 @@ def load() -> ctypes.CDLL:
     lib.flstm_engine_enable_trace.argtypes = [vp, ci]
     lib.flstm_engine_read_trace.argtypes = [vp, vp, sz]
     lib.flstm_tc_plan.argtypes = [sz, sz, ci, ci, sz, ctypes.POINTER(TcPlanInfo)]
+    lib.flstm_engine_wait.argtypes = [vp, vp, ctypes.c_uint]
+    lib.flstm_engine_abort_comm.argtypes = [vp]
     lib.flstm_bias_grad.argtypes = [ci, vp, sz, sz, ci, vp, vp]
     lib.flstm_bias_grad_static.argtypes = [ci, vp, sz, sz, ci, vp, vp]
     lib.flstm_tc_gemm.argtypes = [ci, ci, sz, sz, sz, vp, vp, vp, sz, vp, ci, vp]

@@ -94,6 +94,15 @@ void comm_destroy(Comm *c) {
     delete c;
 }
 
+void comm_abort(Comm *c) {
+    if (!c) return;
+    if (c->comm && api().ok) {
+        if (api().CommAbort) api().CommAbort(c->comm);
+        else api().CommDestroy(c->comm);
+    }
+    delete c;
+}
+
 int comm_allreduce_sum_f32(Comm *c, float *buf, size_t count, cudaStream_t s) {
     if (!c || !c->comm) return set_error(FLSTM_ERR_COMM, "no communicator");
     int r = api().AllReduce(buf, buf, count, kNcclFloat32, kNcclSum, c->comm, s);

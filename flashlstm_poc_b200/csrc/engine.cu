@@ -8,8 +8,10 @@
 // asynchronously on the caller's stream.
 #include "engine.h"
 
+#include <chrono>
 #include <cstring>
 #include <new>
+#include <thread>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -282,6 +284,7 @@ int Engine::backward_range(size_t T, size_t t0, size_t t1, const void *dy, const
     const size_t B = cfg.batch, H = cfg.hidden_size, es = dtype_size(cfg.dtype);
     if (T == 0 || B == 0 || H == 0) return FLSTM_OK;
     if (!cfg.training) return set_error(FLSTM_ERR_INVALID, "engine was created with training = 0");
+    if (comm_aborted) return set_error(FLSTM_ERR_COMM, "the communicator was aborted after a step missed its deadline; attach a new one");
     if (last_T != T) return set_error(FLSTM_ERR_INVALID, "backward(T=%zu) does not follow a forward of the same length (last T=%zu)", T, last_T);
     if (!dy) return set_error(FLSTM_ERR_INVALID, "dy is null");
     if (t0 >= t1 || t1 > T) return set_error(FLSTM_ERR_INVALID, "bad step range [%zu, %zu) of %zu", t0, t1, T);
@@ -599,10 +602,54 @@ int flstm_engine_attach_comm(flstm_engine *engine, const void *id128, int rank, 
     cudaSetDevice(e.device);
     int st = flstm_b200::comm_create(id128, rank, world_size, &e.comm);
     if (st != FLSTM_OK) return st;
-    if (cudaStreamCreateWithFlags(&e.comm_stream, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaEventCreateWithFlags(&e.comm_fork, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&e.comm_join, cudaEventDisableTiming) != cudaSuccess)
+    e.comm_aborted = false;
+    if (!e.comm_stream &&
+        (cudaStreamCreateWithFlags(&e.comm_stream, cudaStreamNonBlocking) != cudaSuccess ||
+         cudaEventCreateWithFlags(&e.comm_fork, cudaEventDisableTiming) != cudaSuccess ||
+         cudaEventCreateWithFlags(&e.comm_join, cudaEventDisableTiming) != cudaSuccess))
         return set_error(FLSTM_ERR_CUDA, "could not create the communication stream");
+    return FLSTM_OK;
+}
+
+int flstm_engine_abort_comm(flstm_engine *engine) {
+    if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    Engine &e = engine->impl;
+    if (e.comm) {
+        flstm_b200::comm_abort(e.comm);
+        e.comm = nullptr;
+        e.comm_aborted = true;
+    }
+    return FLSTM_OK;
+}
+
+int flstm_engine_wait(flstm_engine *engine, cudaStream_t stream, unsigned int timeout_ms) {
+    if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    Engine &e = engine->impl;
+    cudaSetDevice(e.device);
+    cudaEvent_t done = nullptr;
+    FLSTM_CUDA_TRY(cudaEventCreateWithFlags(&done, cudaEventDisableTiming));
+    cudaError_t err = cudaEventRecord(done, stream);
+    const auto start = std::chrono::steady_clock::now();
+    bool finished = false;
+    while (err == cudaSuccess) {
+        err = cudaEventQuery(done);
+        if (err == cudaSuccess) { finished = true; break; }
+        if (err != cudaErrorNotReady) break;
+        err = cudaSuccess;
+        const auto waited = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - start);
+        if (waited.count() >= (long long)timeout_ms) break;
+        std::this_thread::sleep_for(std::chrono::microseconds(200));
+    }
+    cudaEventDestroy(done);
+    if (err != cudaSuccess && err != cudaErrorNotReady)
+        return set_error(FLSTM_ERR_CUDA, "waiting for the step failed: %s", cudaGetErrorString(err));
+    if (!finished) {
+        const bool had_comm = e.comm != nullptr;
+        flstm_engine_abort_comm(engine);
+        return set_error(FLSTM_ERR_TIMEOUT, "the step did not finish within %u ms%s", timeout_ms,
+                         had_comm ? "; the communicator was aborted" : "");
+    }
+    if (e.backend == FLSTM_BACKEND_TC) FLSTM_TRY(flstm_b200::tc::poll_error(e));
     return FLSTM_OK;
 }
 

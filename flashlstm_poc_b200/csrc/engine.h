@@ -70,6 +70,7 @@ struct Engine {
     const void *x_saved = nullptr;  // layer-0 input of the last forward (caller keeps it alive)
     PhaseTimer timer;
     Comm *comm = nullptr;
+    bool comm_aborted = false;  // the watchdog gave up on a step: no collective until a new communicator is attached
     cudaStream_t comm_stream = nullptr;
     cudaEvent_t comm_fork = nullptr, comm_join = nullptr;
     long long *trace = nullptr;  // device: [2 (fwd,bwd)][trace_steps][16] clock stamps of CTA 0
@@ -114,6 +115,7 @@ bool supported(const flstm_engine_config &cfg);
 int init(Engine &e);
 void destroy(Engine &e);
 int on_capacity_change(Engine &e);
+int poll_error(Engine &e);  // reports (and clears) a device-side wait that expired in an earlier launch
 int set_weights(Engine &e, int layer, const float *w_ih, const float *w_hh, const float *b_ih,
                 const float *b_hh, cudaStream_t s);
 int forward_layer(Engine &e, int layer, size_t t0, size_t t1, const void *x_l, void *y_out, cudaStream_t s);
@@ -129,6 +131,7 @@ size_t wavefront_chunk(const Engine &e, size_t n);
 int comm_unique_id(void *id128);
 int comm_create(const void *id128, int rank, int world, Comm **out);
 void comm_destroy(Comm *c);
+void comm_abort(Comm *c);  // ncclCommAbort (falls back to destroy when the library lacks it), frees c
 int comm_allreduce_sum_f32(Comm *c, float *buf, size_t count, cudaStream_t s);
 
 }  // namespace flstm_b200

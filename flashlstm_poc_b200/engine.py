@@ -207,6 +207,22 @@ class Engine:
         with torch.cuda.device(self.device):
             check(self.lib.flstm_engine_attach_comm(self._h, buf, rank, world_size))
 
+    def wait(self, timeout_s: float, stream: Optional[torch.cuda.Stream] = None) -> None:
+        """Host watchdog: block until the work enqueued so far on `stream` has finished, at most `timeout_s`
+        seconds.  Raises FlashLstmError (TIMEOUT) past the deadline, after aborting an attached communicator."""
+        with torch.cuda.device(self.device):
+            s = stream if stream is not None else torch.cuda.current_stream()
+            check(self.lib.flstm_engine_wait(self._h, s.cuda_stream, max(0, int(timeout_s * 1000))))
+
+    def abort_comm(self) -> None:
+        check(self.lib.flstm_engine_abort_comm(self._h))
+
+    @property
+    def config_key(self) -> tuple:
+        """What every rank of a data-parallel group must agree on (the per-rank batch may not differ either:
+        the weight-gradient allreduce assumes equal shards)."""
+        return (self.dtype, self.layers, self.batch, self.input_size, self.hidden_size, bool(self.training))
+
     @staticmethod
     def new_unique_id() -> bytes:
         buf = ctypes.create_string_buffer(128)

@@ -126,6 +126,16 @@ int flstm_engine_backend(const flstm_engine *engine);
 int flstm_comm_unique_id(void *id128);
 int flstm_engine_attach_comm(flstm_engine *engine, const void *id128, int rank, int world_size);
 
+/* Host watchdog for a step: waits until everything enqueued on `stream` so far has finished, polling
+ * without blocking in the driver, for at most `timeout_ms` milliseconds.  FLSTM_OK when the work is
+ * done (a device-side wait that expired inside a kernel is reported here as FLSTM_ERR_TIMEOUT too).
+ * When the deadline passes first the call returns FLSTM_ERR_TIMEOUT and, if a communicator is attached,
+ * aborts it (ncclCommAbort) so that a collective a lost peer will never join cannot block this process;
+ * backward then fails with FLSTM_ERR_COMM until flstm_engine_attach_comm is called again.
+ * flstm_engine_abort_comm does the abort alone.  The reference has no counterpart (single GPU). */
+int flstm_engine_wait(flstm_engine *engine, cudaStream_t stream, unsigned int timeout_ms);
+int flstm_engine_abort_comm(flstm_engine *engine);
+
 /* Per-phase device time of the last forward/backward pair in milliseconds (needs
  * flstm_engine_enable_timing(engine, 1); adds event records, no synchronisation).
  * out[0..5] = projection, recurrent forward, BPTT, weight-grad, input-grad, allreduce. */

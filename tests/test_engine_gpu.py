@@ -267,6 +267,36 @@ def test_cross_layer_wavefront(dtype, L, T, B, I, H, chunk, monkeypatch):
     assert_parity(wave, run_oracle(inp), dtype)
 
 
+def test_host_watchdog_wait():
+    """flstm_engine_wait: a deadline that cannot be met is reported as TIMEOUT without disturbing the work in
+    flight (nothing is cancelled on the GPU; only an attached communicator would be aborted); a generous one
+    returns once the step is done, and the results are the same as without any waiting."""
+    from flashlstm_poc_b200._lib import FlashLstmError
+    from flashlstm_poc_b200.engine import Engine
+
+    dev = torch.device("cuda", 0)
+    w = WORKLOADS["c2_fp16_h1024"].scaled(seq_len=256)
+    inp = make_inputs(w)
+    eng = Engine("f16", 1, w.batch, w.input_size, w.hidden_size, w.seq_len, device=dev)
+    eng.set_weights(0, inp.w_ih[0].to(dev), inp.w_hh[0].to(dev), inp.b_ih[0].to(dev), inp.b_hh[0].to(dev))
+    x, dy = inp.x.to(dev, torch.float16), inp.dy.to(dev, torch.float16)
+    y0, _, _ = eng.forward(x)
+    eng.backward(dy)
+    torch.cuda.synchronize()
+    y0 = y0.clone()
+    y1, _, _ = eng.forward(x)   # a few milliseconds of device work, enqueued asynchronously
+    eng.backward(dy)
+    with pytest.raises(FlashLstmError, match="did not finish within 0 ms"):
+        eng.wait(0.0)
+    eng.wait(30.0)              # returns as soon as the step is done
+    assert torch.cuda.current_stream().query()
+    assert torch.equal(y0, y1)
+    eng.abort_comm()            # no communicator attached: a no-op
+    eng.forward(x)
+    eng.wait(30.0)
+    eng.close()
+
+
 def test_step_ranges_must_be_in_order():
     from flashlstm_poc_b200._lib import FlashLstmError
     from flashlstm_poc_b200.engine import Engine

@@ -43,7 +43,26 @@ def _worker(rank, world, port, dtype, results):
             dx, dh0, dc0 = eng.backward(sh(inp.dy))
         torch.cuda.synchronize()
         grads = [[g.float().cpu().numpy() for g in eng.grads(l)] for l in range(w.layers)]
-        results[rank] = (eng.backend, grads, dx.float().cpu().numpy())
+        # Giving the communicator up and starting over, BETWEEN steps (nothing in flight on any rank, every
+        # rank does it: no collective is left without a peer).  A backward without communicator must refuse.
+        from flashlstm_poc_b200._lib import FlashLstmError
+
+        eng.wait(60.0)
+        eng.abort_comm()
+        eng.forward(sh(inp.x), sh(inp.h0), sh(inp.c0))
+        try:
+            eng.backward(sh(inp.dy))
+            refused = False
+        except FlashLstmError as exc:
+            refused = "aborted" in str(exc)
+        torch.cuda.synchronize()
+        dist.barrier()
+        attach_data_parallel(eng)
+        eng.forward(sh(inp.x), sh(inp.h0), sh(inp.c0))
+        eng.backward(sh(inp.dy))
+        torch.cuda.synchronize()
+        again = eng.grads(0)[0].float().cpu().numpy()
+        results[rank] = (eng.backend, grads, dx.float().cpu().numpy(), refused, bool(np.array_equal(again, grads[0][0])))
         eng.close()
     finally:
         dist.destroy_process_group()
@@ -66,8 +85,9 @@ def test_two_rank_gradients_match_full_batch_oracle(dtype):
         w = Workload("dp", dtype, 2, 64, 64, 16 * world, 12, seed=5, state_std=0.3)
         ref = run_oracle(make_inputs(w))
         for r in range(world):
-            backend, grads, dx = results[r]
+            backend, grads, dx, refused, same_after_reattach = results[r]
             assert backend == ("tc" if dtype == "f16" else "simt")
+            assert refused and same_after_reattach
             for l in range(w.layers):
                 for got, want in zip(grads[l], (ref["dw_ih"][l], ref["dw_hh"][l], ref["db"][l])):
                     err = orc.rel_l2_err(got, want)
