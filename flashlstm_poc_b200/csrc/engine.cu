@@ -82,6 +82,17 @@ Engine::~Engine() {
     if (comm_join) cudaEventDestroy(comm_join);
 }
 
+int Engine::reduce_grads(size_t offset, size_t count, cudaStream_t from) {
+    if (!comm || count == 0) return FLSTM_OK;
+    FLSTM_CUDA_TRY(cudaEventRecord(comm_fork, from));
+    FLSTM_CUDA_TRY(cudaStreamWaitEvent(comm_stream, comm_fork, 0));
+    size_t c0m = timer.mark(comm_stream);
+    FLSTM_TRY(comm_allreduce_sum_f32(comm, grads + offset, count, comm_stream));
+    size_t c1m = timer.mark(comm_stream);
+    timer.span(PH_ALLREDUCE, c0m, c1m);
+    return FLSTM_OK;
+}
+
 int Engine::ensure_lanes(cudaStream_t s) {
     if (lanes.size() != layers.size()) {
         lanes.assign(layers.size(), nullptr);
@@ -319,12 +330,6 @@ int Engine::backward_range(size_t T, size_t t0, size_t t1, const void *dy, const
                                              dcn ? byte_ptr(dcn) + li * slab * es : nullptr, dx_l, dh0 ? dh0 + li * slab : nullptr,
                                              dc0 ? dc0 + li * slab : nullptr, lanes[li], ready));
                 above = ready;
-                if (c0s == 0 && comm) {
-                    // reduce this layer's gradients while the layers below keep back-propagating
-                    FLSTM_CUDA_TRY(cudaEventRecord(comm_fork, lanes[li]));
-                    FLSTM_CUDA_TRY(cudaStreamWaitEvent(comm_stream, comm_fork, 0));
-                    FLSTM_TRY(comm_allreduce_sum_f32(comm, grads + l.grad_offset, l.grad_count, comm_stream));
-                }
                 if (c0s == t0 && li > 0) {  // join the lane after its last chunk of the range
                     cudaEvent_t done = next_lane_event();
                     if (!done) return set_error(FLSTM_ERR_CUDA, "cudaEventCreate failed");
@@ -392,15 +397,9 @@ int Engine::backward_range(size_t T, size_t t0, size_t t1, const void *dy, const
             timer.span(PH_WGRAD, m1, m2);
             timer.span(PH_XGRAD, m2, m3);
         }
-        if (comm && t0 == 0) {
-            // reduce this layer's gradients while the layers below keep back-propagating
-            FLSTM_CUDA_TRY(cudaEventRecord(comm_fork, s));
-            FLSTM_CUDA_TRY(cudaStreamWaitEvent(comm_stream, comm_fork, 0));
-            size_t c0m = timer.mark(comm_stream);
-            FLSTM_TRY(comm_allreduce_sum_f32(comm, grads + l.grad_offset, l.grad_count, comm_stream));
-            size_t c1m = timer.mark(comm_stream);
-            timer.span(PH_ALLREDUCE, c0m, c1m);
-        }
+        // reduce this layer's gradients while the layers below keep back-propagating (the tensor-core path
+        // starts its reductions itself, block by block, as the weight-gradient kernels finish)
+        if (t0 == 0 && backend != FLSTM_BACKEND_TC) FLSTM_TRY(reduce_grads(l.grad_offset, l.grad_count, s));
     }
     if (comm && t0 == 0) {
         FLSTM_CUDA_TRY(cudaEventRecord(comm_join, comm_stream));

@@ -81,6 +81,9 @@ struct Engine {
     std::vector<cudaStream_t> lanes;        // lanes[0] is the caller's stream (not owned)
     std::vector<cudaEvent_t> lane_events;   // pool, reused call after call in stream order
     size_t lane_events_used = 0;
+    // sum `count` floats of the flat gradient buffer at `offset` over the ranks, on the communication stream,
+    // after everything enqueued on `from` so far (no-op without a communicator)
+    int reduce_grads(size_t offset, size_t count, cudaStream_t from);
     int ensure_lanes(cudaStream_t s);
     cudaEvent_t next_lane_event();
 

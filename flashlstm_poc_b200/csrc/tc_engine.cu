@@ -363,32 +363,53 @@ int backward_layer(Engine &e, int li, size_t T, size_t t0, size_t t1, const void
     FLSTM_TRY(lstm_backward_persistent(e.cfg.dtype, st->bwd, t.tm_w, t.tm_dg, p, s));
     e.launches += 1;
     }
-    size_t m1 = e.timer.mark(s), m2 = m1;
-    if (dx_l) {
+    size_t m1 = e.timer.mark(s);
+    auto input_grad = [&]() -> int {
+        if (!dx_l) return FLSTM_OK;
         // dX = dG W_ih for the steps of the range: W_ih (rows tile-interleaved, like dG's columns) is read as stored
         FLSTM_TRY(gemm(e.cfg.dtype, e.cfg.dtype, n * B, l.in_size, 4 * H, byte_ptr(l.dg) + t0 * B * 4 * H * es, 4 * H, false,
                        l.w_ih, l.in_size, true, byte_ptr(dx_l) + t0 * B * l.in_size * es, l.in_size, nullptr, 0, err, st->sms,
                        s));
         ++e.launches;
-        m2 = e.timer.mark(s);
-    }
-    if (dx_ready) FLSTM_CUDA_TRY(cudaEventRecord(dx_ready, s));  // the layer below may start on this range
-    size_t m3 = m2;
-    if (t0 == 0) {
+        return FLSTM_OK;
+    };
+    auto weight_grads = [&]() -> int {
+        if (t0 != 0) return FLSTM_OK;
         // dW = dG^T [X | H_prev] over the whole sequence: both operands read as stored (reduction dim
-        // T*B outermost); rows of the product are written back in torch gate order
+        // T*B outermost); rows of the product are written back in torch gate order.  With a communicator
+        // each block of the layer's gradients starts its allreduce as soon as it is complete.
+        const size_t n_ih = 4 * H * l.in_size;
         FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, l.in_size, T * B, l.dg, 4 * H, true, x_l, l.in_size, true,
                        l.dw_ih, l.in_size, nullptr, (int)H, err, st->sms, s));
+        FLSTM_TRY(e.reduce_grads(l.grad_offset, n_ih, s));
         FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, H, T * B, l.dg, 4 * H, true, l.hs, H, true, l.dw_hh, H, nullptr,
                        (int)H, err, st->sms, s));
         FLSTM_TRY(simt::column_sum_two_pass(e.cfg.dtype, l.dg, T * B, 4 * H,
                                             e.db_part + (size_t)li * simt::column_sum_scratch_floats(4 * H), l.db, (int)H, s));
+        FLSTM_TRY(e.reduce_grads(l.grad_offset + n_ih, l.grad_count - n_ih, s));
         e.launches += 4;
+        return FLSTM_OK;
+    };
+    size_t m2, m3;
+    if (dx_ready) {
+        // wavefront: the layer below waits for dX of this range, so it goes first
+        FLSTM_TRY(input_grad());
+        FLSTM_CUDA_TRY(cudaEventRecord(dx_ready, s));
+        m2 = e.timer.mark(s);
+        FLSTM_TRY(weight_grads());
         m3 = e.timer.mark(s);
+        e.timer.span(PH_XGRAD, m1, m2);
+        e.timer.span(PH_WGRAD, m2, m3);
+    } else {
+        // weight gradients first: their allreduce then hides behind the input-gradient GEMM
+        FLSTM_TRY(weight_grads());
+        m2 = e.timer.mark(s);
+        FLSTM_TRY(input_grad());
+        m3 = e.timer.mark(s);
+        e.timer.span(PH_WGRAD, m1, m2);
+        e.timer.span(PH_XGRAD, m2, m3);
     }
     e.timer.span(PH_BPTT, m0, m1);
-    e.timer.span(PH_XGRAD, m1, m2);
-    e.timer.span(PH_WGRAD, m2, m3);
     FLSTM_CUDA_TRY(cudaMemcpyAsync(st->err_host, err, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
     return FLSTM_OK;
 }
