@@ -50,6 +50,8 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=0, help="override the workload's sequence length (profiling)")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's per-GPU batch (profiling)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying one captured CUDA graph")
+    ap.add_argument("--recompute", type=int, default=0,
+                    help="activation-checkpoint interval R (0 = full gate cache, the benchmark configuration)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cudnn", action="store_true")
@@ -226,6 +228,8 @@ def main():
                  backend=args.backend, device=dev)
     for l in range(w.layers):
         eng.set_weights(l, base.w_ih[l].to(dev), base.w_hh[l].to(dev), base.b_ih[l].to(dev), base.b_hh[l].to(dev))
+    if args.recompute:
+        eng.set_recompute_interval(args.recompute)
     if world > 1:
         from flashlstm_poc_b200.parallel import attach_data_parallel
 
@@ -347,6 +351,8 @@ def main():
         "mfu_vs_measured_bf16_peak": w.flops() / (ms_per_step * 1e-3) / (peaks["bf16_tflops"] * 1e12),
         "dense_gemm_tflops": gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None,
         "backend": eng.backend,
+        "recompute_interval": args.recompute,
+        "workspace_gib": eng.workspace_bytes / 2**30,
     }
 
     # ---- end to end through the reference-facing C ABI with host buffers

@@ -17,6 +17,7 @@ ENGINE_SYMBOLS = [
     "flstm_engine_set_cell_io_f32", "flstm_engine_backend", "flstm_comm_unique_id", "flstm_engine_attach_comm",
     "flstm_engine_enable_timing", "flstm_engine_phase_ms", "flstm_engine_launch_count", "flstm_tc_gemm",
     "flstm_engine_enable_trace", "flstm_engine_read_trace", "flstm_bias_grad", "flstm_tc_plan", "flstm_engine_wait", "flstm_engine_abort_comm",
+                  "flstm_engine_set_recompute_interval", "flstm_engine_workspace_bytes",
     "flstm_bias_grad_static",
     "flstm_last_error",
     "flstm_version",
@@ -104,6 +105,9 @@ def load() -> ctypes.CDLL:
     lib.flstm_tc_plan.argtypes = [sz, sz, ci, ci, sz, ctypes.POINTER(TcPlanInfo)]
     lib.flstm_engine_wait.argtypes = [vp, vp, ctypes.c_uint]
     lib.flstm_engine_abort_comm.argtypes = [vp]
+    lib.flstm_engine_set_recompute_interval.argtypes = [vp, sz]
+    lib.flstm_engine_workspace_bytes.argtypes = [vp]
+    lib.flstm_engine_workspace_bytes.restype = sz
     lib.flstm_bias_grad.argtypes = [ci, vp, sz, sz, ci, vp, vp]
     lib.flstm_bias_grad_static.argtypes = [ci, vp, sz, sz, ci, vp, vp]
     lib.flstm_tc_gemm.argtypes = [ci, ci, sz, sz, sz, vp, vp, vp, sz, vp, ci, vp]

@@ -64,8 +64,6 @@ Engine::~Engine() {
     for (auto &l : layers) {
         dev_free(l.w_ih);
         dev_free(l.w_hh);
-        dev_free(l.w_ih_t);
-        dev_free(l.w_hh_t);
         dev_free(l.bias);
     }
     dev_free(grads);
@@ -120,32 +118,55 @@ void Engine::release_time_buffers() {
         dev_free(l.cs);
         dev_free(l.dg);
         dev_free(l.dx);
-        dev_free(l.dg_t);
-        dev_free(l.xh_t);
+        dev_free(l.y_all);
+        dev_free(l.ck_h);
+        dev_free(l.ck_c);
     }
     t_cap = 0;
+    buf_steps = 0;
+    workspace_bytes = 0;
 }
 
 int Engine::allocate(size_t cap) {
     const size_t B = cfg.batch, H = cfg.hidden_size, es = dtype_size(cfg.dtype);
     const bool tcp = backend == FLSTM_BACKEND_TC;
+    const size_t bs = (recompute && recompute < cap) ? recompute : cap;  // steps the gate-sized buffers span
+    const size_t segments = (cap + bs - 1) / bs;
+    size_t total = 0;
+    auto sized = [&](auto **p, size_t bytes) { total += bytes; return dev_alloc(p, bytes); };
     for (size_t li = 0; li < layers.size(); ++li) {
         auto &l = layers[li];
-        FLSTM_TRY(dev_alloc(&l.gates, cap * B * 4 * H * es));
-        FLSTM_TRY(dev_alloc(&l.hs, (cap + 1) * B * H * es));
-        FLSTM_TRY(dev_alloc(&l.cs, (cap + 1) * B * H * sizeof(float)));
+        FLSTM_TRY(sized(&l.gates, bs * B * 4 * H * es));
+        FLSTM_TRY(sized(&l.hs, (bs + 1) * B * H * es));
+        FLSTM_TRY(sized(&l.cs, (bs + 1) * B * H * sizeof(float)));
         if (cfg.training) {
-            FLSTM_TRY(dev_alloc(&l.dg, cap * B * 4 * H * es));
-            if (li > 0) FLSTM_TRY(dev_alloc(&l.dx, cap * B * l.in_size * es));
-            if (tcp) {
-                FLSTM_TRY(dev_alloc(&l.dg_t, cap * B * 4 * H * es));
-                FLSTM_TRY(dev_alloc(&l.xh_t, cap * B * (l.in_size + H) * es));
-            }
+            // with checkpoints one more slot: dG of the first step of the segment processed before
+            FLSTM_TRY(sized(&l.dg, (bs + (recompute ? 1 : 0)) * B * 4 * H * es));
+            if (li > 0) FLSTM_TRY(sized(&l.dx, cap * B * l.in_size * es));
+        }
+        if (recompute) {
+            if (li + 1 < layers.size()) FLSTM_TRY(sized(&l.y_all, cap * B * H * es));
+            FLSTM_TRY(sized(&l.ck_h, segments * B * H * es));
+            FLSTM_TRY(sized(&l.ck_c, segments * B * H * sizeof(float)));
         }
     }
     t_cap = cap;
+    buf_steps = bs;
+    workspace_bytes = total;
     if (tcp) FLSTM_TRY(tc::on_capacity_change(*this));
     return FLSTM_OK;
+}
+
+int Engine::set_recompute(size_t R) {
+    if (R && backend != FLSTM_BACKEND_TC)
+        return set_error(FLSTM_ERR_UNSUPPORTED, "activation checkpoints need the tensor-core backend (f16/bf16, H %% 64 == 0)");
+    if (R == recompute) return FLSTM_OK;
+    FLSTM_CUDA_TRY(cudaDeviceSynchronize());
+    const size_t cap = t_cap ? t_cap : 1;
+    release_time_buffers();
+    recompute = R;
+    last_T = 0;
+    return allocate(cap);
 }
 
 int Engine::ensure_capacity(size_t T) {
@@ -190,6 +211,11 @@ int Engine::forward_range(size_t T, size_t t0, size_t t1, const void *x, const v
     if (T == 0 || B == 0 || H == 0) return FLSTM_OK;  // zero-sized problem: silent no-op (lstm_forward.cu:493-495)
     if (!x) return set_error(FLSTM_ERR_INVALID, "x is null");
     if (t0 >= t1 || t1 > T) return set_error(FLSTM_ERR_INVALID, "bad step range [%zu, %zu) of %zu", t0, t1, T);
+    if (recompute) {
+        if (t0 != 0 || t1 != T)
+            return set_error(FLSTM_ERR_UNSUPPORTED, "step ranges are not available with activation checkpoints");
+        return forward_checkpointed(T, x, h0, c0, y, hn, cn, s);
+    }
     const int L = (int)layers.size();
     const size_t slab = B * H;
     if (t0 == 0) {
@@ -281,6 +307,100 @@ int Engine::forward_range(size_t T, size_t t0, size_t t1, const void *x, const v
     return FLSTM_OK;
 }
 
+// Activation-checkpoint forward: segments of buf_steps steps run through the segment-sized buffers with
+// segment-local time indices; the state entering each segment is kept, the gate cache is not written.
+int Engine::forward_checkpointed(size_t T, const void *x, const void *h0, const void *c0, void *y, void *hn, void *cn,
+                                 cudaStream_t s) {
+    const size_t B = cfg.batch, H = cfg.hidden_size, es = dtype_size(cfg.dtype), slab = B * H;
+    const int L = (int)layers.size();
+    for (auto &l : layers)
+        if (!l.weights_set) return set_error(FLSTM_ERR_INVALID, "weights have not been set for every layer");
+    FLSTM_TRY(ensure_capacity(T));
+    timer.reset();
+    x_saved = x;
+    last_T = 0;
+    const size_t R = buf_steps, ces = cell_io_f32 ? sizeof(float) : es;
+    struct Restore { Engine &e; ~Restore() { e.seg = SegmentMode{}; } } restore{*this};  // also on early error returns
+    seg.keep_gates = false;
+    int st = FLSTM_OK;
+    for (int li = 0; li < L && st == FLSTM_OK; ++li) {
+        auto &l = layers[li];
+        if (h0) FLSTM_CUDA_TRY(cudaMemcpyAsync(l.hs, byte_ptr(h0) + li * slab * es, slab * es, cudaMemcpyDeviceToDevice, s));
+        else FLSTM_CUDA_TRY(cudaMemsetAsync(l.hs, 0, slab * es, s));
+        if (c0) { FLSTM_TRY(simt::convert(cell_io_f32 ? FLSTM_DTYPE_F32 : cfg.dtype, byte_ptr(c0) + li * slab * ces, FLSTM_DTYPE_F32, l.cs, slab, s)); ++launches; }
+        else FLSTM_CUDA_TRY(cudaMemsetAsync(l.cs, 0, slab * sizeof(float), s));
+        const void *x_l = li == 0 ? x : layers[li - 1].y_all;
+        void *y_l = (li == L - 1) ? y : l.y_all;
+        size_t k = 0;
+        for (size_t seg0 = 0; seg0 < T && st == FLSTM_OK; seg0 += R, ++k) {
+            const size_t n = T - seg0 < R ? T - seg0 : R;
+            // checkpoint k: the state entering the segment (slot 0)
+            FLSTM_CUDA_TRY(cudaMemcpyAsync(byte_ptr(l.ck_h) + k * slab * es, l.hs, slab * es, cudaMemcpyDeviceToDevice, s));
+            FLSTM_CUDA_TRY(cudaMemcpyAsync(l.ck_c + k * slab, l.cs, slab * sizeof(float), cudaMemcpyDeviceToDevice, s));
+            st = tc::forward_layer(*this, li, 0, n, byte_ptr(x_l) + seg0 * B * l.in_size * es,
+                                   y_l ? byte_ptr(y_l) + seg0 * slab * es : nullptr, s);
+            if (st != FLSTM_OK) break;
+            // the state leaving the segment enters the next one
+            FLSTM_CUDA_TRY(cudaMemcpyAsync(l.hs, byte_ptr(l.hs) + n * slab * es, slab * es, cudaMemcpyDeviceToDevice, s));
+            FLSTM_CUDA_TRY(cudaMemcpyAsync(l.cs, l.cs + n * slab, slab * sizeof(float), cudaMemcpyDeviceToDevice, s));
+        }
+        if (st != FLSTM_OK) break;
+        if (hn) FLSTM_CUDA_TRY(cudaMemcpyAsync(byte_ptr(hn) + li * slab * es, l.hs, slab * es, cudaMemcpyDeviceToDevice, s));
+        if (cn) { FLSTM_TRY(simt::convert(FLSTM_DTYPE_F32, l.cs, cell_io_f32 ? FLSTM_DTYPE_F32 : cfg.dtype, byte_ptr(cn) + li * slab * ces, slab, s)); ++launches; }
+    }
+    seg.keep_gates = true;
+    FLSTM_TRY(st);
+    fwd_progress = T;
+    last_T = T;
+    bwd_progress = T;
+    return FLSTM_OK;
+}
+
+// Activation-checkpoint backward: segments from the last to the first; per layer the forward of the segment
+// is re-run from its checkpoint (rebuilding gates, h and c in the segment buffers), then the BPTT runs over
+// it with the gradient carries (dc in dc_layers, dh as dG of the next step / partial sums) kept between
+// segments, and the weight gradients accumulate segment by segment.
+int Engine::backward_checkpointed(size_t T, const void *dy, const void *dhn, const void *dcn, void *dx, float *dh0,
+                                  float *dc0, cudaStream_t s) {
+    const size_t B = cfg.batch, H = cfg.hidden_size, es = dtype_size(cfg.dtype), slab = B * H;
+    const int L = (int)layers.size();
+    const size_t R = buf_steps, K = (T + R - 1) / R;
+    struct Restore { Engine &e; ~Restore() { e.seg = SegmentMode{}; } } restore{*this};  // also on early error returns
+    seg.active = true;
+    int st = FLSTM_OK;
+    for (size_t kk = K; kk-- > 0 && st == FLSTM_OK;) {
+        const size_t seg0 = kk * R, n = T - seg0 < R ? T - seg0 : R;
+        seg.final_segment = kk == 0;
+        seg.first_segment = kk == K - 1;
+        const size_t T_loc = (kk == K - 1) ? n : n + 1;  // slot n of dG then holds the step after the segment
+        for (int li = L - 1; li >= 0 && st == FLSTM_OK; --li) {
+            auto &l = layers[li];
+            FLSTM_CUDA_TRY(cudaMemcpyAsync(l.hs, byte_ptr(l.ck_h) + kk * slab * es, slab * es, cudaMemcpyDeviceToDevice, s));
+            FLSTM_CUDA_TRY(cudaMemcpyAsync(l.cs, l.ck_c + kk * slab, slab * sizeof(float), cudaMemcpyDeviceToDevice, s));
+            const void *x_seg = li == 0 ? byte_ptr(x_saved) + seg0 * B * l.in_size * es
+                                        : byte_ptr(layers[li - 1].y_all) + seg0 * slab * es;
+            st = tc::forward_layer(*this, li, 0, n, x_seg, nullptr, s);  // recompute
+            if (st != FLSTM_OK) break;
+            const void *dy_seg = byte_ptr((li == L - 1) ? dy : layers[li + 1].dx) + seg0 * slab * es;
+            void *dx_seg = li == 0 ? (dx ? byte_ptr(dx) + seg0 * B * l.in_size * es : nullptr) : byte_ptr(l.dx) + seg0 * slab * es;
+            st = tc::backward_layer(*this, li, T_loc, 0, n, x_seg, dy_seg, dhn ? byte_ptr(dhn) + li * slab * es : nullptr,
+                                    dcn ? byte_ptr(dcn) + li * slab * es : nullptr, dx_seg,
+                                    (kk == 0 && dh0) ? dh0 + li * slab : nullptr, (kk == 0 && dc0) ? dc0 + li * slab : nullptr, s);
+            if (st != FLSTM_OK) break;
+            if (kk > 0)  // dG of the segment's first step: what the segment before it continues from
+                FLSTM_CUDA_TRY(cudaMemcpyAsync(byte_ptr(l.dg) + R * B * 4 * H * es, l.dg, B * 4 * H * es, cudaMemcpyDeviceToDevice, s));
+        }
+    }
+    seg = SegmentMode{};
+    FLSTM_TRY(st);
+    if (comm) {
+        FLSTM_CUDA_TRY(cudaEventRecord(comm_join, comm_stream));
+        FLSTM_CUDA_TRY(cudaStreamWaitEvent(s, comm_join, 0));
+    }
+    bwd_progress = 0;
+    return FLSTM_OK;
+}
+
 int Engine::backward(size_t T, const void *dy, const void *dhn, const void *dcn, void *dx, float *dh0,
                      float *dc0, cudaStream_t s) {
     return backward_range(T, 0, T, dy, dhn, dcn, dx, dh0, dc0, s);
@@ -300,6 +420,11 @@ int Engine::backward_range(size_t T, size_t t0, size_t t1, const void *dy, const
     if (!dy) return set_error(FLSTM_ERR_INVALID, "dy is null");
     if (t0 >= t1 || t1 > T) return set_error(FLSTM_ERR_INVALID, "bad step range [%zu, %zu) of %zu", t0, t1, T);
     if (bwd_progress != t1) return set_error(FLSTM_ERR_INVALID, "backward ranges must be contiguous and descending (expected end %zu, got %zu)", bwd_progress, t1);
+    if (recompute) {
+        if (t0 != 0 || t1 != T)
+            return set_error(FLSTM_ERR_UNSUPPORTED, "step ranges are not available with activation checkpoints");
+        return backward_checkpointed(T, dy, dhn, dcn, dx, dh0, dc0, s);
+    }
     const int L = (int)layers.size();
     const size_t slab = B * H;
     const size_t n = t1 - t0;  // steps in the range
@@ -609,6 +734,14 @@ int flstm_engine_attach_comm(flstm_engine *engine, const void *id128, int rank, 
         return set_error(FLSTM_ERR_CUDA, "could not create the communication stream");
     return FLSTM_OK;
 }
+
+int flstm_engine_set_recompute_interval(flstm_engine *engine, size_t interval) {
+    if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    cudaSetDevice(engine->impl.device);
+    return engine->impl.set_recompute(interval);
+}
+
+size_t flstm_engine_workspace_bytes(const flstm_engine *engine) { return engine ? engine->impl.workspace_bytes : 0; }
 
 int flstm_engine_abort_comm(flstm_engine *engine) {
     if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");

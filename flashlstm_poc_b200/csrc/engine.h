@@ -33,16 +33,16 @@ struct LayerBuffers {
     size_t in_size = 0;      // I_l
     void *w_ih = nullptr;    // T (4H, I_l)   SIMT: torch row order; TC: tile-interleaved rows
     void *w_hh = nullptr;    // T (4H, H)     same row order as w_ih
-    void *w_ih_t = nullptr;  // T (I_l, 4H)   TC only: W_ih^T, torch gate order along 4H
-    void *w_hh_t = nullptr;  // T (H, 4H)     TC only: W_hh^T, torch gate order along 4H
     float *bias = nullptr;   // fp32 (4H)     b_ih + b_hh, same order as the rows of w_ih
     void *gates = nullptr;   // T (Tcap, B, 4H)  input projection, overwritten by the gate cache
     void *hs = nullptr;      // T (Tcap+1, B, H) slot 0 = h0, slot t+1 = h_t
     float *cs = nullptr;     // fp32 (Tcap+1, B, H)
     void *dg = nullptr;      // T (Tcap, B, 4H)  pre-activation gradients (training)
     void *dx = nullptr;      // T (Tcap, B, I_l) gradient w.r.t. this layer's input (layers > 0)
-    void *dg_t = nullptr;    // T (4H, Tcap*B)   TC only: dG^T for the weight-gradient GEMMs
-    void *xh_t = nullptr;    // T (I_l + H, Tcap*B) TC only: [X | H_prev]^T
+    // activation-checkpoint mode (Engine::recompute > 0): the time-sized buffers above hold one segment
+    void *y_all = nullptr;   // T (Tcap, B, H)  layers below the top: h_t for every step = the next layer's input
+    void *ck_h = nullptr;    // T (K, B, H)     hidden state entering segment k
+    float *ck_c = nullptr;   // fp32 (K, B, H)  cell state entering segment k
     float *dw_ih = nullptr;  // views into the flat gradient buffer
     float *dw_hh = nullptr;
     float *db = nullptr;
@@ -55,7 +55,20 @@ struct Engine {
     flstm_engine_config cfg{};
     int backend = FLSTM_BACKEND_SIMT;
     int device = 0;
-    size_t t_cap = 0;  // sequence capacity of the time-sized buffers
+    size_t t_cap = 0;  // longest sequence the engine is currently sized for
+    // Activation checkpoints (the reference's recompute interval R, flashlstm_v2/src/lstm_forward.cu:727-783,
+    // lstm_backward.cu:975-1054): with recompute = R > 0 the forward keeps only the h/c state entering every
+    // R-th step, and the backward re-runs the forward of one R-step segment at a time to rebuild its gate
+    // cache.  gates / hs / cs / dg then span buf_steps = min(R, t_cap) steps instead of t_cap.
+    size_t recompute = 0;
+    size_t buf_steps = 0;
+    size_t workspace_bytes = 0;  // bytes of the time-sized buffers currently allocated
+    struct SegmentMode {
+        bool active = false;         // the layer backward works on one segment with segment-local time indices
+        bool final_segment = true;   // the segment that starts at t = 0: dh0/dc0 and the gradient allreduce follow it
+        bool first_segment = true;   // the first one processed (the end of the sequence): weight gradients start from zero
+        bool keep_gates = true;      // forward writes the activated gates back (off in the checkpointing forward pass)
+    } seg;
     std::vector<LayerBuffers> layers;
     float *grads = nullptr;  // flat fp32: per layer [dW_ih | dW_hh | db]
     size_t grad_count = 0;
@@ -99,6 +112,11 @@ struct Engine {
                  float *dc0, cudaStream_t s);
     int forward_range(size_t T, size_t t0, size_t t1, const void *x, const void *h0, const void *c0, void *y, void *hn,
                       void *cn, cudaStream_t s);
+    int forward_checkpointed(size_t T, const void *x, const void *h0, const void *c0, void *y, void *hn, void *cn,
+                             cudaStream_t s);
+    int backward_checkpointed(size_t T, const void *dy, const void *dhn, const void *dcn, void *dx, float *dh0, float *dc0,
+                              cudaStream_t s);
+    int set_recompute(size_t R);
     int backward_range(size_t T, size_t t0, size_t t1, const void *dy, const void *dhn, const void *dcn, void *dx,
                        float *dh0, float *dc0, cudaStream_t s);
 };

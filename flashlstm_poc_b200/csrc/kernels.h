@@ -48,8 +48,9 @@ int column_sum(int dtype, const void *dg, size_t R, size_t N, float *out, cudaSt
 // from tile-interleaved columns (H = unperm_h).
 constexpr int kColumnSumSplits = 32;
 int column_sum_scratch_floats(size_t N);
+// accumulate: out += column sums (segment-by-segment bias gradients)
 int column_sum_two_pass(int dtype, const void *dg, size_t R, size_t N, float *scratch, float *out, int unperm_h,
-                        cudaStream_t s);
+                        cudaStream_t s, bool accumulate = false);
 
 }  // namespace simt
 }  // namespace flstm_b200

@@ -266,7 +266,7 @@ column_sum_partial_kernel(const T *__restrict__ dg, size_t R, size_t N, int spli
 }
 
 __global__ void column_sum_final_kernel(const float *__restrict__ partial, size_t N, int splits, float *__restrict__ out,
-                                        int unperm_h) {
+                                        int unperm_h, int accumulate) {
     const size_t col = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
     if (col >= N) return;
     float t = 0.f;
@@ -276,7 +276,7 @@ __global__ void column_sum_final_kernel(const float *__restrict__ partial, size_
         const int r = (int)col, tile = r >> 6, g = (r >> 4) & 3, u = r & 15;
         o = (size_t)g * unperm_h + tile * 16 + u;
     }
-    out[o] = t;
+    out[o] = accumulate ? out[o] + t : t;
 }
 
 inline int grid_1d(size_t n, int block = 256, int cap = 148 * 16) {
@@ -446,7 +446,7 @@ int column_sum(int dtype, const void *dg, size_t R, size_t N, float *out, cudaSt
 int column_sum_scratch_floats(size_t N) { return (int)(kColumnSumSplits * N); }
 
 int column_sum_two_pass(int dtype, const void *dg, size_t R, size_t N, float *scratch, float *out, int unperm_h,
-                        cudaStream_t s) {
+                        cudaStream_t s, bool accumulate) {
     if (N == 0) return FLSTM_OK;
     dim3 grid(ceil_div(N, 32), kColumnSumSplits);
     switch (dtype) {
@@ -456,7 +456,7 @@ int column_sum_two_pass(int dtype, const void *dg, size_t R, size_t N, float *sc
         default: return set_error(FLSTM_ERR_INVALID, "column_sum: bad dtype %d", dtype);
     }
     FLSTM_TRY(check_launch("column_sum_partial"));
-    column_sum_final_kernel<<<ceil_div(N, 256), 256, 0, s>>>(scratch, N, kColumnSumSplits, out, unperm_h);
+    column_sum_final_kernel<<<ceil_div(N, 256), 256, 0, s>>>(scratch, N, kColumnSumSplits, out, unperm_h, accumulate ? 1 : 0);
     return check_launch("column_sum_final");
 }
 

@@ -174,7 +174,8 @@ void destroy(Engine &e) {
 
 int on_capacity_change(Engine &e) {
     TcState *st = state(e);
-    const size_t B = e.cfg.batch, H = e.cfg.hidden_size, cap = e.t_cap;
+    // time extent of the gate-sized buffers (one segment with activation checkpoints); dG has one slot more then
+    const size_t B = e.cfg.batch, H = e.cfg.hidden_size, cap = e.buf_steps, dg_steps = cap + (e.recompute ? 1 : 0);
     for (size_t li = 0; li < e.layers.size(); ++li) {
         auto &l = e.layers[li];
         auto &t = st->layers[li];
@@ -186,13 +187,13 @@ int on_capacity_change(Engine &e) {
             FLSTM_TRY(make_tensor_map_3d_tile(&t.tm_c_ep, l.cs, 4, cap + 1, B, H, 32, 16));
             FLSTM_TRY(make_tensor_map_3d_tile(&t.tm_h_ep, l.hs, 2, cap + 1, B, H, 32, 16));
             if (e.cfg.training && l.dg)
-                FLSTM_TRY(make_tensor_map_3d(&t.tm_dg3, l.dg, cap, B, 4 * H, 4 * H, B * 4 * H, 128, 64, true));
+                FLSTM_TRY(make_tensor_map_3d(&t.tm_dg3, l.dg, dg_steps, B, 4 * H, 4 * H, B * 4 * H, 128, 64, true));
             continue;
         }
         FLSTM_TRY(make_tensor_map_chunked(&t.tm_h, l.hs, cap + 1, B, H, st->fwd.BT, st->fwd.ch));
         FLSTM_TRY(make_tensor_map_3d(&t.tm_g, l.gates, cap, B, 4 * H, 4 * H, B * 4 * H, st->fwd.BT, 64, false));
         if (e.cfg.training && l.dg)
-            FLSTM_TRY(make_tensor_map_chunked(&t.tm_dg, l.dg, cap, B, 4 * H, st->bwd.BT, st->bwd.ch));
+            FLSTM_TRY(make_tensor_map_chunked(&t.tm_dg, l.dg, dg_steps, B, 4 * H, st->bwd.BT, st->bwd.ch));
     }
     return FLSTM_OK;
 }
@@ -244,7 +245,7 @@ int forward_layer(Engine &e, int li, size_t t0, size_t t1, const void *x_l, void
             sp.t = (int)step;
             sp.B = (int)B;
             sp.H = (int)H;
-            sp.store_gates = e.cfg.training ? 1 : 0;
+            sp.store_gates = (e.cfg.training && e.seg.keep_gates) ? 1 : 0;
             FLSTM_TRY(lstm_step_forward(e.cfg.dtype, st->step, maps, sp, st->sms, s));
         }
         size_t m2 = e.timer.mark(s);
@@ -266,7 +267,7 @@ int forward_layer(Engine &e, int li, size_t t0, size_t t1, const void *x_l, void
     p.t0 = (int)t0;
     p.B = (int)B;
     p.H = (int)H;
-    p.store_gates = e.cfg.training ? 1 : 0;
+    p.store_gates = (e.cfg.training && e.seg.keep_gates) ? 1 : 0;
     p.trace = (li == 0 && t0 == 0) ? e.trace : nullptr;
     p.trace_steps = e.trace_steps;
     FLSTM_TRY(lstm_forward_persistent(e.cfg.dtype, st->fwd, t.tm_w, t.tm_h, t.tm_g, p, s));
@@ -281,7 +282,7 @@ int forward_layer(Engine &e, int li, size_t t0, size_t t1, const void *x_l, void
 // Wide-batch BPTT over the steps [t0, t1), descending: per step one pointwise kernel (dG_t, cell-gradient
 // carry) and one split-K GEMM (the fp32 partial sums of dG_t W_hh that step t-1 adds to its dy).
 static int backward_steps(Engine &e, int li, size_t T, size_t t0, size_t t1, const void *dy_l, const void *dhn_l,
-                          const void *dcn_l, float *dh0_l, float *dc0_l, cudaStream_t s) {
+                          const void *dcn_l, float *dh0_l, float *dc0_l, bool finalize, cudaStream_t s) {
     TcState *st = state(e);
     auto &l = e.layers[li];
     auto &t = st->layers[li];
@@ -302,13 +303,13 @@ static int backward_steps(Engine &e, int li, size_t T, size_t t0, size_t t1, con
                                                l.cs + step * slab, byte_ptr(dy_l) + step * slab * es, parts, nparts, dc,
                                                byte_ptr(l.dg) + step * B * 4 * H * es, (int)B, (int)H, s));
         ++e.launches;
-        if (step > 0 || dh0_l) {
+        if (step > 0 || dh0_l || !finalize) {  // the product at step 0 is dh0, or the carry into the segment before
             FLSTM_TRY(lstm_step_backward_gemm(e.cfg.dtype, st->step, t.tm_dg3, t.tm_w, (int)step, (int)B, (int)H, parts,
                                               e.sync_words, st->sms, s));
             ++e.launches;
         }
     }
-    if (t0 == 0) {
+    if (t0 == 0 && finalize) {
         if (dh0_l) { FLSTM_TRY(sum_parts(parts, splits, slab, dh0_l, s)); ++e.launches; }
         if (dc0_l) FLSTM_CUDA_TRY(cudaMemcpyAsync(dc0_l, dc, slab * sizeof(float), cudaMemcpyDeviceToDevice, s));
     }
@@ -338,7 +339,10 @@ int backward_layer(Engine &e, int li, size_t T, size_t t0, size_t t1, const void
     const size_t B = e.cfg.batch, H = e.cfg.hidden_size, es = dtype_size(e.cfg.dtype), n = t1 - t0;
     unsigned int *err = e.sync_words;
     size_t m0 = e.timer.mark(s);
-    if (st->step.use) FLSTM_TRY(backward_steps(e, li, T, t0, t1, dy_l, dhn_l, dcn_l, dh0_l, dc0_l, s));
+    // with activation checkpoints `T` and the range are segment-local; only the segment that starts the sequence
+    // finishes the recurrence (dh0 / dc0) and the layer's gradients
+    const bool finalize = t0 == 0 && (!e.seg.active || e.seg.final_segment);
+    if (st->step.use) FLSTM_TRY(backward_steps(e, li, T, t0, t1, dy_l, dhn_l, dcn_l, dh0_l, dc0_l, finalize, s));
     else {
     FLSTM_CUDA_TRY(cudaMemsetAsync(e.sync_words + 1, 0, (size_t)st->bwd.ngroups * sizeof(unsigned int), s));
     BwdParams p{};
@@ -357,7 +361,7 @@ int backward_layer(Engine &e, int li, size_t T, size_t t0, size_t t1, const void
     p.err = err;
     p.T = (int)T;
     p.s0 = (int)(T - t1);
-    p.s1 = (int)(T - t0) + (t0 == 0 ? 1 : 0);  // the last range also runs the iteration that writes dh0 / dc0
+    p.s1 = (int)(T - t0) + (finalize ? 1 : 0);  // the last range also runs the iteration that writes dh0 / dc0
     p.B = (int)B;
     p.H = (int)H;
     FLSTM_TRY(lstm_backward_persistent(e.cfg.dtype, st->bwd, t.tm_w, t.tm_dg, p, s));
@@ -378,15 +382,20 @@ int backward_layer(Engine &e, int li, size_t T, size_t t0, size_t t1, const void
         // dW = dG^T [X | H_prev] over the whole sequence: both operands read as stored (reduction dim
         // T*B outermost); rows of the product are written back in torch gate order.  With a communicator
         // each block of the layer's gradients starts its allreduce as soon as it is complete.
+        // With activation checkpoints the sum runs segment by segment (the n steps in the buffers now),
+        // accumulating from the second segment on, and the allreduce follows the last one.
+        const size_t steps = e.seg.active ? n : T;
+        const bool acc = e.seg.active && !e.seg.first_segment, last = !e.seg.active || e.seg.final_segment;
         const size_t n_ih = 4 * H * l.in_size;
-        FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, l.in_size, T * B, l.dg, 4 * H, true, x_l, l.in_size, true,
-                       l.dw_ih, l.in_size, nullptr, (int)H, err, st->sms, s));
-        FLSTM_TRY(e.reduce_grads(l.grad_offset, n_ih, s));
-        FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, H, T * B, l.dg, 4 * H, true, l.hs, H, true, l.dw_hh, H, nullptr,
-                       (int)H, err, st->sms, s));
-        FLSTM_TRY(simt::column_sum_two_pass(e.cfg.dtype, l.dg, T * B, 4 * H,
-                                            e.db_part + (size_t)li * simt::column_sum_scratch_floats(4 * H), l.db, (int)H, s));
-        FLSTM_TRY(e.reduce_grads(l.grad_offset + n_ih, l.grad_count - n_ih, s));
+        FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, l.in_size, steps * B, l.dg, 4 * H, true, x_l, l.in_size, true,
+                       l.dw_ih, l.in_size, nullptr, (int)H, err, st->sms, s, acc));
+        if (last) FLSTM_TRY(e.reduce_grads(l.grad_offset, n_ih, s));
+        FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, H, steps * B, l.dg, 4 * H, true, l.hs, H, true, l.dw_hh, H, nullptr,
+                       (int)H, err, st->sms, s, acc));
+        FLSTM_TRY(simt::column_sum_two_pass(e.cfg.dtype, l.dg, steps * B, 4 * H,
+                                            e.db_part + (size_t)li * simt::column_sum_scratch_floats(4 * H), l.db, (int)H, s,
+                                            acc));
+        if (last) FLSTM_TRY(e.reduce_grads(l.grad_offset + n_ih, l.grad_count - n_ih, s));
         e.launches += 4;
         return FLSTM_OK;
     };

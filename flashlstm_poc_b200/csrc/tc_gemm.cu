@@ -51,7 +51,7 @@ enum OutMode { OUT_F16 = 0, OUT_BF16 = 1, OUT_F32 = 2 };
 
 template <int MODE>
 __device__ __forceinline__ void store_row32(void *dst_row, int col0, const uint32_t (&acc)[32], const float *bias,
-                                            int n_valid) {
+                                            int n_valid, bool accumulate = false) {
     // dst_row: start of this thread's output row; writes columns [col0, col0+32) clipped to n_valid
     float v[32];
 #pragma unroll
@@ -65,10 +65,16 @@ __device__ __forceinline__ void store_row32(void *dst_row, int col0, const uint3
         float *p = static_cast<float *>(dst_row) + col0;
         if (n_valid >= 32 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-                reinterpret_cast<float4 *>(p)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            for (int i = 0; i < 8; ++i) {
+                float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                if (accumulate) {  // D += A B^T: partial products of successive K ranges (sequence segments)
+                    const float4 old = reinterpret_cast<const float4 *>(p)[i];
+                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                reinterpret_cast<float4 *>(p)[i] = o;
+            }
         } else {
-            for (int i = 0; i < 32 && i < n_valid; ++i) p[i] = v[i];
+            for (int i = 0; i < 32 && i < n_valid; ++i) p[i] = accumulate ? p[i] + v[i] : v[i];
         }
     } else {
         uint32_t packed[16];
@@ -145,7 +151,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             const __grid_constant__ CUtensorMap tm_d, void *__restrict__ D,
             size_t ldd, const float *__restrict__ bias, int M, int N, int K, uint32_t idesc, int unperm_h,
-            unsigned int *__restrict__ err_word) {
+            unsigned int *__restrict__ err_word, int accumulate) {
     using S = GemmShape<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -293,7 +299,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c, acc);
                 tmem_ld_wait();
                 const int n_valid = N - (n0 + c);
-                if (row < M && n_valid > 0) store_row32<MODE>(dst_row, n0 + c, acc, HAS_BIAS ? bias : nullptr, n_valid);
+                if (row < M && n_valid > 0)
+                    store_row32<MODE>(dst_row, n0 + c, acc, HAS_BIAS ? bias : nullptr, n_valid, MODE == OUT_F32 && accumulate);
             }
             tcgen05_fence_before();
             __syncwarp();
@@ -318,6 +325,7 @@ struct GemmArgs {
     int unperm_h;
     unsigned int *err;
     int sms;
+    int accumulate;
     cudaStream_t s;
 };
 
@@ -333,7 +341,7 @@ int launch_one(const GemmArgs &g) {
     const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
     const int grid = tiles < g.sms ? tiles : g.sms;
     kern<<<grid, kGemmThreads, S::kSmemBytes, g.s>>>(g.ta, g.tb, g.td, g.D, g.ldd, g.bias, g.M, g.N, g.K, g.idesc,
-                                                    g.unperm_h, g.err);
+                                                    g.unperm_h, g.err, g.accumulate);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "tc gemm launch failed: %s", cudaGetErrorString(e));
     return FLSTM_OK;
@@ -379,7 +387,9 @@ int dispatch(int out_dtype, bool a_mn, bool b_mn, const GemmArgs &g) {
 
 int gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, size_t lda, bool a_mn, const void *B,
          size_t ldb, bool b_mn, void *D, size_t ldd, const float *bias, int unperm_h, unsigned int *err_word, int sms,
-         cudaStream_t s) {
+         cudaStream_t s, bool accumulate) {
+    if (accumulate && out_dtype != FLSTM_DTYPE_F32)
+        return set_error(FLSTM_ERR_UNSUPPORTED, "accumulating GEMM output must be fp32");
     if (dtype != FLSTM_DTYPE_F16 && dtype != FLSTM_DTYPE_BF16)
         return set_error(FLSTM_ERR_UNSUPPORTED, "tensor-core GEMM operands must be f16 or bf16");
     if (M == 0 || N == 0 || K == 0) return FLSTM_OK;
@@ -408,6 +418,7 @@ int gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, 
     g.unperm_h = unperm_h;
     g.err = err_word;
     g.sms = sms;
+    g.accumulate = accumulate ? 1 : 0;
     g.s = s;
     return BN == 256 ? dispatch<256>(out_dtype, a_mn, b_mn, g) : dispatch<128>(out_dtype, a_mn, b_mn, g);
 }

@@ -17,7 +17,7 @@ namespace tc {
 // `err_word` is a device word the kernel sets to 1 if a bounded wait expired.
 int gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, size_t lda, bool a_mn, const void *B,
          size_t ldb, bool b_mn, void *D, size_t ldd, const float *bias, int unperm_h, unsigned int *err_word, int sms,
-         cudaStream_t s);
+         cudaStream_t s, bool accumulate = false);  // accumulate (fp32 output only): D += A B^T
 
 int device_sm_count();
 

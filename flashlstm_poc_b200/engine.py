@@ -207,6 +207,16 @@ class Engine:
         with torch.cuda.device(self.device):
             check(self.lib.flstm_engine_attach_comm(self._h, buf, rank, world_size))
 
+    def set_recompute_interval(self, interval: int) -> None:
+        """Activation checkpoints: keep h/c every `interval` steps and rebuild the gate cache segment by segment in
+        backward (0 = keep the full gate cache).  Re-allocates the time-sized buffers."""
+        with torch.cuda.device(self.device):
+            check(self.lib.flstm_engine_set_recompute_interval(self._h, int(interval)))
+
+    @property
+    def workspace_bytes(self) -> int:
+        return int(self.lib.flstm_engine_workspace_bytes(self._h))
+
     def wait(self, timeout_s: float, stream: Optional[torch.cuda.Stream] = None) -> None:
         """Host watchdog: block until the work enqueued so far on `stream` has finished, at most `timeout_s`
         seconds.  Raises FlashLstmError (TIMEOUT) past the deadline, after aborting an attached communicator."""

@@ -114,6 +114,18 @@ int flstm_engine_cache_ptrs(flstm_engine *engine, int layer, void **gates, float
  * flstm_engine_forward are fp32 (L,B,H) tensors instead of tensors in the engine dtype. */
 int flstm_engine_set_cell_io_f32(flstm_engine *engine, int enabled);
 
+/* Activation checkpoints instead of a full gate cache (the reference's recompute interval R,
+ * flashlstm_v2/include/lstm.hpp:43-60, lstm_forward.cu:727-783, lstm_backward.cu:975-1054).  With
+ * interval R > 0 the forward keeps only the h/c state entering every R-th step (plus each layer's output
+ * sequence) and the backward re-runs the forward of one R-step segment at a time to rebuild its gates, so
+ * the (T,B,4H) gate cache and dG shrink to (R,B,4H): 16 -> 2 bytes per (step, sequence, gate) at R = 8.
+ * Outputs and state gradients are bit-identical to R = 0; weight gradients are summed segment by segment
+ * (fp32) instead of in one pass.  Tensor-core backend only; whole-sequence calls only (no step ranges).
+ * Call between sequences; it re-allocates the time-sized buffers.  flstm_engine_workspace_bytes returns
+ * the bytes those buffers take now. */
+int flstm_engine_set_recompute_interval(flstm_engine *engine, size_t interval);
+size_t flstm_engine_workspace_bytes(const flstm_engine *engine);
+
 /* Which backend the engine resolved to (flstm_backend, never AUTO). */
 int flstm_engine_backend(const flstm_engine *engine);
 
