@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 A step = one forward + full backward pass over one batch of seeded synthetic input (the
-reference has no dataset; see flashlstm_poc_b200/workloads.py).  At N=1 the workload is BASELINE
+reference has no dataset; see flashlstm_poc_b200/workloads.py).  At N=1 the workload is benchmark
 configuration 2 (1 layer, FP16, I=H=1024, B=64, T=512).  At N>1 every rank runs that per-GPU
 batch (weak scaling: global batch 64*N) and the weight gradients are summed with one NCCL
 allreduce per layer inside the backward pass.

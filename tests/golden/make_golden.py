@@ -6,7 +6,7 @@ lstm_backward_cudnn_like).  This script imports that file from a checkout of the
 reference, runs it on seeded inputs and stores inputs + outputs as .npz fixtures next to
 this file.  The fixtures travel with the repository; the reference checkout does not.
 
-usage: python tests/golden/make_golden.py [path-to-reference-checkout]
+usage: python tests/golden/make_golden.py <path-to-reference-checkout>
 """
 
 from __future__ import annotations
@@ -41,7 +41,9 @@ def load_reference(root: str):
 
 
 def main() -> None:
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit(__doc__)
+    root = sys.argv[1]
     ref = load_reference(root)
     for name, T, B, I, H, seed, state_std in CASES:
         g = torch.Generator().manual_seed(seed)

@@ -50,7 +50,7 @@ def test_engine_matches_oracle(backend, dtype, L, T, B, I, H):
 
 
 def test_config1_fp32_full_size_against_torch_lstm():
-    """BASELINE config 1 at full size, ground truth = fp32 CPU torch.nn.LSTM (loss = sum(y*dY))."""
+    """Benchmark configuration 1 (fp32, I=H=256, B=32, T=128) at full size, ground truth = fp32 CPU torch.nn.LSTM (loss = sum(y*dY))."""
     w = WORKLOADS["c1_fp32_h256"]
     inp = make_inputs(w)
     got, eng = run_engine(w, inp)
@@ -64,7 +64,7 @@ def test_config1_fp32_full_size_against_torch_lstm():
                                         ("c3_bf16_l2_h2048", dict(seq_len=32, batch=32, input_size=512, hidden_size=512)),
                                         ("c5_bf16_l4_h1024", dict(seq_len=16, batch=64, input_size=256, hidden_size=256))])
 def test_scaled_baseline_configs(name, scale):
-    """The 16-bit BASELINE configurations at sizes the CPU oracle finishes in seconds."""
+    """The 16-bit benchmark configurations at sizes the CPU oracle finishes in seconds."""
     w = WORKLOADS[name].scaled(**scale)
     inp = make_inputs(w)
     got, eng = run_engine(w, inp)
