@@ -61,6 +61,13 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t ra
 __device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
+// 16 bytes into a cluster peer's (or this CTA's) shared memory; their arrival is counted on the mbarrier at
+// `bar_addr` (same CTA as `addr`), so the data carries its own completion signal: the sender neither waits for
+// the stores nor sends an arrive after them
+__device__ __forceinline__ void st_async_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t bar_addr) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(bar_addr) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr) : "memory");
 }
@@ -190,7 +197,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         for (int i = 0; i < 2; ++i) {
             mbar_init(&tfull[i], 1);
             mbar_init(&tempty[i], 4);
-            mbar_init(&rbar[i], 64);
+            mbar_init(&rbar[i], KS > 1 ? 1 : 64);  // split K: one expect_tx arrival, the partials count themselves in
         }
         mbar_init(wbar, 1);
         *abort_w = 0;
@@ -378,9 +385,10 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                             const uint32_t off = (uint32_t)(((rb * KS + kq) * UPO + lu) * RS + c0) * 4u;
                             if (KS > 1) {
                                 const uint32_t dst = map_to_rank(red_local + off, owner);
+                                const uint32_t bar = map_to_rank(rbar_local + rb * 8, owner);
 #pragma unroll
                                 for (int i = 0; i < 8; ++i)
-                                    st_cluster_v4(dst + 16 * i, acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+                                    st_async_v4(dst + 16 * i, acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3], bar);
                             } else {
                                 float4 *dst = reinterpret_cast<float4 *>(s_red + off / 4);
 #pragma unroll
@@ -393,10 +401,11 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     tcgen05_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&tempty[buf]);
-                    if (lane < 16) {
-                        const uint32_t owner = (warp * 16 + lane) / UPO;
-                        if (KS > 1) mbar_arrive_cluster(map_to_rank(rbar_local + rb * 8, owner));
-                        else mbar_arrive(&rbar[rb]);
+                    if (KS > 1) {
+                        // this CTA receives UPO rows of BT fp32 partials from each of the KS CTAs (itself included)
+                        if (tid == 0) mbar_expect_tx(&rbar[rb], (uint32_t)(KS * UPO * BT * 4));
+                    } else if (lane < 16) {
+                        mbar_arrive(&rbar[rb]);
                     }
                     if (tid == 0) FLSTM_STAMP(s - p.s0, 9);
                     ok = mbar_wait_cluster(&rbar[rb], (wi >> 1) & 1, abort_w);

@@ -46,10 +46,13 @@ class LSTM(nn.Module):
     named as in torch.nn.LSTM (weight_ih_l{k}, ...); `dtype` selects the engine's arithmetic."""
 
     def __init__(self, input_size: int, hidden_size: int, num_layers: int = 1, *, dtype: torch.dtype = torch.float16,
-                 device="cuda", backend: str = "auto"):
+                 device="cuda", backend: str = "auto", recompute_interval: int = 0):
         super().__init__()
         self.input_size, self.hidden_size, self.num_layers = input_size, hidden_size, num_layers
         self.compute_dtype, self.backend = dtype, backend
+        # > 0: activation checkpoints every `recompute_interval` steps instead of a full gate cache (the
+        # reference's recompute_interval, flashlstm_v2/python/flashlstm/streaming_lstm.py:356)
+        self.recompute_interval = int(recompute_interval)
         bound = 1.0 / math.sqrt(hidden_size)
         for l in range(num_layers):
             I = input_size if l == 0 else hidden_size
@@ -75,6 +78,8 @@ class LSTM(nn.Module):
         if eng is None:
             eng = Engine(DTYPE_OF_TORCH[self.compute_dtype], self.num_layers, B, self.input_size, self.hidden_size, T,
                          training=True, backend=self.backend, device=x.device)
+            if self.recompute_interval:
+                eng.set_recompute_interval(self.recompute_interval)
             if self._comm is not None:
                 eng.attach_comm(*self._comm)
             self._engines[key] = eng

@@ -228,13 +228,15 @@ def test_v2_rejects_misuse_without_aborting():
     assert lib.flstm_last_status() == 0
 
 
-def test_lstm_module_stacked_bf16_autograd():
-    """nn.LSTM-compatible module: 2 layers, BF16, gradients through autograd vs fp32 torch.nn.LSTM."""
+@pytest.mark.parametrize("recompute_interval", [0, 4])
+def test_lstm_module_stacked_bf16_autograd(recompute_interval):
+    """nn.LSTM-compatible module: 2 layers, BF16, gradients through autograd vs fp32 torch.nn.LSTM; also with
+    activation checkpoints every 4 of the 6 steps."""
     from flashlstm_poc_b200.lstm import LSTM
 
     torch.manual_seed(3)
     T, B, I, H, L = 6, 8, 64, 64, 2
-    m = LSTM(I, H, L, dtype=torch.bfloat16)
+    m = LSTM(I, H, L, dtype=torch.bfloat16, recompute_interval=recompute_interval)
     ref = torch.nn.LSTM(I, H, L)
     with torch.no_grad():
         for n, p in m.named_parameters():
