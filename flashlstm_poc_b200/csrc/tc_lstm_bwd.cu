@@ -24,6 +24,7 @@
 #include "common.cuh"
 #include "tc_common.cuh"
 #include "tc_kernels.h"
+#include "tc_recurrent.cuh"
 
 namespace flstm_b200 {
 namespace tc {
@@ -32,110 +33,6 @@ namespace {
 
 constexpr int kBwdThreads = 192;
 constexpr int kChunkBytesW = 64 * 64 * 2;
-
-__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int *p) {
-    unsigned int v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void red_release_gpu_add(unsigned int *p, unsigned int v) {
-    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// shared::cta address -> shared::cluster address of the same offset in CTA `rank`
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-// 16 bytes into a cluster peer's (or this CTA's) shared memory; their arrival is counted on the mbarrier at
-// `bar_addr` (same CTA as `addr`), so the data carries its own completion signal: the sender neither waits for
-// the stores nor sends an arrive after them
-__device__ __forceinline__ void st_async_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t bar_addr) {
-    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
-                 ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(bar_addr) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_w) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    const unsigned long long t0 = global_timer_ns();
-    uint32_t spins = 0;
-    while (!mbar_try_wait_cluster(bar, parity)) {
-        if ((++spins & 255u) == 0) {
-            if (*abort_w) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
-                *abort_w = 1;
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-__device__ __forceinline__ bool wait_counter(const unsigned int *ctr, unsigned int target, unsigned int *err_word,
-                                             volatile uint32_t *abort_w) {
-    if (ld_acquire_gpu(ctr) >= target) return true;
-    const unsigned long long t0 = global_timer_ns();
-    uint32_t spins = 0;
-    while (ld_acquire_gpu(ctr) < target) {
-        if ((++spins & 63u) == 0) {
-            if (*abort_w) return false;
-            if (*reinterpret_cast<volatile unsigned int *>(err_word)) {
-                *abort_w = 1;
-                return false;
-            }
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
-                *abort_w = 1;
-                atomicExch(err_word, 3u);
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-template <bool BF16>
-__device__ __forceinline__ float load16(const uint16_t *p) {
-    if (BF16) return __bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(p));
-    return __half2float(*reinterpret_cast<const __half *>(p));
-}
-template <bool BF16>
-__device__ __forceinline__ uint16_t to16(float v) {
-    if (BF16) {
-        __nv_bfloat16 h = __float2bfloat16_rn(v);
-        return *reinterpret_cast<uint16_t *>(&h);
-    }
-    __half h = __float2half_rn(v);
-    return *reinterpret_cast<uint16_t *>(&h);
-}
 
 struct PairIn {
     float gi, gf, gg, go, ct, cp, dy;
@@ -197,7 +94,9 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         for (int i = 0; i < 2; ++i) {
             mbar_init(&tfull[i], 1);
             mbar_init(&tempty[i], 4);
-            mbar_init(&rbar[i], KS > 1 ? 1 : 64);  // split K: one expect_tx arrival, the partials count themselves in
+            // split K: the remote partials count themselves in (st.async), one expect_tx arrival announces their
+            // bytes, and the UPO lanes that hold this CTA's own rows arrive after their plain stores
+            mbar_init(&rbar[i], KS > 1 ? 1 + UPO : 64);
         }
         mbar_init(wbar, 1);
         *abort_w = 0;
@@ -238,7 +137,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             // the group's counter; in the previous launch: already complete)
             for (int s = (p.s0 > 1 ? p.s0 : 1); s < p.s1 && ok; ++s) {
                 const int t_src = p.T - s;  // dG_{t+1} with t = T-1-s
-                if (s > p.s0) ok = wait_counter(counter, (unsigned)(p.jt * KS * 4) * (unsigned)(s - p.s0), p.err, abort_w);
+                if (s > p.s0) ok = wait_counter(counter, (unsigned)(p.jt * KS * 4) * (unsigned)(s - p.s0), p.err, abort_w, 3u);
                 if (!ok) break;
                 fence_proxy_async_all();
                 FLSTM_STAMP(s - p.s0, 0);
@@ -383,7 +282,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                             const int row = warp * 16 + lane;        // unit within the tile
                             const uint32_t owner = row / UPO, lu = row % UPO;
                             const uint32_t off = (uint32_t)(((rb * KS + kq) * UPO + lu) * RS + c0) * 4u;
-                            if (KS > 1) {
+                            if (KS > 1 && owner != (uint32_t)kq) {
                                 const uint32_t dst = map_to_rank(red_local + off, owner);
                                 const uint32_t bar = map_to_rank(rbar_local + rb * 8, owner);
 #pragma unroll
@@ -402,8 +301,10 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&tempty[buf]);
                     if (KS > 1) {
-                        // this CTA receives UPO rows of BT fp32 partials from each of the KS CTAs (itself included)
-                        if (tid == 0) mbar_expect_tx(&rbar[rb], (uint32_t)(KS * UPO * BT * 4));
+                        // this CTA receives UPO rows of BT fp32 partials from each of the other KS-1 CTAs; its own
+                        // rows were stored directly by the lanes that hold them
+                        if (tid == 0) mbar_expect_tx(&rbar[rb], (uint32_t)((KS - 1) * UPO * BT * 4));
+                        if (lane < 16 && (uint32_t)((warp * 16 + lane) / UPO) == (uint32_t)kq) mbar_arrive(&rbar[rb]);
                     } else if (lane < 16) {
                         mbar_arrive(&rbar[rb]);
                     }

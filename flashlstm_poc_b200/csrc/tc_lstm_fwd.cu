@@ -27,6 +27,7 @@
 #include "common.cuh"
 #include "tc_common.cuh"
 #include "tc_kernels.h"
+#include "tc_recurrent.cuh"
 
 namespace flstm_b200 {
 namespace tc {
@@ -35,56 +36,6 @@ namespace {
 
 constexpr int kFwdThreads = 192;  // 4 epilogue warps + producer warp + MMA warp
 constexpr int kChunkBytesW = 64 * 64 * 2;
-
-__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int *p) {
-    unsigned int v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void red_release_gpu_add(unsigned int *p, unsigned int v) {
-    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
-// Bounded poll of a monotonic counter written by other CTAs.
-__device__ __forceinline__ bool wait_counter(const unsigned int *ctr, unsigned int target, unsigned int *err_word,
-                                             volatile uint32_t *abort_w) {
-    if (ld_acquire_gpu(ctr) >= target) return true;
-    const unsigned long long t0 = global_timer_ns();
-    uint32_t spins = 0;
-    while (ld_acquire_gpu(ctr) < target) {
-        if ((++spins & 63u) == 0) {
-            if (*abort_w) return false;
-            if (*reinterpret_cast<volatile unsigned int *>(err_word)) {
-                *abort_w = 1;
-                return false;
-            }
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
-                *abort_w = 1;
-                atomicExch(err_word, 2u);
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-template <bool BF16>
-__device__ __forceinline__ float load16(const uint16_t *p) {
-    if (BF16) return __bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(p));
-    return __half2float(*reinterpret_cast<const __half *>(p));
-}
-template <bool BF16>
-__device__ __forceinline__ uint16_t to16(float v) {
-    if (BF16) {
-        __nv_bfloat16 h = __float2bfloat16_rn(v);
-        return *reinterpret_cast<uint16_t *>(&h);
-    }
-    __half h = __float2half_rn(v);
-    return *reinterpret_cast<uint16_t *>(&h);
-}
 
 }  // namespace
 
@@ -195,7 +146,7 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                             // h_{t-1} of this batch group is complete when every CTA of the group has
                             // arrived tt times in this launch (4 epilogue warps each); the state a launch
                             // starts from was completed by the previous launch
-                            ok = wait_counter(counter, (unsigned)(p.cta_rows * 4) * (unsigned)tt, p.err, abort_w);
+                            ok = wait_counter(counter, (unsigned)(p.cta_rows * 4) * (unsigned)tt, p.err, abort_w, 2u);
                             if (!ok) break;
                             fence_proxy_async_all();
                         }
