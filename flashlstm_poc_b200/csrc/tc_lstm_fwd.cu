@@ -36,6 +36,7 @@ namespace {
 
 constexpr int kFwdThreads = 192;  // 4 epilogue warps + producer warp + MMA warp
 constexpr int kChunkBytesW = 64 * 64 * 2;
+constexpr int kReleasesPerCta = 1;  // arrivals on the step counter per CTA and step (4 = one per epilogue warp)
 
 }  // namespace
 
@@ -146,7 +147,7 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                             // h_{t-1} of this batch group is complete when every CTA of the group has
                             // arrived tt times in this launch (4 epilogue warps each); the state a launch
                             // starts from was completed by the previous launch
-                            ok = wait_counter(counter, (unsigned)(p.cta_rows * 4) * (unsigned)tt, p.err, abort_w, 2u);
+                            ok = wait_counter(counter, (unsigned)(p.cta_rows * kReleasesPerCta) * (unsigned)tt, p.err, abort_w, 2u);
                             if (!ok) break;
                             fence_proxy_async_all();
                         }
@@ -299,8 +300,13 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         // publish h_t: the release is cumulative over the warp's stores ordered before it
                         // by __syncwarp.  The generic->async proxy fence sits on the consumer side, between
                         // its acquire of the counter and its TMA loads.
-                        __syncwarp();
-                        if (lane == 0) red_release_gpu_add(counter, 1u);
+                        if (kReleasesPerCta == 1) {
+                            named_barrier_sync(2, 128);
+                            if (tid == 0) red_release_gpu_add(counter, 1u);
+                        } else {
+                            __syncwarp();
+                            if (lane == 0) red_release_gpu_add(counter, 1u);
+                        }
                         if (tid == 0) FLSTM_STAMP(tt, 8);
                     }
                     // everything nobody waits for: cell state, gate cache, the caller's y
