@@ -34,7 +34,8 @@ namespace tc {
 
 namespace {
 
-constexpr int kFwdThreads = 192;  // 4 epilogue warps + producer warp + MMA warp
+constexpr int kFwdThreads = 320;  // warps 0-3 epilogue (TMEM readers), 4 producer, 5 MMA, 6-9 pointwise helpers
+constexpr int kFwdEpilogueThreads = 256;
 constexpr int kChunkBytesW = 64 * 64 * 2;
 constexpr int kReleasesPerCta = 1;  // arrivals on the step counter per CTA and step (4 = one per epilogue warp)
 
@@ -93,7 +94,7 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             mbar_init(&tfull[i], 1);
             mbar_init(&tempty[i], 4);
             mbar_init(&pfull[i], 1);
-            mbar_init(&pempty[i], 4);
+            mbar_init(&pempty[i], kFwdEpilogueThreads / 32);
         }
         mbar_init(wbar, 1);
         *abort_w = 0;
@@ -217,10 +218,12 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue (128 threads)
-        const int tid = threadIdx.x;         // 0..127
-        const int u = tid & 15, nb = tid >> 4;  // phase-B ownership: unit u, sequences nb + 8*i
-        constexpr int PAIRS = BT / 8;
+        // ------------------------------------------------------------ epilogue (256 threads)
+        // Warps 0-3 own the TMEM lane quadrants and move the accumulator to shared memory (phase A); the
+        // pointwise update (phase B) is spread over them and the four helper warps 6-9.
+        const int tid = warp < 4 ? threadIdx.x : threadIdx.x - 64;  // 0..255
+        const int u = tid & 15, nb = tid >> 4;  // phase-B ownership: unit u, sequences nb + 16*i
+        constexpr int PAIRS = BT / 16;
         float c_keep[PAIRS];
         const bool keep_c = items_per_step == 1;
         const size_t slab = (size_t)p.B * p.H;
@@ -242,7 +245,7 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     float c_prev[PAIRS];
 #pragma unroll
                     for (int i = 0; i < PAIRS; ++i) {
-                        const int b = b0 + nb + 8 * i;
+                        const int b = b0 + nb + 16 * i;
                         if (keep_c && tt > 0) c_prev[i] = c_keep[i];
                         else c_prev[i] = (b < p.B) ? p.cs[(size_t)t * slab + (size_t)b * p.H + j * 16 + u] : 0.f;
                     }
@@ -251,27 +254,29 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     if (tid == 0) FLSTM_STAMP(tt, 5);
                     tcgen05_fence_after();
                     float *ex = s_ex + (wi & 1) * 64 * EXS;
-                    // phase A: lanes 0..15 of warp g hold the recurrent sums of gate g, units 0..15, all
-                    // BT sequences; they go to shared memory as they are
+                    // phase A (warps 0-3): lanes 0..15 of warp g hold the recurrent sums of gate g, units 0..15,
+                    // all BT sequences; they go to shared memory as they are
+                    if (warp < 4) {
 #pragma unroll
-                    for (int c0 = 0; c0 < BT; c0 += 32) {
-                        uint32_t acc[32];
-                        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BT + c0, acc);
-                        tmem_ld_wait();
-                        if (lane < 16) {
-                            float4 *dst = reinterpret_cast<float4 *>(ex + (warp * 16 + lane) * EXS + c0);
+                        for (int c0 = 0; c0 < BT; c0 += 32) {
+                            uint32_t acc[32];
+                            tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BT + c0, acc);
+                            tmem_ld_wait();
+                            if (lane < 16) {
+                                float4 *dst = reinterpret_cast<float4 *>(ex + (warp * 16 + lane) * EXS + c0);
 #pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                dst[i] = make_float4(__uint_as_float(acc[4 * i]), __uint_as_float(acc[4 * i + 1]),
-                                                     __uint_as_float(acc[4 * i + 2]), __uint_as_float(acc[4 * i + 3]));
+                                for (int i = 0; i < 8; ++i)
+                                    dst[i] = make_float4(__uint_as_float(acc[4 * i]), __uint_as_float(acc[4 * i + 1]),
+                                                         __uint_as_float(acc[4 * i + 2]), __uint_as_float(acc[4 * i + 3]));
+                            }
                         }
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tempty[buf]);
                     }
-                    tcgen05_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&tempty[buf]);
                     ok = mbar_wait(&pfull[pb], (wi >> 1) & 1, abort_w);
                     if (!ok) break;
-                    named_barrier_sync(1, 128);
+                    named_barrier_sync(1, kFwdEpilogueThreads);
                     if (tid == 0) FLSTM_STAMP(tt, 6);
                     // phase B: one thread per (unit, sequence) pair does the whole pointwise update
                     const uint16_t *ptile = reinterpret_cast<const uint16_t *>(s_p + pb * BT * 128);
@@ -279,7 +284,7 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     uint16_t h16[PAIRS];
 #pragma unroll
                     for (int i = 0; i < PAIRS; ++i) {
-                        const int nn = nb + 8 * i;
+                        const int nn = nb + 16 * i;
                         const float ai = ex[(0 * 16 + u) * EXS + nn] + load16<BF16>(ptile + nn * 64 + 0 * 16 + u);
                         const float af = ex[(1 * 16 + u) * EXS + nn] + load16<BF16>(ptile + nn * 64 + 1 * 16 + u);
                         const float ag = ex[(2 * 16 + u) * EXS + nn] + load16<BF16>(ptile + nn * 64 + 2 * 16 + u);
@@ -301,7 +306,7 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         // by __syncwarp.  The generic->async proxy fence sits on the consumer side, between
                         // its acquire of the counter and its TMA loads.
                         if (kReleasesPerCta == 1) {
-                            named_barrier_sync(2, 128);
+                            named_barrier_sync(2, kFwdEpilogueThreads);
                             if (tid == 0) red_release_gpu_add(counter, 1u);
                         } else {
                             __syncwarp();
@@ -312,7 +317,7 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     // everything nobody waits for: cell state, gate cache, the caller's y
 #pragma unroll
                     for (int i = 0; i < PAIRS; ++i) {
-                        const int b = b0 + nb + 8 * i;
+                        const int b = b0 + nb + 16 * i;
                         if (b >= p.B) continue;
                         const size_t idx = (size_t)b * p.H + j * 16 + u;
                         p.cs[(size_t)(t + 1) * slab + idx] = c_keep[i];
