@@ -31,7 +31,8 @@ namespace tc {
 
 namespace {
 
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 320;  // warps 0-3 epilogue (TMEM readers), 4 producer, 5 MMA, 6-9 pointwise helpers
+constexpr int kBwdEpilogueThreads = 256;
 constexpr int kChunkBytesW = 64 * 64 * 2;
 constexpr int kReleasesPerCta = 1;  // arrivals on the step counter per CTA and step (4 = one per epilogue warp)
 
@@ -61,7 +62,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_dg, BwdParams p) {
     constexpr int UPO = 64 / KS;            // units this CTA owns after the reduce-scatter
     constexpr int UQ = UPO / 16;            // 16-unit groups per owner
-    constexpr int PAIRS = UQ * (BT / 8);    // (unit, sequence) pairs per epilogue thread
+    constexpr int PAIRS = UQ * (BT / 16);   // (unit, sequence) pairs per epilogue thread
     constexpr bool PREFETCH = PAIRS <= 8;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -205,9 +206,11 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue (128 threads)
-        const int tid = threadIdx.x;
-        const int u16 = tid & 15, nb = tid >> 4;
+        // ------------------------------------------------------------ epilogue (256 threads)
+        // Warps 0-3 own the TMEM lane quadrants: they read the accumulator and scatter the partial sums (phase A).
+        // The reduction of the partials and the pointwise backward are spread over them and helper warps 6-9.
+        const int tid = warp < 4 ? threadIdx.x : threadIdx.x - 64;  // 0..255
+        const int u16 = tid & 15, nb = tid >> 4;  // unit u16 (+16q), sequences nb + 16*i
         const size_t slab = (size_t)p.B * p.H;
         const size_t G = (size_t)4 * p.H;
         const uint16_t *gates = static_cast<const uint16_t *>(p.gates);
@@ -229,7 +232,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 float dc_in[PAIRS];
                 auto unit_of = [&](int q) { return j * 64 + kq * UPO + q * 16 + u16; };
                 auto load_pair = [&](int q, int i, PairIn &v) {
-                    const int b = b0 + nb + 8 * i, U = unit_of(q);
+                    const int b = b0 + nb + 16 * i, U = unit_of(q);
                     if (b < p.B && t >= 0) {
                         const uint16_t *grow = gates + ((size_t)t * p.B + b) * G + (size_t)(U >> 4) * 64 + (U & 15);
                         v.gi = load16<BF16>(grow);
@@ -248,9 +251,9 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
 #pragma unroll
                 for (int q = 0; q < UQ; ++q)
 #pragma unroll
-                    for (int i = 0; i < BT / 8; ++i) {
-                        const int k = q * (BT / 8) + i;
-                        const int b = b0 + nb + 8 * i;
+                    for (int i = 0; i < BT / 16; ++i) {
+                        const int k = q * (BT / 16) + i;
+                        const int b = b0 + nb + 16 * i;
                         const size_t idx = (size_t)b * p.H + unit_of(q);
                         if (s == 0) dc_in[k] = (dcn && b < p.B) ? load16<BF16>(dcn + idx) : 0.f;
                         else if (keep_dc && s > p.s0) dc_in[k] = dc_keep[k];
@@ -263,9 +266,9 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
 #pragma unroll
                     for (int q = 0; q < UQ; ++q)
 #pragma unroll
-                        for (int i = 0; i < BT / 8; ++i) {
-                            const int b = b0 + nb + 8 * i;
-                            dh_in[q * (BT / 8) + i] = (dhn && b < p.B) ? load16<BF16>(dhn + (size_t)b * p.H + unit_of(q)) : 0.f;
+                        for (int i = 0; i < BT / 16; ++i) {
+                            const int b = b0 + nb + 16 * i;
+                            dh_in[q * (BT / 16) + i] = (dhn && b < p.B) ? load16<BF16>(dhn + (size_t)b * p.H + unit_of(q)) : 0.f;
                         }
                 } else {
                     const int buf = wi & 1, rb = wi & 1;
@@ -273,41 +276,43 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     if (!ok) break;
                     if (tid == 0) FLSTM_STAMP(s - p.s0, 5);
                     tcgen05_fence_after();
-                    // phase A: lanes 0..15 of warp w hold units 16w+lane of the tile, all BT sequences
+                    if (warp < 4) {
+                        // phase A (warps 0-3): lanes 0..15 of warp w hold units 16w+lane of the tile, all BT sequences
 #pragma unroll
-                    for (int c0 = 0; c0 < BT; c0 += 32) {
-                        uint32_t acc[32];
-                        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BT + c0, acc);
-                        tmem_ld_wait();
-                        if (lane < 16) {
-                            const int row = warp * 16 + lane;        // unit within the tile
-                            const uint32_t owner = row / UPO, lu = row % UPO;
-                            const uint32_t off = (uint32_t)(((rb * KS + kq) * UPO + lu) * RS + c0) * 4u;
-                            if (KS > 1 && owner != (uint32_t)kq) {
-                                const uint32_t dst = map_to_rank(red_local + off, owner);
-                                const uint32_t bar = map_to_rank(rbar_local + rb * 8, owner);
+                        for (int c0 = 0; c0 < BT; c0 += 32) {
+                            uint32_t acc[32];
+                            tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BT + c0, acc);
+                            tmem_ld_wait();
+                            if (lane < 16) {
+                                const int row = warp * 16 + lane;        // unit within the tile
+                                const uint32_t owner = row / UPO, lu = row % UPO;
+                                const uint32_t off = (uint32_t)(((rb * KS + kq) * UPO + lu) * RS + c0) * 4u;
+                                if (KS > 1 && owner != (uint32_t)kq) {
+                                    const uint32_t dst = map_to_rank(red_local + off, owner);
+                                    const uint32_t bar = map_to_rank(rbar_local + rb * 8, owner);
 #pragma unroll
-                                for (int i = 0; i < 8; ++i)
-                                    st_async_v4(dst + 16 * i, acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3], bar);
-                            } else {
-                                float4 *dst = reinterpret_cast<float4 *>(s_red + off / 4);
+                                    for (int i = 0; i < 8; ++i)
+                                        st_async_v4(dst + 16 * i, acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3], bar);
+                                } else {
+                                    float4 *dst = reinterpret_cast<float4 *>(s_red + off / 4);
 #pragma unroll
-                                for (int i = 0; i < 8; ++i)
-                                    dst[i] = make_float4(__uint_as_float(acc[4 * i]), __uint_as_float(acc[4 * i + 1]),
-                                                         __uint_as_float(acc[4 * i + 2]), __uint_as_float(acc[4 * i + 3]));
+                                    for (int i = 0; i < 8; ++i)
+                                        dst[i] = make_float4(__uint_as_float(acc[4 * i]), __uint_as_float(acc[4 * i + 1]),
+                                                             __uint_as_float(acc[4 * i + 2]), __uint_as_float(acc[4 * i + 3]));
+                                }
                             }
                         }
-                    }
-                    tcgen05_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&tempty[buf]);
-                    if (KS > 1) {
-                        // this CTA receives UPO rows of BT fp32 partials from each of the other KS-1 CTAs; its own
-                        // rows were stored directly by the lanes that hold them
-                        if (tid == 0) mbar_expect_tx(&rbar[rb], (uint32_t)((KS - 1) * UPO * BT * 4));
-                        if (lane < 16 && (uint32_t)((warp * 16 + lane) / UPO) == (uint32_t)kq) mbar_arrive(&rbar[rb]);
-                    } else if (lane < 16) {
-                        mbar_arrive(&rbar[rb]);
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tempty[buf]);
+                        if (KS > 1) {
+                            // this CTA receives UPO rows of BT fp32 partials from each of the other KS-1 CTAs; its own
+                            // rows were stored directly by the lanes that hold them
+                            if (tid == 0) mbar_expect_tx(&rbar[rb], (uint32_t)((KS - 1) * UPO * BT * 4));
+                            if (lane < 16 && (uint32_t)((warp * 16 + lane) / UPO) == (uint32_t)kq) mbar_arrive(&rbar[rb]);
+                        } else if (lane < 16) {
+                            mbar_arrive(&rbar[rb]);
+                        }
                     }
                     if (tid == 0) FLSTM_STAMP(s - p.s0, 9);
                     ok = mbar_wait_cluster(&rbar[rb], (wi >> 1) & 1, abort_w);
@@ -317,15 +322,15 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
 #pragma unroll
                     for (int q = 0; q < UQ; ++q)
 #pragma unroll
-                        for (int i = 0; i < BT / 8; ++i) {
-                            const int lu = q * 16 + u16, nn = nb + 8 * i;
+                        for (int i = 0; i < BT / 16; ++i) {
+                            const int lu = q * 16 + u16, nn = nb + 16 * i;
                             float acc = 0.f;
 #pragma unroll
                             for (int src = 0; src < KS; ++src) acc += red[(src * UPO + lu) * RS + nn];
-                            dh_in[q * (BT / 8) + i] = acc;
+                            dh_in[q * (BT / 16) + i] = acc;
                         }
                     // every warp has read this item's partials before any warp sends the next item's
-                    named_barrier_sync(1, 128);
+                    named_barrier_sync(1, kBwdEpilogueThreads);
                     if (tid == 0) FLSTM_STAMP(s - p.s0, 6);
                     ++wi;
                 }
@@ -333,9 +338,9 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
 #pragma unroll
                 for (int q = 0; q < UQ; ++q)
 #pragma unroll
-                    for (int i = 0; i < BT / 8; ++i) {
-                        const int k = q * (BT / 8) + i;
-                        const int b = b0 + nb + 8 * i, U = unit_of(q);
+                    for (int i = 0; i < BT / 16; ++i) {
+                        const int k = q * (BT / 16) + i;
+                        const int b = b0 + nb + 16 * i, U = unit_of(q);
                         if (b >= p.B) continue;
                         const size_t idx = (size_t)b * p.H + U;
                         if (t < 0) {
@@ -370,7 +375,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 // publish dG_t (release, cumulative over the warp's stores); the generic->async proxy fence
                 // is on the consumer side, after its acquire and before its TMA loads
                 if (kReleasesPerCta == 1) {
-                    named_barrier_sync(2, 128);
+                    named_barrier_sync(2, kBwdEpilogueThreads);
                     if (tid == 0) red_release_gpu_add(counter, 1u);
                 } else {
                     __syncwarp();
@@ -385,9 +390,9 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
 #pragma unroll
             for (int q = 0; q < UQ; ++q)
 #pragma unroll
-                for (int i = 0; i < BT / 8; ++i) {
-                    const int b = b0 + nb + 8 * i;
-                    if (b < p.B) p.dc[(size_t)b * p.H + j * 64 + kq * UPO + q * 16 + u16] = dc_keep[q * (BT / 8) + i];
+                for (int i = 0; i < BT / 16; ++i) {
+                    const int b = b0 + nb + 16 * i;
+                    if (b < p.B) p.dc[(size_t)b * p.H + j * 64 + kq * UPO + q * 16 + u16] = dc_keep[q * (BT / 16) + i];
                 }
         }
     }
