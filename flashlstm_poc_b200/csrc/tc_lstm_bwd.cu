@@ -34,7 +34,6 @@ namespace {
 constexpr int kBwdThreads = 320;  // warps 0-3 epilogue (TMEM readers), 4 producer, 5 MMA, 6-9 pointwise helpers
 constexpr int kBwdEpilogueThreads = 256;
 constexpr int kChunkBytesW = 64 * 64 * 2;
-constexpr int kReleasesPerCta = 1;  // arrivals on the step counter per CTA and step (4 = one per epilogue warp)
 
 struct PairIn {
     float gi, gf, gg, go, ct, cp, dy;
@@ -139,7 +138,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             // the group's counter; in the previous launch: already complete)
             for (int s = (p.s0 > 1 ? p.s0 : 1); s < p.s1 && ok; ++s) {
                 const int t_src = p.T - s;  // dG_{t+1} with t = T-1-s
-                if (s > p.s0) ok = wait_counter(counter, (unsigned)(p.jt * KS * kReleasesPerCta) * (unsigned)(s - p.s0), p.err, abort_w, 3u);
+                if (s > p.s0) ok = wait_counter(counter, (unsigned)(p.jt * KS) * (unsigned)(s - p.s0), p.err, abort_w, 3u);
                 if (!ok) break;
                 fence_proxy_async_all();
                 FLSTM_STAMP(s - p.s0, 0);
@@ -374,13 +373,10 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 if (tid == 0) FLSTM_STAMP(s - p.s0, 7);
                 // publish dG_t (release, cumulative over the warp's stores); the generic->async proxy fence
                 // is on the consumer side, after its acquire and before its TMA loads
-                if (kReleasesPerCta == 1) {
-                    named_barrier_sync(2, kBwdEpilogueThreads);
-                    if (tid == 0) red_release_gpu_add(counter, 1u);
-                } else {
-                    __syncwarp();
-                    if (lane == 0) red_release_gpu_add(counter, 1u);
-                }
+                // ONE arrival per CTA (see the forward kernel): after the named barrier thread 0's release is
+                // cumulative over every epilogue warp's stores
+                named_barrier_sync(2, kBwdEpilogueThreads);
+                if (tid == 0) red_release_gpu_add(counter, 1u);
                 if (tid == 0) FLSTM_STAMP(s - p.s0, 8);
             }
         }

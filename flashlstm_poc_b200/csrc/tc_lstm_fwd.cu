@@ -37,7 +37,6 @@ namespace {
 constexpr int kFwdThreads = 320;  // warps 0-3 epilogue (TMEM readers), 4 producer, 5 MMA, 6-9 pointwise helpers
 constexpr int kFwdEpilogueThreads = 256;
 constexpr int kChunkBytesW = 64 * 64 * 2;
-constexpr int kReleasesPerCta = 1;  // arrivals on the step counter per CTA and step (4 = one per epilogue warp)
 
 }  // namespace
 
@@ -146,9 +145,9 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         tma_load_3d(s_p + pb * BT * 128, &tm_g, j * 64, b0, t, &pfull[pb]);
                         if (first && tt > 0) {
                             // h_{t-1} of this batch group is complete when every CTA of the group has
-                            // arrived tt times in this launch (4 epilogue warps each); the state a launch
+                            // arrived tt times in this launch (once per step each); the state a launch
                             // starts from was completed by the previous launch
-                            ok = wait_counter(counter, (unsigned)(p.cta_rows * kReleasesPerCta) * (unsigned)tt, p.err, abort_w, 2u);
+                            ok = wait_counter(counter, (unsigned)(p.cta_rows) * (unsigned)tt, p.err, abort_w, 2u);
                             if (!ok) break;
                             fence_proxy_async_all();
                         }
@@ -302,16 +301,13 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     if (lane == 0) mbar_arrive(&pempty[pb]);  // this warp is done with the P tile
                     if (last_item) {
                         if (tid == 0) FLSTM_STAMP(tt, 7);
-                        // publish h_t: the release is cumulative over the warp's stores ordered before it
-                        // by __syncwarp.  The generic->async proxy fence sits on the consumer side, between
-                        // its acquire of the counter and its TMA loads.
-                        if (kReleasesPerCta == 1) {
-                            named_barrier_sync(2, kFwdEpilogueThreads);
-                            if (tid == 0) red_release_gpu_add(counter, 1u);
-                        } else {
-                            __syncwarp();
-                            if (lane == 0) red_release_gpu_add(counter, 1u);
-                        }
+                        // publish h_t: after the named barrier thread 0's release is cumulative over every epilogue
+                        // warp's stores.  The generic->async proxy fence sits on the consumer side, between its
+                        // acquire of the counter and its TMA loads.
+                        // ONE arrival per CTA: the arrivals of a step serialise on the counter's address in L2, and
+                        // one per epilogue warp cost every step about a thousand cycles more
+                        named_barrier_sync(2, kFwdEpilogueThreads);
+                        if (tid == 0) red_release_gpu_add(counter, 1u);
                         if (tid == 0) FLSTM_STAMP(tt, 8);
                     }
                     // everything nobody waits for: cell state, gate cache, the caller's y
