@@ -110,8 +110,10 @@ gemm_kernel(int M, int N, int K, const TAB *__restrict__ A, size_t lda, const TA
 }
 
 // ---------------------------------------------------------------- fused forward step
-// CTA tile: 16 batch rows x 16 hidden units x 4 gates; thread (b,u) owns the four gate sums.
-constexpr int SB = 16, SU = 16, SK = 32;
+// CTA tile: 8 sequences x 8 hidden units; four consecutive lanes hold the four gate sums of one
+// (sequence, unit) pair, so a launch has (H/8) x (B/8) CTAs (128 for H = 256, B = 32: every SM has one) and
+// a thread's dot product is H long.  Lane 0 of each quad gathers the gates and does the pointwise update.
+constexpr int SB = 8, SU = 8, SK = 64;
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -119,36 +121,38 @@ step_forward_kernel(int B, int H, const T *__restrict__ h_prev, const T *__restr
                     T *__restrict__ p_t, const float *__restrict__ c_prev, float *__restrict__ c_next,
                     T *__restrict__ h_next, T *__restrict__ y_t) {
     __shared__ float hs[SB][SK + 1];
-    __shared__ float ws[4][SU][SK + 1];
+    __shared__ float ws[4 * SU][SK + 1];  // row = unit * 4 + gate
     const int tid = threadIdx.x;
-    const int ul = tid % SU, bl = tid / SU;
+    const int g = tid & 3, ul = (tid >> 2) % SU, bl = tid / (4 * SU);
     const int u0 = blockIdx.x * SU, b0 = blockIdx.y * SB;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc = 0.f;
     for (int k0 = 0; k0 < H; k0 += SK) {
         for (int e = tid; e < SB * SK; e += 256) {
             int b = e / SK, k = e % SK;
             hs[b][k] = (b0 + b < B && k0 + k < H) ? ld(h_prev + (size_t)(b0 + b) * H + k0 + k) : 0.f;
         }
         for (int e = tid; e < 4 * SU * SK; e += 256) {
-            int k = e % SK, u = (e / SK) % SU, g = e / (SK * SU);
-            ws[g][u][k] = (u0 + u < H && k0 + k < H) ? ld(w_hh + ((size_t)g * H + u0 + u) * H + k0 + k) : 0.f;
+            int k = e % SK, r = e / SK, u = r >> 2, gg = r & 3;
+            ws[r][k] = (u0 + u < H && k0 + k < H) ? ld(w_hh + ((size_t)gg * H + u0 + u) * H + k0 + k) : 0.f;
         }
         __syncthreads();
-#pragma unroll
-        for (int k = 0; k < SK; ++k) {
-            float hv = hs[bl][k];
-#pragma unroll
-            for (int g = 0; g < 4; ++g) acc[g] = fmaf(hv, ws[g][ul][k], acc[g]);
-        }
+        const float *hrow = hs[bl], *wrow = ws[ul * 4 + g];
+#pragma unroll 16
+        for (int k = 0; k < SK; ++k) acc = fmaf(hrow[k], wrow[k], acc);
         __syncthreads();
     }
+    // the quad's four gate sums -> its first lane
+    const unsigned full = 0xffffffffu;
+    const int base = (tid & 31) & ~3;
+    const float s_i = __shfl_sync(full, acc, base), s_f = __shfl_sync(full, acc, base + 1);
+    const float s_g = __shfl_sync(full, acc, base + 2), s_o = __shfl_sync(full, acc, base + 3);
     const int b = b0 + bl, u = u0 + ul;
-    if (b >= B || u >= H) return;
+    if (g != 0 || b >= B || u >= H) return;
     T *row = p_t + (size_t)b * 4 * H;
-    float ai = acc[0] + ld(row + u);
-    float af = acc[1] + ld(row + H + u);
-    float ag = acc[2] + ld(row + 2 * H + u);
-    float ao = acc[3] + ld(row + 3 * H + u);
+    float ai = s_i + ld(row + u);
+    float af = s_f + ld(row + H + u);
+    float ag = s_g + ld(row + 2 * H + u);
+    float ao = s_o + ld(row + 3 * H + u);
     float gi = sigmoid_acc(ai), gf = sigmoid_acc(af), gg = tanh_acc(ag), go = sigmoid_acc(ao);
     size_t idx = (size_t)b * H + u;
     float c = fmaf(gf, c_prev[idx], gi * gg);
@@ -164,7 +168,8 @@ step_forward_kernel(int B, int H, const T *__restrict__ h_prev, const T *__restr
 
 // ---------------------------------------------------------------- fused backward step
 // dh[b,u] = dy_t[b,u] + sum_k dg_next[b,k] w_hh[k,u]  (k over 4H), then pointwise backward.
-// When FINAL, only the matrix product is formed and written to dh_out (fp32).
+// Same 8 x 8 tile; the four lanes of a quad split the 4H-long sum (k = lane, lane + 4, ...) and add up with
+// shuffles.  When FINAL, only the matrix product is formed and written to dh_out (fp32).
 template <typename T, bool FINAL>
 __global__ void __launch_bounds__(256)
 step_backward_kernel(int B, int H, const T *__restrict__ dg_next, const T *__restrict__ w_hh,
@@ -172,31 +177,34 @@ step_backward_kernel(int B, int H, const T *__restrict__ dg_next, const T *__res
                      const T *__restrict__ gates_t, const float *__restrict__ c_t,
                      const float *__restrict__ c_prev, float *__restrict__ dc, T *__restrict__ dg_t,
                      float *__restrict__ dh_out) {
-    __shared__ float ds[SB][SK + 1];
-    __shared__ float ws[SK][SU + 1];
+    constexpr int BK2 = 128;
+    __shared__ float ds[SB][BK2 + 1];
+    __shared__ float ws[BK2][SU + 1];
     const int tid = threadIdx.x;
-    const int ul = tid % SU, bl = tid / SU;
+    const int q = tid & 3, ul = (tid >> 2) % SU, bl = tid / (4 * SU);
     const int u0 = blockIdx.x * SU, b0 = blockIdx.y * SB;
     const int G = 4 * H;
     float acc = 0.f;
     if (dg_next) {
-        for (int k0 = 0; k0 < G; k0 += SK) {
-            for (int e = tid; e < SB * SK; e += 256) {
-                int b = e / SK, k = e % SK;
+        for (int k0 = 0; k0 < G; k0 += BK2) {
+            for (int e = tid; e < SB * BK2; e += 256) {
+                int b = e / BK2, k = e % BK2;
                 ds[b][k] = (b0 + b < B && k0 + k < G) ? ld(dg_next + (size_t)(b0 + b) * G + k0 + k) : 0.f;
             }
-            for (int e = tid; e < SK * SU; e += 256) {
+            for (int e = tid; e < BK2 * SU; e += 256) {
                 int u = e % SU, k = e / SU;
                 ws[k][u] = (u0 + u < H && k0 + k < G) ? ld(w_hh + (size_t)(k0 + k) * H + u0 + u) : 0.f;
             }
             __syncthreads();
-#pragma unroll
-            for (int k = 0; k < SK; ++k) acc = fmaf(ds[bl][k], ws[k][ul], acc);
+#pragma unroll 8
+            for (int k = q; k < BK2; k += 4) acc = fmaf(ds[bl][k], ws[k][ul], acc);
             __syncthreads();
         }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
     }
     const int b = b0 + bl, u = u0 + ul;
-    if (b >= B || u >= H) return;
+    if (q != 0 || b >= B || u >= H) return;
     const size_t idx = (size_t)b * H + u;
     if (FINAL) {
         dh_out[idx] = acc;
