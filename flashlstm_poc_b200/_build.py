@@ -27,7 +27,7 @@ EXT = os.path.join(PKG, "_flashlstm" + (sysconfig.get_config_var("EXT_SUFFIX") o
 STAMP = os.path.join(OBJ, "stamp.txt")
 
 CU_SOURCES = [
-    "engine.cu", "simt_kernels.cu", "tc_engine.cu", "tc_gemm.cu", "tc_lstm_fwd.cu", "tc_lstm_bwd.cu", "tc_lstm_step.cu", "comm.cu", "static_scratch.cu", "api_v1.cu", "api_v2.cu",
+    "engine.cu", "simt_kernels.cu", "simt_persistent.cu", "tc_engine.cu", "tc_gemm.cu", "tc_lstm_fwd.cu", "tc_lstm_bwd.cu", "tc_lstm_step.cu", "comm.cu", "static_scratch.cu", "api_v1.cu", "api_v2.cu",
 ]
 
 NVCC_FLAGS = [

@@ -74,6 +74,7 @@ Engine::~Engine() {
     for (size_t i = 1; i < lanes.size(); ++i)
         if (lanes[i]) cudaStreamDestroy(lanes[i]);
     for (auto ev : lane_events) cudaEventDestroy(ev);
+    if (simt_err_host) cudaFreeHost(simt_err_host);
     if (comm) comm_destroy(comm);
     if (comm_stream) cudaStreamDestroy(comm_stream);
     if (comm_fork) cudaEventDestroy(comm_fork);
@@ -88,6 +89,17 @@ int Engine::reduce_grads(size_t offset, size_t count, cudaStream_t from) {
     FLSTM_TRY(comm_allreduce_sum_f32(comm, grads + offset, count, comm_stream));
     size_t c1m = timer.mark(comm_stream);
     timer.span(PH_ALLREDUCE, c0m, c1m);
+    return FLSTM_OK;
+}
+
+// A bounded wait that expired inside a persistent CUDA-core kernel is reported by the next call.
+int Engine::simt_check_error() {
+    if (simt_err_host && *simt_err_host) {
+        const unsigned int code = *simt_err_host;
+        *simt_err_host = 0;
+        cudaMemset(sync_words, 0, sizeof(unsigned int));
+        return set_error(FLSTM_ERR_TIMEOUT, "a bounded device-side wait expired in a persistent kernel (code %u)", code);
+    }
     return FLSTM_OK;
 }
 
@@ -278,13 +290,35 @@ int Engine::forward_range(size_t T, size_t t0, size_t t1, const void *x, const v
                                      l.bias, s));
                 ++launches;
                 size_t m1 = timer.mark(s);
-                for (size_t t = t0; t < t1; ++t) {
-                    FLSTM_TRY(simt::step_forward(cfg.dtype, B, H, byte_ptr(l.hs) + t * slab * es, l.w_hh,
-                                                 byte_ptr(l.gates) + t * B * 4 * H * es, l.cs + t * slab,
-                                                 l.cs + (t + 1) * slab, byte_ptr(l.hs) + (t + 1) * slab * es,
-                                                 y_out ? byte_ptr(y_out) + t * slab * es : nullptr, s));
+                if (simt_grid) {
+                    FLSTM_TRY(simt_check_error());
+                    const size_t tiles = (size_t)simt::persistent_batch_tiles(B);
+                    FLSTM_CUDA_TRY(cudaMemsetAsync(sync_words + 32, 0, tiles * sizeof(unsigned int), s));
+                    simt::PersistentFwdParams pp{};
+                    pp.w_hh = l.w_hh;
+                    pp.hs = l.hs;
+                    pp.cs = l.cs;
+                    pp.gates = l.gates;
+                    pp.y = y_out;
+                    pp.counters = sync_words + 32;
+                    pp.err = sync_words;
+                    pp.B = (int)B;
+                    pp.H = (int)H;
+                    pp.t0 = (int)t0;
+                    pp.T = (int)(t1 - t0);
+                    pp.store_gates = 1;
+                    FLSTM_TRY(simt::persistent_forward(cfg.dtype, simt_grid, pp, s));
+                    FLSTM_CUDA_TRY(cudaMemcpyAsync(simt_err_host, sync_words, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
+                    ++launches;
+                } else {
+                    for (size_t t = t0; t < t1; ++t) {
+                        FLSTM_TRY(simt::step_forward(cfg.dtype, B, H, byte_ptr(l.hs) + t * slab * es, l.w_hh,
+                                                     byte_ptr(l.gates) + t * B * 4 * H * es, l.cs + t * slab,
+                                                     l.cs + (t + 1) * slab, byte_ptr(l.hs) + (t + 1) * slab * es,
+                                                     y_out ? byte_ptr(y_out) + t * slab * es : nullptr, s));
+                    }
+                    launches += t1 - t0;
                 }
-                launches += t1 - t0;
                 size_t m2 = timer.mark(s);
                 timer.span(PH_PROJ, m0, m1);
                 timer.span(PH_RECUR_FWD, m1, m2);
@@ -489,19 +523,47 @@ int Engine::backward_range(size_t T, size_t t0, size_t t1, const void *dy, const
                 if (dcn_l) { FLSTM_TRY(simt::convert(cfg.dtype, dcn_l, FLSTM_DTYPE_F32, dc_l, slab, s)); ++launches; }
                 else FLSTM_CUDA_TRY(cudaMemsetAsync(dc_l, 0, slab * sizeof(float), s));
             }
-            for (size_t step = 0; step < n; ++step) {
-                size_t t = t1 - 1 - step;
-                const void *dg_next = (t == T - 1) ? nullptr : byte_ptr(l.dg) + (t + 1) * B * 4 * H * es;
-                FLSTM_TRY(simt::step_backward(cfg.dtype, B, H, dg_next, l.w_hh, dhn_l,
-                                              byte_ptr(dy_l) + t * slab * es,
-                                              byte_ptr(l.gates) + t * B * 4 * H * es, l.cs + (t + 1) * slab,
-                                              l.cs + t * slab, dc_l, byte_ptr(l.dg) + t * B * 4 * H * es, s));
+            if (simt_grid) {
+                FLSTM_TRY(simt_check_error());
+                const size_t tiles = (size_t)simt::persistent_batch_tiles(B);
+                FLSTM_CUDA_TRY(cudaMemsetAsync(sync_words + 32, 0, tiles * sizeof(unsigned int), s));
+                simt::PersistentBwdParams pp{};
+                pp.w_hh = l.w_hh;
+                pp.cs = l.cs;
+                pp.gates = l.gates;
+                pp.dg = l.dg;
+                pp.dy = dy_l;
+                pp.dhn = dhn_l;
+                pp.dc = dc_l;
+                pp.dh0 = dh0_l;
+                pp.dc0 = dc0_l;
+                pp.counters = sync_words + 32;
+                pp.err = sync_words;
+                pp.B = (int)B;
+                pp.H = (int)H;
+                pp.T = (int)T;
+                pp.s0 = (int)(T - t1);
+                pp.s1 = (int)(T - t0) + ((t0 == 0 && (dh0_l || dc0_l)) ? 1 : 0);  // the last range also forms dh0 / dc0
+                FLSTM_TRY(simt::persistent_backward(cfg.dtype, simt_grid, pp, s));
+                FLSTM_CUDA_TRY(cudaMemcpyAsync(simt_err_host, sync_words, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
+                ++launches;
+            } else {
+                for (size_t step = 0; step < n; ++step) {
+                    size_t t = t1 - 1 - step;
+                    const void *dg_next = (t == T - 1) ? nullptr : byte_ptr(l.dg) + (t + 1) * B * 4 * H * es;
+                    FLSTM_TRY(simt::step_backward(cfg.dtype, B, H, dg_next, l.w_hh, dhn_l,
+                                                  byte_ptr(dy_l) + t * slab * es,
+                                                  byte_ptr(l.gates) + t * B * 4 * H * es, l.cs + (t + 1) * slab,
+                                                  l.cs + t * slab, dc_l, byte_ptr(l.dg) + t * B * 4 * H * es, s));
+                }
+                launches += n;
             }
-            launches += n;
             size_t m1 = timer.mark(s), m2 = m1;
             if (t0 == 0) {
-                if (dh0_l) { FLSTM_TRY(simt::final_dh(cfg.dtype, B, H, l.dg, l.w_hh, dh0_l, s)); ++launches; }
-                if (dc0_l) FLSTM_CUDA_TRY(cudaMemcpyAsync(dc0_l, dc_l, slab * sizeof(float), cudaMemcpyDeviceToDevice, s));
+                if (!simt_grid) {
+                    if (dh0_l) { FLSTM_TRY(simt::final_dh(cfg.dtype, B, H, l.dg, l.w_hh, dh0_l, s)); ++launches; }
+                    if (dc0_l) FLSTM_CUDA_TRY(cudaMemcpyAsync(dc0_l, dc_l, slab * sizeof(float), cudaMemcpyDeviceToDevice, s));
+                }
                 // deferred parameter gradients over the whole sequence
                 FLSTM_TRY(simt::gemm(cfg.dtype, FLSTM_DTYPE_F32, 4 * H, l.in_size, T * B, l.dg, 4 * H, false, x_l,
                                      l.in_size, false, l.dw_ih, l.in_size, nullptr, s));
@@ -635,6 +697,19 @@ int flstm_engine_create(const flstm_engine_config *config, flstm_engine **out) {
     if (e.backend == FLSTM_BACKEND_TC) {
         st = flstm_b200::tc::init(e);
         if (st != FLSTM_OK) return fail(st);
+    } else {
+        int grid = 0;
+        if (flstm_b200::simt::persistent_fits(config->dtype, B, H, config->training != 0, &grid)) {
+            void *raw = nullptr;
+            const size_t words = 32 + (size_t)flstm_b200::simt::persistent_batch_tiles(B);
+            if (cudaMalloc(&raw, words * sizeof(unsigned int)) != cudaSuccess) return fail(set_error(FLSTM_ERR_CUDA, "cudaMalloc failed"));
+            e.sync_words = static_cast<unsigned int *>(raw);
+            cudaMemset(raw, 0, words * sizeof(unsigned int));
+            if (cudaMallocHost(&raw, sizeof(unsigned int)) != cudaSuccess) return fail(set_error(FLSTM_ERR_CUDA, "cudaMallocHost failed"));
+            e.simt_err_host = static_cast<unsigned int *>(raw);
+            *e.simt_err_host = 0;
+            e.simt_grid = grid;
+        }
     }
     st = e.allocate(config->max_seq_len ? config->max_seq_len : 1);
     if (st != FLSTM_OK) return fail(st);
@@ -782,6 +857,7 @@ int flstm_engine_wait(flstm_engine *engine, cudaStream_t stream, unsigned int ti
                          had_comm ? "; the communicator was aborted" : "");
     }
     if (e.backend == FLSTM_BACKEND_TC) FLSTM_TRY(flstm_b200::tc::poll_error(e));
+    else FLSTM_TRY(e.simt_check_error());
     return FLSTM_OK;
 }
 

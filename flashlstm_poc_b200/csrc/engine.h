@@ -89,6 +89,10 @@ struct Engine {
     long long *trace = nullptr;  // device: [2 (fwd,bwd)][trace_steps][16] clock stamps of CTA 0
     int trace_steps = 0;
     void *tc_state = nullptr;  // tensor-core path: cached tensor maps etc. (tc_engine.cu)
+    // CUDA-core path: persistent recurrent kernels when the shape fits (simt_persistent.cu)
+    int simt_grid = 0;                       // 0: one launch per step
+    unsigned int *simt_err_host = nullptr;   // pinned mirror of the error word
+    int simt_check_error();
     // Cross-layer wavefront (wide-batch path with stacked layers): layer l > 0 runs its time chunks on
     // lanes[l] one chunk behind layer l-1, so independent per-step kernels of different layers share the GPU.
     std::vector<cudaStream_t> lanes;        // lanes[0] is the caller's stream (not owned)

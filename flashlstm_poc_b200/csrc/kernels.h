@@ -40,6 +40,39 @@ int step_backward(int dtype, size_t B, size_t H, const void *dg_next, const void
 // dh0 (fp32) = dg_0 W_hh
 int final_dh(int dtype, size_t B, size_t H, const void *dg0, const void *w_hh, float *dh0, cudaStream_t s);
 
+// ---- persistent fp32 recurrent kernels (simt_persistent.cu): one cooperative launch per layer and range
+struct PersistentFwdParams {
+    const void *w_hh;        // (4H, H) engine dtype, torch row order
+    void *hs;                // (T+1, B, H) engine dtype; slot t0 holds the state the launch starts from
+    float *cs;               // (T+1, B, H) fp32
+    void *gates;             // (T, B, 4H): projection in, activated gates out (when store_gates)
+    void *y;                 // optional (T, B, H) copy of h_t
+    unsigned int *counters;  // one per batch tile of 8 sequences, zeroed before the launch
+    unsigned int *err;       // error word (a bounded wait expired)
+    int B, H;
+    int t0, T;               // first step and number of steps of this launch
+    int store_gates;
+};
+struct PersistentBwdParams {
+    const void *w_hh;
+    const float *cs;
+    const void *gates;
+    void *dg;                // (T, B, 4H): written; dG_{t+1} is read back for the next iteration
+    const void *dy;          // (T, B, H)
+    const void *dhn;         // (B, H) or null: added at the last time step
+    float *dc;               // (B, H) fp32 cell-gradient carry: read at launch start, written at its end
+    float *dh0, *dc0;        // (B, H) fp32 or null, written by the iteration s == T
+    unsigned int *counters, *err;
+    int B, H;
+    int T;                   // length of the whole sequence
+    int s0, s1;              // reverse iterations [s0, s1): iteration s is time T-1-s
+};
+// whether the shape fits (shared memory for the W_hh slices, all CTAs co-resident); grid = CTAs to launch
+bool persistent_fits(int dtype, size_t B, size_t H, bool training, int *grid);
+int persistent_batch_tiles(size_t B);
+int persistent_forward(int dtype, int grid, PersistentFwdParams p, cudaStream_t s);
+int persistent_backward(int dtype, int grid, PersistentBwdParams p, cudaStream_t s);
+
 // out[n] = sum_r dg[r, n] over R rows (deterministic order)
 int column_sum(int dtype, const void *dg, size_t R, size_t N, float *out, cudaStream_t s);
 
