@@ -75,6 +75,7 @@ Engine::~Engine() {
         if (lanes[i]) cudaStreamDestroy(lanes[i]);
     for (auto ev : lane_events) cudaEventDestroy(ev);
     if (simt_err_host) cudaFreeHost(simt_err_host);
+    dev_free(simt_scratch);
     if (comm) comm_destroy(comm);
     if (comm_stream) cudaStreamDestroy(comm_stream);
     if (comm_fork) cudaEventDestroy(comm_fork);
@@ -566,9 +567,9 @@ int Engine::backward_range(size_t T, size_t t0, size_t t1, const void *dy, const
                 }
                 // deferred parameter gradients over the whole sequence
                 FLSTM_TRY(simt::gemm(cfg.dtype, FLSTM_DTYPE_F32, 4 * H, l.in_size, T * B, l.dg, 4 * H, false, x_l,
-                                     l.in_size, false, l.dw_ih, l.in_size, nullptr, s));
+                                     l.in_size, false, l.dw_ih, l.in_size, nullptr, s, simt_scratch, simt_scratch_floats));
                 FLSTM_TRY(simt::gemm(cfg.dtype, FLSTM_DTYPE_F32, 4 * H, H, T * B, l.dg, 4 * H, false, l.hs, H, false,
-                                     l.dw_hh, H, nullptr, s));
+                                     l.dw_hh, H, nullptr, s, simt_scratch, simt_scratch_floats));
                 FLSTM_TRY(simt::column_sum(cfg.dtype, l.dg, T * B, 4 * H, l.db, s));
                 launches += 3;
                 m2 = timer.mark(s);
@@ -698,6 +699,19 @@ int flstm_engine_create(const flstm_engine_config *config, flstm_engine **out) {
         st = flstm_b200::tc::init(e);
         if (st != FLSTM_OK) return fail(st);
     } else {
+        if (config->training) {
+            // room for up to 8 partial products of the largest weight gradient, at most 64 MiB
+            size_t widest = config->input_size > H ? config->input_size : H;
+            size_t floats = 8 * 4 * H * widest;
+            if (floats > (size_t)16 << 20) floats = (size_t)16 << 20;
+            void *raw = nullptr;
+            if (cudaMalloc(&raw, floats * sizeof(float)) == cudaSuccess) {
+                e.simt_scratch = static_cast<float *>(raw);
+                e.simt_scratch_floats = floats;
+            } else {
+                cudaGetLastError();  // the GEMMs then run unsplit
+            }
+        }
         int grid = 0;
         if (flstm_b200::simt::persistent_fits(config->dtype, B, H, config->training != 0, &grid)) {
             void *raw = nullptr;

@@ -93,6 +93,8 @@ struct Engine {
     int simt_grid = 0;                       // 0: one launch per step
     unsigned int *simt_err_host = nullptr;   // pinned mirror of the error word
     int simt_check_error();
+    float *simt_scratch = nullptr;           // split-K partial products of the weight-gradient GEMMs
+    size_t simt_scratch_floats = 0;
     // Cross-layer wavefront (wide-batch path with stacked layers): layer l > 0 runs its time chunks on
     // lanes[l] one chunk behind layer l-1, so independent per-step kernels of different layers share the GPU.
     std::vector<cudaStream_t> lanes;        // lanes[0] is the caller's stream (not owned)

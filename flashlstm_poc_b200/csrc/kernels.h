@@ -22,9 +22,11 @@ int gather_slabs(int src_dtype, const void *src, size_t slab_elems, size_t strid
 // C[M,N] (row-major, ldc) = sum_k A(m,k) B(k,n) (+ bias[n]); fp32 accumulation.
 //   a_kcontig: A(m,k) = A[m*lda + k]   else A(m,k) = A[k*lda + m]
 //   b_kcontig: B(k,n) = B[n*ldb + k]   else B(k,n) = B[k*ldb + n]
+// With a scratch buffer (fp32 C, no bias) long contractions with few output tiles are split along K into
+// partial products that a second kernel adds in a fixed order.
 int gemm(int ab_dtype, int c_dtype, size_t M, size_t N, size_t K, const void *A, size_t lda,
          bool a_kcontig, const void *B, size_t ldb, bool b_kcontig, void *C, size_t ldc,
-         const float *bias, cudaStream_t s);
+         const float *bias, cudaStream_t s, float *scratch = nullptr, size_t scratch_floats = 0);
 
 // One forward time step: gates = p_t + h_prev W_hh^T, activations, cell/hidden update.
 // p_t (B,4H) holds the input projection (bias included) and is overwritten with the

@@ -51,15 +51,20 @@ constexpr int BM = 64, BN = 64, BK = 16;
 
 template <typename TAB, typename TC, bool A_KC, bool B_KC>
 __global__ void __launch_bounds__(256)
-gemm_kernel(int M, int N, int K, const TAB *__restrict__ A, size_t lda, const TAB *__restrict__ B,
-            size_t ldb, TC *__restrict__ C, size_t ldc, const float *__restrict__ bias) {
+gemm_kernel(int M, int N, int K_total, const TAB *__restrict__ A, size_t lda, const TAB *__restrict__ B,
+            size_t ldb, TC *__restrict__ C, size_t ldc, const float *__restrict__ bias, int k_per_split,
+            size_t c_split_stride) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Bs[BK][BN + 4];
     const int tid = threadIdx.x;
     const int tx = tid % 16, ty = tid / 16;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    // split K: block z contracts over [z * k_per_split, ...) and writes its own partial product
+    const int kz0 = blockIdx.z * k_per_split;
+    const int K = (kz0 + k_per_split < K_total) ? kz0 + k_per_split : K_total;
+    C += (size_t)blockIdx.z * c_split_stride;
     float acc[4][4] = {};
-    for (int k0 = 0; k0 < K; k0 += BK) {
+    for (int k0 = kz0; k0 < K; k0 += BK) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             int e = tid + i * 256;
@@ -323,21 +328,56 @@ int gather_from(const TI *src, size_t slab, size_t stride, size_t count, int dst
     return check_launch("gather_slabs");
 }
 
+__global__ void sum_splits_kernel(const float *__restrict__ parts, int splits, size_t M, size_t N, float *__restrict__ C,
+                                  size_t ldc) {
+    const size_t total = M * N;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float v = 0.f;
+        for (int z = 0; z < splits; ++z) v += parts[(size_t)z * total + i];  // fixed order: deterministic
+        C[(i / N) * ldc + i % N] = v;
+    }
+}
+
 template <typename TAB, typename TC>
 int gemm_typed(size_t M, size_t N, size_t K, const TAB *A, size_t lda, bool akc, const TAB *B, size_t ldb,
-               bool bkc, TC *C, size_t ldc, const float *bias, cudaStream_t s) {
-    dim3 grid(ceil_div(N, BN), ceil_div(M, BM));
-    if (akc && bkc) gemm_kernel<TAB, TC, true, true><<<grid, 256, 0, s>>>((int)M, (int)N, (int)K, A, lda, B, ldb, C, ldc, bias);
-    else if (akc && !bkc) gemm_kernel<TAB, TC, true, false><<<grid, 256, 0, s>>>((int)M, (int)N, (int)K, A, lda, B, ldb, C, ldc, bias);
-    else if (!akc && bkc) gemm_kernel<TAB, TC, false, true><<<grid, 256, 0, s>>>((int)M, (int)N, (int)K, A, lda, B, ldb, C, ldc, bias);
-    else gemm_kernel<TAB, TC, false, false><<<grid, 256, 0, s>>>((int)M, (int)N, (int)K, A, lda, B, ldb, C, ldc, bias);
-    return check_launch("gemm");
+               bool bkc, TC *C, size_t ldc, const float *bias, cudaStream_t s, int splits = 1, float *parts = nullptr) {
+    dim3 grid(ceil_div(N, BN), ceil_div(M, BM), splits);
+    const int kper = splits > 1 ? (int)(((K + splits - 1) / splits + BK - 1) / BK * BK) : (int)K;
+    TC *out = C;
+    size_t out_ld = ldc, stride = 0;
+    if (splits > 1) {  // partial products go to the scratch buffer (only instantiated for fp32 C)
+        out = reinterpret_cast<TC *>(parts);
+        out_ld = N;
+        stride = M * N;
+    }
+    if (akc && bkc) gemm_kernel<TAB, TC, true, true><<<grid, 256, 0, s>>>((int)M, (int)N, (int)K, A, lda, B, ldb, out, out_ld, bias, kper, stride);
+    else if (akc && !bkc) gemm_kernel<TAB, TC, true, false><<<grid, 256, 0, s>>>((int)M, (int)N, (int)K, A, lda, B, ldb, out, out_ld, bias, kper, stride);
+    else if (!akc && bkc) gemm_kernel<TAB, TC, false, true><<<grid, 256, 0, s>>>((int)M, (int)N, (int)K, A, lda, B, ldb, out, out_ld, bias, kper, stride);
+    else gemm_kernel<TAB, TC, false, false><<<grid, 256, 0, s>>>((int)M, (int)N, (int)K, A, lda, B, ldb, out, out_ld, bias, kper, stride);
+    FLSTM_TRY(check_launch("gemm"));
+    if (splits > 1) {
+        sum_splits_kernel<<<grid_1d(M * N), 256, 0, s>>>(parts, splits, M, N, reinterpret_cast<float *>(C), ldc);
+        return check_launch("gemm split sum");
+    }
+    return FLSTM_OK;
 }
 
 template <typename TAB>
 int gemm_ab(int c_dtype, size_t M, size_t N, size_t K, const TAB *A, size_t lda, bool akc, const TAB *B,
-            size_t ldb, bool bkc, void *C, size_t ldc, const float *bias, cudaStream_t s) {
-    if (c_dtype == FLSTM_DTYPE_F32) return gemm_typed(M, N, K, A, lda, akc, B, ldb, bkc, (float *)C, ldc, bias, s);
+            size_t ldb, bool bkc, void *C, size_t ldc, const float *bias, cudaStream_t s, float *scratch,
+            size_t scratch_floats) {
+    if (c_dtype == FLSTM_DTYPE_F32) {
+        // long contractions with few output tiles (the weight gradients): split K over grid.z into the scratch
+        // buffer, then add the partial products in a fixed order
+        int splits = 1;
+        const size_t tiles = (size_t)ceil_div(N, BN) * ceil_div(M, BM);
+        if (scratch && !bias && K >= 1024 && tiles < 148) {
+            while (splits < 8 && tiles * splits * 2 <= 296 && K / (splits * 2) >= 256 &&
+                   (size_t)(splits * 2) * M * N <= scratch_floats)
+                splits *= 2;
+        }
+        return gemm_typed(M, N, K, A, lda, akc, B, ldb, bkc, (float *)C, ldc, bias, s, splits, scratch);
+    }
     // a 16-bit C has the same type as A and B
     return gemm_typed(M, N, K, A, lda, akc, B, ldb, bkc, (TAB *)C, ldc, bias, s);
 }
@@ -372,14 +412,15 @@ int gather_slabs(int src_dtype, const void *src, size_t slab, size_t stride, siz
 }
 
 int gemm(int ab_dtype, int c_dtype, size_t M, size_t N, size_t K, const void *A, size_t lda, bool akc,
-         const void *B, size_t ldb, bool bkc, void *C, size_t ldc, const float *bias, cudaStream_t s) {
+         const void *B, size_t ldb, bool bkc, void *C, size_t ldc, const float *bias, cudaStream_t s, float *scratch,
+         size_t scratch_floats) {
     if (M == 0 || N == 0) return FLSTM_OK;
     if (c_dtype != FLSTM_DTYPE_F32 && c_dtype != ab_dtype)
         return set_error(FLSTM_ERR_INVALID, "gemm: C dtype must be f32 or the operand dtype");
     switch (ab_dtype) {
-        case FLSTM_DTYPE_F32: return gemm_ab(c_dtype, M, N, K, (const float *)A, lda, akc, (const float *)B, ldb, bkc, C, ldc, bias, s);
-        case FLSTM_DTYPE_F16: return gemm_ab(c_dtype, M, N, K, (const __half *)A, lda, akc, (const __half *)B, ldb, bkc, C, ldc, bias, s);
-        case FLSTM_DTYPE_BF16: return gemm_ab(c_dtype, M, N, K, (const __nv_bfloat16 *)A, lda, akc, (const __nv_bfloat16 *)B, ldb, bkc, C, ldc, bias, s);
+        case FLSTM_DTYPE_F32: return gemm_ab(c_dtype, M, N, K, (const float *)A, lda, akc, (const float *)B, ldb, bkc, C, ldc, bias, s, scratch, scratch_floats);
+        case FLSTM_DTYPE_F16: return gemm_ab(c_dtype, M, N, K, (const __half *)A, lda, akc, (const __half *)B, ldb, bkc, C, ldc, bias, s, scratch, scratch_floats);
+        case FLSTM_DTYPE_BF16: return gemm_ab(c_dtype, M, N, K, (const __nv_bfloat16 *)A, lda, akc, (const __nv_bfloat16 *)B, ldb, bkc, C, ldc, bias, s, scratch, scratch_floats);
     }
     return set_error(FLSTM_ERR_INVALID, "gemm: bad dtype %d", ab_dtype);
 }
