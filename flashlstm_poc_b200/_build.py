@@ -56,7 +56,7 @@ def _fingerprint() -> str:
         for base, _, files in os.walk(d):
             paths += [os.path.join(base, f) for f in files]
     for p in sorted(paths) + [os.path.abspath(__file__)]:
-        h.update(p.encode())
+        h.update(os.path.relpath(p, ROOT).encode())  # the tree may sit elsewhere on another machine
         with open(p, "rb") as f:
             h.update(f.read())
     h.update(" ".join(NVCC_FLAGS).encode())
