@@ -140,7 +140,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 const int t_src = p.T - s;  // dG_{t+1} with t = T-1-s
                 if (s > p.s0) ok = wait_counter(counter, (unsigned)(p.jt * KS) * (unsigned)(s - p.s0), p.err, abort_w, 3u);
                 if (!ok) break;
-                fence_proxy_async_all();
+                fence_proxy_async_global();
                 FLSTM_STAMP(s - p.s0, 0);
                 for (int n = 0; n < nt_count && ok; ++n) {
                     const int b0 = (ng * nt_count + n) * BT;

@@ -149,7 +149,7 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                             // starts from was completed by the previous launch
                             ok = wait_counter(counter, (unsigned)(p.cta_rows) * (unsigned)tt, p.err, abort_w, 2u);
                             if (!ok) break;
-                            fence_proxy_async_all();
+                            fence_proxy_async_global();
                         }
                         if (first) FLSTM_STAMP(tt, 0);
                         first = false;
