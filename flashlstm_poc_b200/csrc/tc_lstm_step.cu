@@ -388,7 +388,7 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     if (threadIdx.x == 0 && *abort_w) atomicExch(a.err, 1u);
 }
 
-// Pointwise backward of one time step for 8 hidden units of one sequence per thread:
+// Pointwise backward of one time step for 4 hidden units of one sequence per thread:
 //   dh = dy_t + sum of the fp32 partial products dG_{t+1} W_hh;  dc, dG_t as in the persistent BPTT kernel.
 template <bool BF16>
 __global__ void __launch_bounds__(256)
@@ -396,78 +396,53 @@ step_bwd_pointwise_kernel(const uint16_t *__restrict__ gates_t, const float *__r
                           const float *__restrict__ c_prev, const uint16_t *__restrict__ dy_t,
                           const float *__restrict__ parts, int nparts, float *__restrict__ dc,
                           uint16_t *__restrict__ dg_t, int B, int H) {
-    const int octets = H >> 3;
-    const size_t total = (size_t)B * octets, slab = (size_t)B * H;
+    const int quads = H >> 2;
+    const size_t total = (size_t)B * quads, slab = (size_t)B * H;
     grid_dependency_wait();
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const int b = (int)(i / octets), U0 = (int)(i % octets) * 8;
+        const int b = (int)(i / quads), U0 = (int)(i % quads) * 4;
         const size_t sidx = (size_t)b * H + U0;
-        // columns of the four gates of units U0..U0+7 in the tile-interleaved order
+        // columns of the four gates of units U0..U0+3 in the tile-interleaved order
         const size_t gcol = (size_t)b * 4 * H + (size_t)(U0 >> 4) * 64 + (U0 & 15);
-        float gate[4][8], ct[8], cp[8], dh[8], dcv[8];
+        float gate[4][4], dh[4];
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-            const uint4 v = *reinterpret_cast<const uint4 *>(gates_t + gcol + g * 16);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const float2 f = unpack2<BF16>(w[k]);
-                gate[g][2 * k] = f.x;
-                gate[g][2 * k + 1] = f.y;
-            }
+            const uint2 v = *reinterpret_cast<const uint2 *>(gates_t + gcol + g * 16);
+            const float2 lo = unpack2<BF16>(v.x), hi = unpack2<BF16>(v.y);
+            gate[g][0] = lo.x; gate[g][1] = lo.y; gate[g][2] = hi.x; gate[g][3] = hi.y;
         }
         {
-            const uint4 v = *reinterpret_cast<const uint4 *>(dy_t + sidx);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const float2 f = unpack2<BF16>(w[k]);
-                dh[2 * k] = f.x;
-                dh[2 * k + 1] = f.y;
-            }
+            const uint2 v = *reinterpret_cast<const uint2 *>(dy_t + sidx);
+            const float2 lo = unpack2<BF16>(v.x), hi = unpack2<BF16>(v.y);
+            dh[0] = lo.x; dh[1] = lo.y; dh[2] = hi.x; dh[3] = hi.y;
         }
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const float4 a = *reinterpret_cast<const float4 *>(c_t + sidx + 4 * h);
-            const float4 p = *reinterpret_cast<const float4 *>(c_prev + sidx + 4 * h);
-            const float4 d = *reinterpret_cast<const float4 *>(dc + sidx + 4 * h);
-            ct[4 * h] = a.x; ct[4 * h + 1] = a.y; ct[4 * h + 2] = a.z; ct[4 * h + 3] = a.w;
-            cp[4 * h] = p.x; cp[4 * h + 1] = p.y; cp[4 * h + 2] = p.z; cp[4 * h + 3] = p.w;
-            dcv[4 * h] = d.x; dcv[4 * h + 1] = d.y; dcv[4 * h + 2] = d.z; dcv[4 * h + 3] = d.w;
+        const float4 ctv = *reinterpret_cast<const float4 *>(c_t + sidx);
+        const float4 cpv = *reinterpret_cast<const float4 *>(c_prev + sidx);
+        const float4 dcv4 = *reinterpret_cast<const float4 *>(dc + sidx);
+        const float ct[4] = {ctv.x, ctv.y, ctv.z, ctv.w}, cp[4] = {cpv.x, cpv.y, cpv.z, cpv.w};
+        const float dcin[4] = {dcv4.x, dcv4.y, dcv4.z, dcv4.w};
+        for (int s = 0; s < nparts; ++s) {
+            const float4 r = *reinterpret_cast<const float4 *>(parts + (size_t)s * slab + sidx);
+            dh[0] += r.x; dh[1] += r.y; dh[2] += r.z; dh[3] += r.w;
         }
-        {
-            float rec[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int s = 0; s < nparts; ++s) {
+        float da[4][4], dcp[4];
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const float4 r = *reinterpret_cast<const float4 *>(parts + (size_t)s * slab + sidx + 4 * h);
-                    rec[4 * h] += r.x; rec[4 * h + 1] += r.y; rec[4 * h + 2] += r.z; rec[4 * h + 3] += r.w;
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) dh[u] += rec[u];
-        }
-        float da[4][8], dcp[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < 4; ++u) {
             const float gi = gate[0][u], gf = gate[1][u], gg = gate[2][u], go = gate[3][u];
             const float tc = tanh_fast(ct[u]);
             const float d_o = dh[u] * tc;
-            const float dcu = dcv[u] + dh[u] * go * (1.f - tc * tc);
+            const float dcu = dcin[u] + dh[u] * go * (1.f - tc * tc);
             da[0][u] = dcu * gg * gi * (1.f - gi);
             da[1][u] = dcu * cp[u] * gf * (1.f - gf);
             da[2][u] = dcu * gi * (1.f - gg * gg);
             da[3][u] = d_o * go * (1.f - go);
             dcp[u] = dcu * gf;
         }
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-            *reinterpret_cast<float4 *>(dc + sidx + 4 * h) = make_float4(dcp[4 * h], dcp[4 * h + 1], dcp[4 * h + 2], dcp[4 * h + 3]);
+        *reinterpret_cast<float4 *>(dc + sidx) = make_float4(dcp[0], dcp[1], dcp[2], dcp[3]);
 #pragma unroll
         for (int g = 0; g < 4; ++g)
-            *reinterpret_cast<uint4 *>(dg_t + gcol + g * 16) =
-                make_uint4(pack2<BF16>(da[g][0], da[g][1]), pack2<BF16>(da[g][2], da[g][3]),
-                           pack2<BF16>(da[g][4], da[g][5]), pack2<BF16>(da[g][6], da[g][7]));
+            *reinterpret_cast<uint2 *>(dg_t + gcol + g * 16) =
+                make_uint2(pack2<BF16>(da[g][0], da[g][1]), pack2<BF16>(da[g][2], da[g][3]));
     }
 }
 
@@ -581,9 +556,9 @@ int lstm_step_backward_gemm(int dtype, const StepPlan &plan, const CUtensorMap &
 
 int lstm_step_backward_pointwise(int dtype, const void *gates_t, const float *c_t, const float *c_prev, const void *dy_t,
                                  const float *parts, int nparts, float *dc, void *dg_t, int B, int H, cudaStream_t s) {
-    const size_t total = (size_t)B * (H / 8);
+    const size_t total = (size_t)B * (H / 4);
     int grid = (int)((total + 255) / 256);
-    if (grid > 148 * 8) grid = 148 * 8;
+    if (grid > 148 * 16) grid = 148 * 16;
     const uint16_t *g16 = static_cast<const uint16_t *>(gates_t), *dy16 = static_cast<const uint16_t *>(dy_t);
     uint16_t *dg16 = static_cast<uint16_t *>(dg_t);
     cudaError_t e = dtype == FLSTM_DTYPE_BF16
