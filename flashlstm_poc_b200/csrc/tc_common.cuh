@@ -94,7 +94,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
 }
 
 // ------------------------------------------------------------------ proxies and fences
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 // global memory only: what a TMA load of data that other SMs wrote with ordinary stores needs
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
