@@ -18,7 +18,7 @@ ENGINE_SYMBOLS = [
     "flstm_engine_enable_timing", "flstm_engine_phase_ms", "flstm_engine_launch_count", "flstm_tc_gemm",
     "flstm_engine_enable_trace", "flstm_engine_read_trace", "flstm_bias_grad", "flstm_tc_plan", "flstm_engine_wait", "flstm_engine_abort_comm",
                   "flstm_engine_set_recompute_interval", "flstm_engine_workspace_bytes",
-    "flstm_bias_grad_static",
+    "flstm_bias_grad_static", "flstm_engine_set_wait_limit", "flstm_engine_selftest_missing_arrivals",
     "flstm_last_error",
     "flstm_version",
 ]
@@ -105,6 +105,8 @@ def load() -> ctypes.CDLL:
     lib.flstm_tc_plan.argtypes = [sz, sz, ci, ci, sz, ctypes.POINTER(TcPlanInfo)]
     lib.flstm_engine_wait.argtypes = [vp, vp, ctypes.c_uint]
     lib.flstm_engine_abort_comm.argtypes = [vp]
+    lib.flstm_engine_set_wait_limit.argtypes = [vp, ctypes.c_ulonglong]
+    lib.flstm_engine_selftest_missing_arrivals.argtypes = [vp, ctypes.c_uint]
     lib.flstm_engine_set_recompute_interval.argtypes = [vp, sz]
     lib.flstm_engine_workspace_bytes.argtypes = [vp]
     lib.flstm_engine_workspace_bytes.restype = sz

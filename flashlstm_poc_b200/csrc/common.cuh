@@ -81,4 +81,13 @@ __device__ __forceinline__ float sigmoid_fast(float a) { return fmaf(0.5f, tanh_
 
 inline int ceil_div(size_t a, size_t b) { return static_cast<int>((a + b - 1) / b); }
 
+// Opt-in dynamic shared memory above 48 KB.  cudaFuncSetAttribute acts on the CURRENT device only, so the
+// largest limit set so far is remembered per (kernel, device); one process may drive several GPUs from
+// several threads (engine.cu).  The limit of a kernel only ever grows: engines of different shapes share it.
+cudaError_t ensure_smem_limit(const void *kernel, int bytes);
+template <typename Kern>
+inline cudaError_t ensure_smem_limit(Kern kernel, size_t bytes) {
+    return ensure_smem_limit(reinterpret_cast<const void *>(kernel), static_cast<int>(bytes));
+}
+
 }  // namespace flstm_b200

@@ -10,8 +10,11 @@
 
 #include <chrono>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <new>
 #include <thread>
+#include <utility>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -31,6 +34,20 @@ int set_error(int status, const char *fmt, ...) {
     va_end(ap);
     last_error_slot() = buf;
     return status;
+}
+
+cudaError_t ensure_smem_limit(const void *kernel, int bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<const void *, int>, int> limits;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lock(mu);
+    int &have = limits[{kernel, dev}];
+    if (have >= bytes) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) have = bytes;
+    return e;
 }
 
 namespace {
@@ -308,6 +325,8 @@ int Engine::forward_range(size_t T, size_t t0, size_t t1, const void *x, const v
                     pp.t0 = (int)t0;
                     pp.T = (int)(t1 - t0);
                     pp.store_gates = 1;
+                    pp.wait_ns = wait_limit_ns;
+                    pp.extra_arrivals = selftest_missing_arrivals;
                     FLSTM_TRY(simt::persistent_forward(cfg.dtype, simt_grid, pp, s));
                     FLSTM_CUDA_TRY(cudaMemcpyAsync(simt_err_host, sync_words, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
                     ++launches;
@@ -545,6 +564,8 @@ int Engine::backward_range(size_t T, size_t t0, size_t t1, const void *dy, const
                 pp.T = (int)T;
                 pp.s0 = (int)(T - t1);
                 pp.s1 = (int)(T - t0) + ((t0 == 0 && (dh0_l || dc0_l)) ? 1 : 0);  // the last range also forms dh0 / dc0
+                pp.wait_ns = wait_limit_ns;
+                pp.extra_arrivals = selftest_missing_arrivals;
                 FLSTM_TRY(simt::persistent_backward(cfg.dtype, simt_grid, pp, s));
                 FLSTM_CUDA_TRY(cudaMemcpyAsync(simt_err_host, sync_words, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
                 ++launches;
@@ -633,6 +654,21 @@ PhaseTimer::~PhaseTimer() {
 // ====================================================================== C ABI
 using flstm_b200::Engine;
 using flstm_b200::set_error;
+
+namespace {
+// Every entry point works on the engine's own device, whatever device is current on the calling thread,
+// and leaves the caller's current device as it found it.
+struct DeviceScope {
+    int prev = -1;
+    bool switched = false;
+    explicit DeviceScope(int dev) {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) switched = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceScope() {
+        if (switched) cudaSetDevice(prev);
+    }
+};
+}  // namespace
 
 extern "C" {
 
@@ -733,7 +769,7 @@ int flstm_engine_create(const flstm_engine_config *config, flstm_engine **out) {
 
 int flstm_engine_destroy(flstm_engine *engine) {
     if (!engine) return FLSTM_OK;
-    cudaSetDevice(engine->impl.device);
+    DeviceScope scope(engine->impl.device);
     cudaDeviceSynchronize();
     delete engine;
     return FLSTM_OK;
@@ -742,30 +778,35 @@ int flstm_engine_destroy(flstm_engine *engine) {
 int flstm_engine_set_weights(flstm_engine *engine, int layer, const float *w_ih, const float *w_hh,
                              const float *b_ih, const float *b_hh, void *stream) {
     if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    DeviceScope scope(engine->impl.device);
     return engine->impl.set_weights(layer, w_ih, w_hh, b_ih, b_hh, static_cast<cudaStream_t>(stream));
 }
 
 int flstm_engine_forward(flstm_engine *engine, size_t seq_len, const void *x, const void *h0, const void *c0,
                          void *y, void *h_n, void *c_n, void *stream) {
     if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    DeviceScope scope(engine->impl.device);
     return engine->impl.forward(seq_len, x, h0, c0, y, h_n, c_n, static_cast<cudaStream_t>(stream));
 }
 
 int flstm_engine_backward(flstm_engine *engine, size_t seq_len, const void *dy, const void *d_hn,
                           const void *d_cn, void *dx, float *dh0, float *dc0, void *stream) {
     if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    DeviceScope scope(engine->impl.device);
     return engine->impl.backward(seq_len, dy, d_hn, d_cn, dx, dh0, dc0, static_cast<cudaStream_t>(stream));
 }
 
 int flstm_engine_forward_range(flstm_engine *engine, size_t seq_len, size_t t0, size_t t1, const void *x, const void *h0,
                                const void *c0, void *y, void *h_n, void *c_n, void *stream) {
     if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    DeviceScope scope(engine->impl.device);
     return engine->impl.forward_range(seq_len, t0, t1, x, h0, c0, y, h_n, c_n, static_cast<cudaStream_t>(stream));
 }
 
 int flstm_engine_backward_range(flstm_engine *engine, size_t seq_len, size_t t0, size_t t1, const void *dy,
                                 const void *d_hn, const void *d_cn, void *dx, float *dh0, float *dc0, void *stream) {
     if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    DeviceScope scope(engine->impl.device);
     return engine->impl.backward_range(seq_len, t0, t1, dy, d_hn, d_cn, dx, dh0, dc0, static_cast<cudaStream_t>(stream));
 }
 
@@ -812,7 +853,7 @@ int flstm_engine_attach_comm(flstm_engine *engine, const void *id128, int rank, 
     if (!engine || !id128) return set_error(FLSTM_ERR_INVALID, "null argument");
     Engine &e = engine->impl;
     if (e.comm) return set_error(FLSTM_ERR_INVALID, "a communicator is already attached");
-    cudaSetDevice(e.device);
+    DeviceScope scope(e.device);
     int st = flstm_b200::comm_create(id128, rank, world_size, &e.comm);
     if (st != FLSTM_OK) return st;
     e.comm_aborted = false;
@@ -826,7 +867,7 @@ int flstm_engine_attach_comm(flstm_engine *engine, const void *id128, int rank, 
 
 int flstm_engine_set_recompute_interval(flstm_engine *engine, size_t interval) {
     if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
-    cudaSetDevice(engine->impl.device);
+    DeviceScope scope(engine->impl.device);
     return engine->impl.set_recompute(interval);
 }
 
@@ -846,7 +887,7 @@ int flstm_engine_abort_comm(flstm_engine *engine) {
 int flstm_engine_wait(flstm_engine *engine, cudaStream_t stream, unsigned int timeout_ms) {
     if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
     Engine &e = engine->impl;
-    cudaSetDevice(e.device);
+    DeviceScope scope(e.device);
     cudaEvent_t done = nullptr;
     FLSTM_CUDA_TRY(cudaEventCreateWithFlags(&done, cudaEventDisableTiming));
     cudaError_t err = cudaEventRecord(done, stream);
@@ -878,6 +919,7 @@ int flstm_engine_wait(flstm_engine *engine, cudaStream_t stream, unsigned int ti
 int flstm_engine_enable_trace(flstm_engine *engine, int steps) {
     if (!engine || steps < 0) return set_error(FLSTM_ERR_INVALID, "bad argument");
     Engine &e = engine->impl;
+    DeviceScope scope(e.device);
     cudaDeviceSynchronize();
     if (e.trace) cudaFree(e.trace);
     e.trace = nullptr;
@@ -895,6 +937,7 @@ int flstm_engine_enable_trace(flstm_engine *engine, int steps) {
 int flstm_engine_read_trace(flstm_engine *engine, long long *out_host, size_t count) {
     if (!engine || !out_host) return set_error(FLSTM_ERR_INVALID, "null argument");
     Engine &e = engine->impl;
+    DeviceScope scope(e.device);
     const size_t have = (size_t)2 * e.trace_steps * 16;
     if (!e.trace || count > have) return set_error(FLSTM_ERR_INVALID, "trace holds %zu values", have);
     if (cudaMemcpy(out_host, e.trace, count * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess)
@@ -911,7 +954,20 @@ int flstm_engine_enable_timing(flstm_engine *engine, int enabled) {
 
 int flstm_engine_phase_ms(flstm_engine *engine, float *out6) {
     if (!engine || !out6) return set_error(FLSTM_ERR_INVALID, "null argument");
+    DeviceScope scope(engine->impl.device);
     return engine->impl.timer.totals(out6);
+}
+
+int flstm_engine_set_wait_limit(flstm_engine *engine, unsigned long long limit_us) {
+    if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    engine->impl.wait_limit_ns = limit_us * 1000ull;
+    return FLSTM_OK;
+}
+
+int flstm_engine_selftest_missing_arrivals(flstm_engine *engine, unsigned int arrivals) {
+    if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    engine->impl.selftest_missing_arrivals = arrivals;
+    return FLSTM_OK;
 }
 
 unsigned long long flstm_engine_launch_count(const flstm_engine *engine) {

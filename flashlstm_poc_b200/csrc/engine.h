@@ -79,6 +79,10 @@ struct Engine {
     size_t fwd_progress = 0; // steps of the current forward already enqueued
     size_t bwd_progress = 0; // backward has been enqueued down to this step
     unsigned long long launches = 0;
+    // Limit of every device-side wait of the persistent kernels in nanoseconds (0 = the kernels' 2 s default) and
+    // the timeout self-test: a step barrier that waits for this many arrivals which nobody makes.
+    unsigned long long wait_limit_ns = 0;
+    unsigned int selftest_missing_arrivals = 0;
     bool cell_io_f32 = false;       // c0 / c_n cross the API as fp32 instead of the engine dtype
     const void *x_saved = nullptr;  // layer-0 input of the last forward (caller keeps it alive)
     PhaseTimer timer;

@@ -54,6 +54,8 @@ struct PersistentFwdParams {
     int B, H;
     int t0, T;               // first step and number of steps of this launch
     int store_gates;
+    unsigned long long wait_ns;   // limit of the step-barrier wait (0 = the 2 s default)
+    unsigned int extra_arrivals;  // self-test of the timeout path: wait for this many arrivals nobody makes
 };
 struct PersistentBwdParams {
     const void *w_hh;
@@ -68,6 +70,8 @@ struct PersistentBwdParams {
     int B, H;
     int T;                   // length of the whole sequence
     int s0, s1;              // reverse iterations [s0, s1): iteration s is time T-1-s
+    unsigned long long wait_ns;   // as in PersistentFwdParams
+    unsigned int extra_arrivals;
 };
 // whether the shape fits (shared memory for the W_hh slices, all CTAs co-resident); grid = CTAs to launch
 bool persistent_fits(int dtype, size_t B, size_t H, bool training, int *grid);

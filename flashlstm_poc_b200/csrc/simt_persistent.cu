@@ -59,7 +59,9 @@ persistent_forward_kernel(PersistentFwdParams p) {
         const int t = p.t0 + tt;
         if (tt > 0) {
             // h_{t-1} of this batch tile is complete when each of its unit_tiles CTAs has arrived tt times
-            if (tid == 0 && !wait_counter(counter, (unsigned)unit_tiles * (unsigned)tt, p.err, &abort_w, 5u)) abort_w = 1;
+            if (tid == 0 && !wait_counter(counter, (unsigned)unit_tiles * (unsigned)tt + p.extra_arrivals, p.err, &abort_w, 5u,
+                                          p.wait_ns ? p.wait_ns : tc::kWaitLimitNs))
+                abort_w = 1;
             __syncthreads();
             if (abort_w) break;
         }
@@ -135,7 +137,9 @@ persistent_backward_kernel(PersistentBwdParams p) {
         float acc = 0.f;
         if (s > 0) {
             if (s > p.s0) {
-                if (tid == 0 && !wait_counter(counter, (unsigned)unit_tiles * (unsigned)(s - p.s0), p.err, &abort_w, 6u)) abort_w = 1;
+                if (tid == 0 && !wait_counter(counter, (unsigned)unit_tiles * (unsigned)(s - p.s0) + p.extra_arrivals, p.err, &abort_w,
+                                              6u, p.wait_ns ? p.wait_ns : tc::kWaitLimitNs))
+                    abort_w = 1;
                 __syncthreads();
                 if (abort_w) break;
             }
@@ -180,16 +184,12 @@ persistent_backward_kernel(PersistentBwdParams p) {
     if (tid == 0 && abort_w) atomicCAS(p.err, 0u, 1u);
 }
 
-// The opt-in shared-memory limit of a kernel only ever grows: engines of different widths share the kernels.
 template <typename Kern>
 bool raise_smem_limit(Kern kern, size_t smem) {
-    static size_t configured = 0;  // per kernel instantiation
-    if (smem <= configured) return true;
-    if (cudaFuncSetAttribute(reinterpret_cast<const void *>(kern), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    if (ensure_smem_limit(kern, smem) != cudaSuccess) {
         cudaGetLastError();
         return false;
     }
-    configured = smem;
     return true;
 }
 

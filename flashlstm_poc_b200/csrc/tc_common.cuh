@@ -2,8 +2,9 @@
 //   mbarrier (init / expect-tx / bounded wait), TMA tiled loads and stores
 //   (cp.async.bulk.tensor, one CTA per copy), tcgen05 (TMEM alloc, UMMA issue, commit, TMEM loads),
 //   shared-memory matrix descriptors and the UMMA instruction descriptor.
-// Every wait is bounded: after kWaitLimitNs the waiter raises an abort word and returns false, so a
-// kernel always terminates and the host reports FLSTM_ERR_TIMEOUT instead of hanging the GPU.
+// Every wait is bounded: after its limit (kWaitLimitNs unless the launch passes another one) the waiter raises
+// an abort word and returns false, so a kernel always terminates and the host reports FLSTM_ERR_TIMEOUT
+// instead of hanging the GPU.
 #pragma once
 
 #include <cuda.h>
@@ -14,7 +15,7 @@
 namespace flstm_b200 {
 namespace tc {
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s: the default limit of every device-side wait
 
 // ------------------------------------------------------------------ small utilities
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -77,18 +78,30 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  `abort_word` lives in shared memory and is shared by every waiter of the CTA.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_word) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_word,
+                                          unsigned long long limit_ns = kWaitLimitNs) {
     if (mbar_test_wait(bar, parity)) return true;
     const unsigned long long t0 = global_timer_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 255u) == 0) {
             if (*abort_word) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
+            if (global_timer_ns() - t0 > limit_ns) {
                 *abort_word = 1;
                 return false;
             }
         }
+    }
+    return true;
+}
+// Bounded wait that does not look at the abort word: used on the way out of a kernel to let copies that are
+// still in flight towards this CTA's shared memory land before the CTA exits.
+__device__ __forceinline__ bool mbar_drain(uint64_t *bar, uint32_t parity, unsigned long long limit_ns = kWaitLimitNs) {
+    if (mbar_test_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 255u) == 0 && global_timer_ns() - t0 > limit_ns) return false;
     }
     return true;
 }

@@ -270,6 +270,8 @@ int forward_layer(Engine &e, int li, size_t t0, size_t t1, const void *x_l, void
     p.store_gates = (e.cfg.training && e.seg.keep_gates) ? 1 : 0;
     p.trace = (li == 0 && t0 == 0) ? e.trace : nullptr;
     p.trace_steps = e.trace_steps;
+    p.wait_ns = e.wait_limit_ns;
+    p.extra_arrivals = e.selftest_missing_arrivals;
     FLSTM_TRY(lstm_forward_persistent(e.cfg.dtype, st->fwd, t.tm_w, t.tm_h, t.tm_g, p, s));
     size_t m2 = e.timer.mark(s);
     e.timer.span(PH_PROJ, m0, m1);
@@ -364,6 +366,8 @@ int backward_layer(Engine &e, int li, size_t T, size_t t0, size_t t1, const void
     p.s1 = (int)(T - t0) + (finalize ? 1 : 0);  // the last range also runs the iteration that writes dh0 / dc0
     p.B = (int)B;
     p.H = (int)H;
+    p.wait_ns = e.wait_limit_ns;
+    p.extra_arrivals = e.selftest_missing_arrivals;
     FLSTM_TRY(lstm_backward_persistent(e.cfg.dtype, st->bwd, t.tm_w, t.tm_dg, p, s));
     e.launches += 1;
     }
@@ -471,7 +475,7 @@ extern "C" int flstm_tc_plan(size_t batch, size_t hidden_size, int training, int
     out->fwd_smem_bytes = f.smem_bytes;
     if (training) {
         tc::BwdPlan b{};
-        FLSTM_TRY(tc::plan_bwd((int)batch, (int)hidden_size, sm_count, smem_limit, &b));
+        FLSTM_TRY(tc::plan_bwd((int)batch, (int)hidden_size, sm_count, smem_limit, &b, /*check_device=*/false));
         out->bwd_batch_tile = b.BT;
         out->bwd_cluster_size = b.KS;
         out->bwd_grid = b.grid;

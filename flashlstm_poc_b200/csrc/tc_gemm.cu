@@ -333,11 +333,7 @@ template <int BN, int MODE, bool HAS_BIAS, bool A_MN, bool B_MN, bool TMA_OUT>
 int launch_one(const GemmArgs &g) {
     using S = GemmShape<BN>;
     auto kern = gemm_kernel<BN, MODE, HAS_BIAS, A_MN, B_MN, TMA_OUT>;
-    static bool configured = false;  // per instantiation
-    if (!configured) {
-        FLSTM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes));
-        configured = true;
-    }
+    FLSTM_CUDA_TRY(ensure_smem_limit(kern, (size_t)S::kSmemBytes));
     const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
     const int grid = tiles < g.sms ? tiles : g.sms;
     kern<<<grid, kGemmThreads, S::kSmemBytes, g.s>>>(g.ta, g.tb, g.td, g.D, g.ldd, g.bias, g.M, g.N, g.K, g.idesc,

@@ -47,6 +47,8 @@ struct FwdParams {
     int store_gates;      // write the activated gates back (the gate cache)
     long long *trace;     // optional: CTA 0 stamps clock64() at 16 points of each of the first trace_steps steps
     int trace_steps;
+    unsigned long long wait_ns;   // limit of every device-side wait (0 = the 2 s default)
+    unsigned int extra_arrivals;  // self-test of the timeout path: the step barrier waits for this many arrivals nobody makes
     // filled by the launcher from the plan
     int rt, cta_rows, nt, stages, ch;
     uint32_t idesc;
@@ -86,11 +88,15 @@ struct BwdParams {
     int trace_steps;
     int T, B, H;          // T = length of the whole sequence
     int s0, s1;           // reverse iterations [s0, s1) of this launch; iteration s is time T-1-s, s == T writes dh0/dc0
+    unsigned long long wait_ns;   // limit of every device-side wait (0 = the 2 s default)
+    unsigned int extra_arrivals;  // self-test of the timeout path (see FwdParams)
     int jt, nt, stages, ch;
     uint32_t idesc;
 };
 
-int plan_bwd(int B, int H, int sms, size_t smem_limit, BwdPlan *plan);
+// check_device: verify with the occupancy query of the CURRENT device that all clusters of the grid are resident
+// at once (shrinking the number of batch groups if need be) and fail when they are not; false = host arithmetic only.
+int plan_bwd(int B, int H, int sms, size_t smem_limit, BwdPlan *plan, bool check_device = true);
 // tm_w: the same map as the forward's (W_hh rows tile-interleaved, 64x64 boxes): the BPTT reads the
 // slice as an MN-major operand.  tm_dg: dG as a chunked map (make_tensor_map_chunked) of width 4H
 // with box rows BT and plan.ch chunks.

@@ -8,11 +8,18 @@
 // the fused pointwise backward for its 64/KS units:
 //   producer warp : waits on the grid barrier for dG_{t+1}, streams it (BT x 64 chunks) via TMA
 //   MMA warp      : tcgen05.mma M=64 (hidden units) x N=BT (batch) x K=16 into TMEM
-//   4 epilogue warps: tcgen05.ld -> partials to the owner CTA's shared memory -> sum -> gate cache
-//                   (128-bit-segment loads), c_t, c_{t-1}, dY_t -> dG_t (16-bit, tile-interleaved),
+//   4 epilogue warps: tcgen05.ld -> partials to the owner CTA's shared memory -> sum -> gate cache,
+//                   c_t, c_{t-1}, dY_t (prefetched before the wait) -> dG_t (16-bit, tile-interleaved),
 //                   dc carry in registers -> publish dG_t (release add on the group's counter)
 // The cell state is READ from the forward's cache; it is never reconstructed from y and o as the
 // reference does (flashlstm_v2/src/lstm_backward.cu:188-197).
+//
+// Every wait is bounded (BwdParams::wait_ns, 2 s by default) and the way out after a timeout is the forward
+// kernel's: the producer and MMA threads break out of their loops and wait (bounded) for the copies / UMMAs
+// they started; the 256 epilogue threads stay together because the named barrier after their waits ORs the
+// failures (barrier.cta.red.or) and no wait lies between it and the release barrier of the step; everybody
+// meets at the final __syncthreads and the cluster barrier (each CTA gets there on its own: its waits for a
+// peer's partial sums are bounded too), then the tensor memory is freed.
 //
 // Replaces, per step, BackwardPointwiseKernel + GemmNN (flashlstm_v2/src/lstm_backward.cu:158-227,
 // 1057-1101) and the whole recompute loop (:991-1054), which the gate cache makes unnecessary.
@@ -114,6 +121,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     tcgen05_fence_after();
     if (KS > 1) cluster_sync_all();  // every CTA's barriers exist before any remote arrive
     const uint32_t tmem_base = *tmem_slot;
+    const unsigned long long wait_ns = p.wait_ns ? p.wait_ns : kWaitLimitNs;
     const int nt_count = p.nt;
     const int c_first = kq * KCper;  // first K chunk (= forward row tile) of this CTA
     const bool tracing = p.trace != nullptr && blockIdx.x == 0;
@@ -133,22 +141,28 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             }
             int stage = 0;
             uint32_t phase = 0;
+            uint32_t ring_issued = 0, ring_parity = 0;  // the last copy started into every ring stage
             // this launch runs reverse iterations [s0, s1); iteration s handles time t = T-1-s and, for
             // s >= 1, first contracts dG_{t+1}, which iteration s-1 produced (in this launch: wait for
-            // the group's counter; in the previous launch: already complete)
+            // the group's counter; in the previous launch: already complete).  p.extra_arrivals is 0 except in
+            // the self-test of the timeout path, where it asks for arrivals that nobody makes.
             for (int s = (p.s0 > 1 ? p.s0 : 1); s < p.s1 && ok; ++s) {
                 const int t_src = p.T - s;  // dG_{t+1} with t = T-1-s
-                if (s > p.s0) ok = wait_counter(counter, (unsigned)(p.jt * KS) * (unsigned)(s - p.s0), p.err, abort_w, 3u);
+                if (s > p.s0)
+                    ok = wait_counter(counter, (unsigned)(p.jt * KS) * (unsigned)(s - p.s0) + p.extra_arrivals, p.err, abort_w,
+                                      3u, wait_ns);
                 if (!ok) break;
                 fence_proxy_async_global();
                 FLSTM_STAMP(s - p.s0, 0);
                 for (int n = 0; n < nt_count && ok; ++n) {
                     const int b0 = (ng * nt_count + n) * BT;
                     for (int ld = 0; ld < NLOAD; ++ld) {
-                        ok = mbar_wait(&empty[stage], phase ^ 1, abort_w);
+                        ok = mbar_wait(&empty[stage], phase ^ 1, abort_w, wait_ns);
                         if (!ok) break;
                         uint8_t *sd = s_ring + stage * L.ring_stage_bytes;
                         mbar_expect_tx(&full[stage], (uint32_t)L.ring_stage_bytes);
+                        ring_issued |= 1u << stage;
+                        ring_parity = (ring_parity & ~(1u << stage)) | (phase << stage);
                         // CH chunks of the dG tile with one copy: (x, row, chunk, step)
                         tma_load_4d(sd, &tm_dg, 0, b0, c_first + ld * CH, t_src, &full[stage]);
                         if (!W_RESIDENT)
@@ -160,24 +174,29 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 }
                 FLSTM_STAMP(s - p.s0, 1);
             }
+            // way out (normal or aborted): every copy this thread started must have landed before the CTA exits
+            if (W_RESIDENT) mbar_drain(wbar, 0, wait_ns);
+            for (int i = 0; i < L.stages; ++i)
+                if (ring_issued >> i & 1u) mbar_drain(&full[i], ring_parity >> i & 1u, wait_ns);
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------ MMA issuer
         if (elect_one()) {
             bool ok = true;
-            if (W_RESIDENT) ok = mbar_wait(wbar, 0, abort_w);
+            if (W_RESIDENT) ok = mbar_wait(wbar, 0, abort_w, wait_ns);
             int stage = 0;
             uint32_t phase = 0;
             const uint32_t s_w_u32 = smem_u32(s_w), idesc = p.idesc;
             const uint32_t items = (uint32_t)(p.s1 - (p.s0 > 1 ? p.s0 : 1)) * nt_count;
+            int last_commit = -1;
             for (uint32_t wi = 0; wi < items && ok; ++wi) {
                 const int buf = wi & 1;
-                ok = mbar_wait(&tempty[buf], ((wi >> 1) & 1) ^ 1, abort_w);
+                ok = mbar_wait(&tempty[buf], ((wi >> 1) & 1) ^ 1, abort_w, wait_ns);
                 if (!ok) break;
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BT;
                 for (int ld = 0; ld < NLOAD; ++ld) {
-                    ok = mbar_wait(&full[stage], phase, abort_w);
+                    ok = mbar_wait(&full[stage], phase, abort_w, wait_ns);
                     if (!ok) break;
                     if (ld == 0) FLSTM_STAMP((int)(wi / nt_count) + 1 - (p.s0 > 0 ? 1 : 0), 2);
                     if (ld == NLOAD - 1) FLSTM_STAMP((int)(wi / nt_count) + 1 - (p.s0 > 0 ? 1 : 0), 3);
@@ -201,8 +220,11 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 }
                 if (!ok) break;
                 umma_commit(&tfull[buf]);
+                last_commit = (int)wi;
                 FLSTM_STAMP((int)(wi / nt_count) + 1 - (p.s0 > 0 ? 1 : 0), 4);
             }
+            // the tensor memory is freed at the end of the kernel: the last committed batch of UMMAs must be done
+            if (last_commit >= 0) mbar_drain(&tfull[last_commit & 1], (uint32_t)(last_commit >> 1) & 1u, wait_ns);
         }
     } else {
         // ------------------------------------------------------------ epilogue (256 threads)
@@ -271,11 +293,13 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         }
                 } else {
                     const int buf = wi & 1, rb = wi & 1;
-                    ok = mbar_wait(&tfull[buf], (wi >> 1) & 1, abort_w);
-                    if (!ok) break;
+                    // No thread leaves between here and the named barrier below, whatever its waits return: the
+                    // barrier ORs the failures, so that all 256 threads go on or give up together.  A warp sends
+                    // its partial sums only if all of its lanes saw the accumulator complete.
+                    bool good = __all_sync(0xffffffffu, mbar_wait(&tfull[buf], (wi >> 1) & 1, abort_w, wait_ns));
                     if (tid == 0) FLSTM_STAMP(s - p.s0, 5);
                     tcgen05_fence_after();
-                    if (warp < 4) {
+                    if (warp < 4 && good) {
                         // phase A (warps 0-3): lanes 0..15 of warp w hold units 16w+lane of the tile, all BT sequences
 #pragma unroll
                         for (int c0 = 0; c0 < BT; c0 += 32) {
@@ -314,8 +338,7 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         }
                     }
                     if (tid == 0) FLSTM_STAMP(s - p.s0, 9);
-                    ok = mbar_wait_cluster(&rbar[rb], (wi >> 1) & 1, abort_w);
-                    if (!ok) break;
+                    if (good) good = mbar_wait_cluster(&rbar[rb], (wi >> 1) & 1, abort_w, wait_ns);
                     if (tid == 0) FLSTM_STAMP(s - p.s0, 10);
                     const float *red = s_red + (size_t)rb * KS * UPO * RS;
 #pragma unroll
@@ -329,7 +352,10 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                             dh_in[q * (BT / 16) + i] = acc;
                         }
                     // every warp has read this item's partials before any warp sends the next item's
-                    named_barrier_sync(1, kBwdEpilogueThreads);
+                    if (named_barrier_or(1, kBwdEpilogueThreads, !good)) {
+                        ok = false;
+                        break;
+                    }
                     if (tid == 0) FLSTM_STAMP(s - p.s0, 6);
                     ++wi;
                 }
@@ -394,7 +420,15 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     }
     tcgen05_fence_before();
     __syncthreads();
-    if (KS > 1) cluster_sync_all();  // nobody leaves while a peer may still write into its shared memory
+    if (KS > 1) {
+        cluster_sync_all();  // nobody leaves while a peer may still send into its shared memory
+        if (*abort_w) {
+            // after an abort this CTA may not have waited for partial sums that a peer sent before it reached the
+            // barrier above: give those asynchronous stores time to land before the shared memory is released
+            const unsigned long long t0 = global_timer_ns();
+            while (global_timer_ns() - t0 < 20000ull) {}
+        }
+    }
     if (warp == 5) tmem_dealloc(tmem_base, kTmemCols);
     if (threadIdx.x == 0 && *abort_w) atomicCAS(p.err, 0u, 1u);
 }
@@ -404,11 +438,7 @@ template <int BT, int KS, bool RES, bool BF16>
 static int launch_bwd(const CUtensorMap &tw, const CUtensorMap &tdg, const BwdParams &p, int grid, int smem_bytes,
                       cudaStream_t s) {
     auto kern = lstm_bwd_kernel<BT, KS, RES, BF16>;
-    static int configured = 0;
-    if (configured < smem_bytes) {
-        FLSTM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-        configured = smem_bytes;
-    }
+    FLSTM_CUDA_TRY(ensure_smem_limit(kern, (size_t)smem_bytes));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kBwdThreads);
@@ -429,9 +459,10 @@ static int launch_bwd(const CUtensorMap &tw, const CUtensorMap &tdg, const BwdPa
     cfg.attrs = attr;
     cfg.numAttrs = na;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tdg, p);
-    if (e != cudaSuccess && KS > 1) {
-        // some drivers reject cooperative + cluster: co-residency was checked with
-        // cudaOccupancyMaxActiveClusters at planning time, so launch with the cluster attribute only
+    if (KS > 1 && (e == cudaErrorNotSupported || e == cudaErrorInvalidValue)) {
+        // a driver that refuses the cooperative and cluster attributes TOGETHER: the planner has already proved
+        // with cudaOccupancyMaxActiveClusters that every cluster of this grid is resident at once (plan_bwd fails
+        // otherwise), so the cluster attribute alone gives the same guarantee.  Any other error is reported.
         cudaGetLastError();
         cfg.attrs = attr + 1;
         cfg.numAttrs = 1;
@@ -444,7 +475,10 @@ static int launch_bwd(const CUtensorMap &tw, const CUtensorMap &tdg, const BwdPa
 template <int BT, int KS, bool RES>
 static int max_clusters(int smem_bytes, int grid) {
     auto kern = lstm_bwd_kernel<BT, KS, RES, false>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -1;
+    if (ensure_smem_limit(kern, (size_t)smem_bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kBwdThreads);
@@ -473,7 +507,7 @@ static int query_clusters(const BwdPlan &pl) {
     return -1;
 }
 
-int plan_bwd(int B, int H, int sms, size_t smem_limit, BwdPlan *plan) {
+int plan_bwd(int B, int H, int sms, size_t smem_limit, BwdPlan *plan, bool check_device) {
     if (H % 64 != 0 || H < 64) return set_error(FLSTM_ERR_UNSUPPORTED, "hidden size must be a multiple of 64");
     const int jt = H / 64, kc_total = H / 16;
     // split K = 4H so that a CTA's slice of W_hh (kc_total/KS chunks of 8 KB) can stay resident
@@ -525,11 +559,17 @@ int plan_bwd(int B, int H, int sms, size_t smem_limit, BwdPlan *plan) {
     plan->resident = resident;
     plan->smem_bytes = l.total;
     plan->grid = jt * KS * ngroups;
-    if (KS > 1) {
-        // clusters must all be co-resident: shrink the number of batch groups until they are
+    if (KS > 1 && check_device) {
+        // The CTAs wait on one another, so every cluster must be resident at once: shrink the number of batch
+        // groups until the occupancy query says so.  A failed query or a grid that still does not fit is a
+        // planning error (the caller falls back to another path); it is never left to the bounded waits.
         for (;;) {
             const int fit = query_clusters(*plan);
-            if (fit < 0 || fit * KS >= plan->grid || plan->ngroups == 1) break;
+            if (fit < 0)
+                return set_error(FLSTM_ERR_UNSUPPORTED, "BPTT planning: the cluster occupancy query failed (clusters of %d CTAs, %d bytes of shared memory)", KS, plan->smem_bytes);
+            if (fit * KS >= plan->grid) break;
+            if (plan->ngroups == 1)
+                return set_error(FLSTM_ERR_UNSUPPORTED, "BPTT planning: %d clusters of %d CTAs are needed at once, the device holds %d", plan->grid / KS, KS, fit);
             plan->ngroups -= 1;
             plan->nt = (tiles + plan->ngroups - 1) / plan->ngroups;
             plan->ngroups = (tiles + plan->nt - 1) / plan->nt;

@@ -14,7 +14,15 @@
 //                   h_t (16-bit).  h_t is stored and published first; the cell state and the activated
 //                   gates (the FP16/BF16 gate cache, written over P_t in global memory) follow
 // Steps are separated by a per-batch-group barrier in global memory (release add / acquire poll).
-// Every wait is bounded; a timeout raises the error word and every CTA drains and returns.
+// Every wait is bounded (FwdParams::wait_ns, 2 s by default); a timeout raises the CTA's abort word and the
+// global error word, and every role leaves:
+//   * the producer and MMA threads run their loops alone and simply break; on the way out the producer waits
+//     (bounded) for every TMA copy it started and the MMA thread for its last committed UMMAs;
+//   * the 256 epilogue threads never leave between their waits and the named barrier that follows: the barrier
+//     ORs "my wait failed" over all of them (barrier.cta.red.or), so they continue or break TOGETHER and nobody is
+//     left at a bar.sync; no wait lies between that barrier and the release barrier of the same step;
+//   * all 320 threads meet at the final __syncthreads, after which the tensor memory is freed.
+// Other CTAs learn of an abort through the global error word, which their counter polls read.
 //
 // Replaces, per step, the reference's ScaleAndPackColumnsKernel + GemmTN + ForwardPointwiseKernel
 // launches (flashlstm_v2/src/lstm_forward.cu:744-830) and v1's GEMM + lstm_pointwise_kernel pair
@@ -111,6 +119,7 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    const unsigned long long wait_ns = p.wait_ns ? p.wait_ns : kWaitLimitNs;
     const int nt_count = p.nt;  // batch tiles per group
     const int items_per_step = p.rt * nt_count;
     const bool tracing = p.trace != nullptr && blockIdx.x == 0;
@@ -131,6 +140,8 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             }
             int stage = 0;
             uint32_t phase = 0, wi = 0;
+            // what was issued last into every ring stage / P buffer, so that nothing is left in flight at exit
+            uint32_t ring_issued = 0, ring_parity = 0, p_issued = 0, p_parity = 0;
             for (int tt = 0; tt < p.T && ok; ++tt) {
                 const int t = p.t0 + tt;  // absolute time step; this launch runs steps [t0, t0 + T)
                 bool first = true;
@@ -139,25 +150,31 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     for (int n = 0; n < nt_count && ok; ++n, ++wi) {
                         const int b0 = (ng * nt_count + n) * BT;
                         const int pb = wi & 1;
-                        ok = mbar_wait(&pempty[pb], ((wi >> 1) & 1) ^ 1, abort_w);
+                        ok = mbar_wait(&pempty[pb], ((wi >> 1) & 1) ^ 1, abort_w, wait_ns);
                         if (!ok) break;
                         mbar_expect_tx(&pfull[pb], BT * 128);
                         tma_load_3d(s_p + pb * BT * 128, &tm_g, j * 64, b0, t, &pfull[pb]);
+                        p_issued |= 1u << pb;
+                        p_parity = (p_parity & ~(1u << pb)) | (((wi >> 1) & 1u) << pb);
                         if (first && tt > 0) {
                             // h_{t-1} of this batch group is complete when every CTA of the group has
                             // arrived tt times in this launch (once per step each); the state a launch
-                            // starts from was completed by the previous launch
-                            ok = wait_counter(counter, (unsigned)(p.cta_rows) * (unsigned)tt, p.err, abort_w, 2u);
+                            // starts from was completed by the previous launch.  p.extra_arrivals is 0 except in
+                            // the self-test of the timeout path, where it asks for arrivals that nobody makes.
+                            ok = wait_counter(counter, (unsigned)(p.cta_rows) * (unsigned)tt + p.extra_arrivals, p.err,
+                                              abort_w, 2u, wait_ns);
                             if (!ok) break;
                             fence_proxy_async_global();
                         }
                         if (first) FLSTM_STAMP(tt, 0);
                         first = false;
                         for (int ld = 0; ld < NLOAD; ++ld) {
-                            ok = mbar_wait(&empty[stage], phase ^ 1, abort_w);
+                            ok = mbar_wait(&empty[stage], phase ^ 1, abort_w, wait_ns);
                             if (!ok) break;
                             uint8_t *sh = s_ring + stage * L.ring_stage_bytes;
                             mbar_expect_tx(&full[stage], (uint32_t)L.ring_stage_bytes);
+                            ring_issued |= 1u << stage;
+                            ring_parity = (ring_parity & ~(1u << stage)) | (phase << stage);
                             // CH chunks of the h tile with one copy: (x, row, chunk, step)
                             tma_load_4d(sh, &tm_h, 0, b0, ld * CH, t, &full[stage]);
                             if (!W_RESIDENT)
@@ -170,25 +187,33 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     }
                 }
             }
+            // Way out (normal or aborted): every copy this thread started must have landed before the CTA
+            // exits.  After a normal run the consumers have already waited for all of them, so this costs nothing.
+            if (W_RESIDENT) mbar_drain(wbar, 0, wait_ns);
+            for (int i = 0; i < L.stages; ++i)
+                if (ring_issued >> i & 1u) mbar_drain(&full[i], ring_parity >> i & 1u, wait_ns);
+            for (int i = 0; i < 2; ++i)
+                if (p_issued >> i & 1u) mbar_drain(&pfull[i], p_parity >> i & 1u, wait_ns);
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------ MMA issuer
         if (elect_one()) {
             bool ok = true;
-            if (W_RESIDENT) ok = mbar_wait(wbar, 0, abort_w);
+            if (W_RESIDENT) ok = mbar_wait(wbar, 0, abort_w, wait_ns);
             int stage = 0;
             uint32_t phase = 0, wi = 0;
             const uint32_t s_w_u32 = smem_u32(s_w), idesc = p.idesc;
             const uint32_t total_items = (uint32_t)p.T * items_per_step;
+            int last_commit = -1;
             for (uint32_t it = 0; it < total_items && ok; ++it, ++wi) {
                 const int r = (it % items_per_step) / nt_count;
                 const int buf = wi & 1;
-                ok = mbar_wait(&tempty[buf], ((wi >> 1) & 1) ^ 1, abort_w);
+                ok = mbar_wait(&tempty[buf], ((wi >> 1) & 1) ^ 1, abort_w, wait_ns);
                 if (!ok) break;
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BT;
                 for (int ld = 0; ld < NLOAD; ++ld) {
-                    ok = mbar_wait(&full[stage], phase, abort_w);
+                    ok = mbar_wait(&full[stage], phase, abort_w, wait_ns);
                     if (!ok) break;
                     if (ld == 0) FLSTM_STAMP((int)(it / items_per_step), 2);
                     if (ld == NLOAD - 1) FLSTM_STAMP((int)(it / items_per_step), 3);
@@ -213,8 +238,11 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 }
                 if (!ok) break;
                 umma_commit(&tfull[buf]);
+                last_commit = (int)wi;
                 FLSTM_STAMP((int)(it / items_per_step), 4);
             }
+            // the tensor memory is freed at the end of the kernel: the last committed batch of UMMAs must be done
+            if (last_commit >= 0) mbar_drain(&tfull[last_commit & 1], (uint32_t)(last_commit >> 1) & 1u, wait_ns);
         }
     } else {
         // ------------------------------------------------------------ epilogue (256 threads)
@@ -248,8 +276,9 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         if (keep_c && tt > 0) c_prev[i] = c_keep[i];
                         else c_prev[i] = (b < p.B) ? p.cs[(size_t)t * slab + (size_t)b * p.H + j * 16 + u] : 0.f;
                     }
-                    ok = mbar_wait(&tfull[buf], (wi >> 1) & 1, abort_w);
-                    if (!ok) break;
+                    // No thread leaves between here and the named barrier below, whatever its waits return: the
+                    // barrier ORs the failures, so that all 256 threads go on or give up together.
+                    bool good = mbar_wait(&tfull[buf], (wi >> 1) & 1, abort_w, wait_ns);
                     if (tid == 0) FLSTM_STAMP(tt, 5);
                     tcgen05_fence_after();
                     float *ex = s_ex + (wi & 1) * 64 * EXS;
@@ -273,9 +302,11 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&tempty[buf]);
                     }
-                    ok = mbar_wait(&pfull[pb], (wi >> 1) & 1, abort_w);
-                    if (!ok) break;
-                    named_barrier_sync(1, kFwdEpilogueThreads);
+                    if (good) good = mbar_wait(&pfull[pb], (wi >> 1) & 1, abort_w, wait_ns);
+                    if (named_barrier_or(1, kFwdEpilogueThreads, !good)) {
+                        ok = false;
+                        break;
+                    }
                     if (tid == 0) FLSTM_STAMP(tt, 6);
                     // phase B: one thread per (unit, sequence) pair does the whole pointwise update
                     const uint16_t *ptile = reinterpret_cast<const uint16_t *>(s_p + pb * BT * 128);
@@ -341,11 +372,7 @@ template <int BT, bool RES, bool BF16>
 static int launch_fwd(const CUtensorMap &tw, const CUtensorMap &th, const CUtensorMap &tg, const FwdParams &p, int grid,
                       int smem_bytes, cudaStream_t s) {
     auto kern = lstm_fwd_kernel<BT, RES, BF16>;
-    static int configured = 0;
-    if (configured < smem_bytes) {
-        FLSTM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-        configured = smem_bytes;
-    }
+    FLSTM_CUDA_TRY(ensure_smem_limit(kern, (size_t)smem_bytes));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kFwdThreads);

@@ -464,11 +464,7 @@ int launch_step(const CUtensorMap &ta, const CUtensorMap &tb, const EpilogueMaps
                 cudaStream_t s) {
     using S = StepShape<BN, EPI>;
     auto kern = step_kernel<BN, EPI, B_MN, BF16>;
-    static bool configured = false;  // per instantiation
-    if (!configured) {
-        FLSTM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes));
-        configured = true;
-    }
+    FLSTM_CUDA_TRY(ensure_smem_limit(kern, (size_t)S::kSmemBytes));
     const int tiles = ((a.M + BM - 1) / BM) * (a.N / BN) * a.splits;
     const int grid = tiles < sms ? tiles : sms;
     cudaError_t e = launch_chained(kern, grid, kStepThreads, S::kSmemBytes, s, ta, tb, *em.g, *em.c, *em.h, *em.y, a);

@@ -23,6 +23,23 @@ __device__ __forceinline__ void red_release_gpu_add(unsigned int *p, unsigned in
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+// Named barrier that also ORs a predicate over its `threads` participants: every participant arrives whatever
+// its own bounded waits returned, and all of them leave with the same verdict, so nobody is left at the barrier
+// by threads that gave up earlier.
+__device__ __forceinline__ bool named_barrier_or(int id, int threads, bool pred) {
+    uint32_t out;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.u32 p, %3, 0;\n"
+        "barrier.cta.red.or.pred q, %1, %2, p;\n"
+        "selp.u32 %0, 1, 0, q;\n"
+        "}\n"
+        : "=r"(out)
+        : "r"(id), "r"(threads), "r"((uint32_t)pred)
+        : "memory");
+    return out != 0;
+}
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -57,14 +74,15 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t pa
         : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_w) {
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_w,
+                                                  unsigned long long limit_ns = kWaitLimitNs) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
     const unsigned long long t0 = global_timer_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait_cluster(bar, parity)) {
         if ((++spins & 255u) == 0) {
             if (*abort_w) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
+            if (global_timer_ns() - t0 > limit_ns) {
                 *abort_w = 1;
                 return false;
             }
@@ -75,7 +93,8 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity
 
 // Bounded poll of a monotonic counter written by other CTAs; `code` goes to the error word on expiry.
 __device__ __forceinline__ bool wait_counter(const unsigned int *ctr, unsigned int target, unsigned int *err_word,
-                                             volatile uint32_t *abort_w, unsigned int code) {
+                                             volatile uint32_t *abort_w, unsigned int code,
+                                             unsigned long long limit_ns = kWaitLimitNs) {
     if (ld_acquire_gpu(ctr) >= target) return true;
     const unsigned long long t0 = global_timer_ns();
     uint32_t spins = 0;
@@ -86,7 +105,7 @@ __device__ __forceinline__ bool wait_counter(const unsigned int *ctr, unsigned i
                 *abort_w = 1;
                 return false;
             }
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
+            if (global_timer_ns() - t0 > limit_ns) {
                 *abort_w = 1;
                 atomicExch(err_word, code);
                 return false;

@@ -224,6 +224,16 @@ class Engine:
             s = stream if stream is not None else torch.cuda.current_stream()
             check(self.lib.flstm_engine_wait(self._h, s.cuda_stream, max(0, int(timeout_s * 1000))))
 
+    def set_wait_limit(self, microseconds: int) -> None:
+        """Limit of every device-side wait of the persistent kernels (0 = the 2 s default)."""
+        check(self.lib.flstm_engine_set_wait_limit(self._h, int(microseconds)))
+
+    def selftest_missing_arrivals(self, arrivals: int) -> None:
+        """Timeout self-test: every step barrier of the following launches waits for `arrivals` arrivals that no
+        CTA makes, so the second time step's wait runs out after the limit and the launch returns with the
+        error word set (the next call raises TIMEOUT).  0 switches it off."""
+        check(self.lib.flstm_engine_selftest_missing_arrivals(self._h, int(arrivals)))
+
     def abort_comm(self) -> None:
         check(self.lib.flstm_engine_abort_comm(self._h))
 

@@ -86,7 +86,9 @@ def _round_to(t: torch.Tensor, dtype: str) -> torch.Tensor:
     return t.to(TORCH_DTYPE[dtype]).to(torch.float32)
 
 
-def make_inputs(w: Workload) -> Inputs:
+def make_inputs(w: Workload, rows: Optional[slice] = None) -> Inputs:
+    """`rows` keeps only that slice of the batch (the draw itself is always the full batch, so every rank of a
+    batch-sharded run sees the values a single-GPU run sees for the same sequences)."""
     torch.manual_seed(w.seed)
     proto = torch.nn.LSTM(w.input_size, w.hidden_size, num_layers=w.layers)
     w_ih, w_hh, b_ih, b_hh = [], [], [], []
@@ -95,13 +97,16 @@ def make_inputs(w: Workload) -> Inputs:
         w_hh.append(_round_to(getattr(proto, f"weight_hh_l{l}").detach().clone(), w.dtype))
         b_ih.append(getattr(proto, f"bias_ih_l{l}").detach().clone())
         b_hh.append(getattr(proto, f"bias_hh_l{l}").detach().clone())
-    x = _round_to(torch.randn(w.seq_len, w.batch, w.input_size), w.dtype)
+    def keep(t: torch.Tensor) -> torch.Tensor:
+        return t if rows is None else t[:, rows].contiguous()
+
+    x = keep(_round_to(torch.randn(w.seq_len, w.batch, w.input_size), w.dtype))
     if w.state_std > 0:
-        h0 = _round_to(torch.randn(w.layers, w.batch, w.hidden_size) * w.state_std, w.dtype)
-        c0 = _round_to(torch.randn(w.layers, w.batch, w.hidden_size) * w.state_std, w.dtype)
+        h0 = keep(_round_to(torch.randn(w.layers, w.batch, w.hidden_size) * w.state_std, w.dtype))
+        c0 = keep(_round_to(torch.randn(w.layers, w.batch, w.hidden_size) * w.state_std, w.dtype))
     else:
         h0 = c0 = None
-    dy = _round_to(torch.randn(w.seq_len, w.batch, w.hidden_size), w.dtype) if w.training else None
+    dy = keep(_round_to(torch.randn(w.seq_len, w.batch, w.hidden_size), w.dtype)) if w.training else None
     return Inputs(w_ih, w_hh, b_ih, b_hh, x, h0, c0, dy)
 
 

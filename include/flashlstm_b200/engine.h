@@ -148,6 +148,17 @@ int flstm_engine_attach_comm(flstm_engine *engine, const void *id128, int rank, 
 int flstm_engine_wait(flstm_engine *engine, cudaStream_t stream, unsigned int timeout_ms);
 int flstm_engine_abort_comm(flstm_engine *engine);
 
+/* Every device-side wait of the persistent recurrent kernels (step barrier, mbarrier waits, cluster exchange)
+ * gives up after a limit, 2 s unless set here (limit_us = 0 restores the default): the kernel raises an error
+ * word, every role drains and the launch returns; the next call on the engine (or flstm_engine_wait) then
+ * reports FLSTM_ERR_TIMEOUT and the engine stays usable.  The reference has no counterpart: its kernels never
+ * wait on one another (flashlstm_v2/src/lstm_forward.cu:744-830 launches per step).
+ * flstm_engine_selftest_missing_arrivals exercises that path without any fault: with arrivals = n > 0 every
+ * step barrier of the following launches waits for n arrivals that no CTA makes, so the wait of the second
+ * time step runs out after the limit.  Set a limit of a few milliseconds first; arrivals = 0 switches it off. */
+int flstm_engine_set_wait_limit(flstm_engine *engine, unsigned long long limit_us);
+int flstm_engine_selftest_missing_arrivals(flstm_engine *engine, unsigned int arrivals);
+
 /* Per-phase device time of the last forward/backward pair in milliseconds (needs
  * flstm_engine_enable_timing(engine, 1); adds event records, no synchronisation).
  * out[0..5] = projection, recurrent forward, BPTT, weight-grad, input-grad, allreduce. */

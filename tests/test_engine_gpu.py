@@ -317,3 +317,30 @@ def test_step_ranges_must_be_in_order():
     with pytest.raises(FlashLstmError, match="descending"):
         eng.backward_range_into(8, 0, 4, y, None, None, None, None, None)
     eng.close()
+
+
+def test_step_trace_of_the_persistent_kernels_is_ordered():
+    """The in-kernel step trace (flstm_engine_enable_trace): every step's stamps ascend from the barrier to the
+    release, in the forward and in the BPTT kernel."""
+    from flashlstm_poc_b200 import step_trace
+    from flashlstm_poc_b200.engine import Engine
+
+    w = Workload("trace", "f16", 1, 256, 256, 32, 24, seed=2)
+    inp = make_inputs(w)
+    dev = torch.device("cuda", 0)
+    eng = Engine(w.dtype, 1, w.batch, w.input_size, w.hidden_size, w.seq_len, device=dev)
+    eng.set_weights(0, inp.w_ih[0].to(dev), inp.w_hh[0].to(dev), inp.b_ih[0].to(dev), inp.b_hh[0].to(dev))
+    x, dy = inp.x.to(dev, torch.float16), inp.dy.to(dev, torch.float16)
+
+    def run_step():
+        eng.forward(x)
+        eng.backward(dy)
+
+    run_step()
+    stamps = step_trace.collect(eng, run_step, steps=16)
+    summary = step_trace.summarize(stamps, skip=2)
+    eng.close()
+    for kernel in ("forward", "bptt"):
+        rows = summary[kernel]
+        assert rows["period"] > 0
+        assert 0 < rows["step barrier satisfied"] < rows["last UMMA committed"] < rows["released"] <= rows["period"] * 1.5

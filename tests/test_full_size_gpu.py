@@ -1,9 +1,11 @@
-"""The two large BF16 benchmark configurations at FULL size on the GPU, checked on a batch slice.
+"""The benchmark configurations at FULL size on the GPU.
 
-Sequences are independent across the batch in the forward pass and in dx / dh0 / dc0, so the CPU oracle is
-run on a few rows of the batch only (seconds instead of minutes) and compared with the same rows of the
-engine's full-size run.  Weight gradients sum over the batch; they are covered at reduced batch by the other
-parity tests."""
+Sequences are independent across the batch in the forward pass and in dx / dh0 / dc0, so for the two large
+BF16 configurations the CPU oracle is run on a few rows of the batch only (seconds instead of minutes) and
+compared with the same rows of the engine's full-size run.  Weight and bias gradients sum over time and batch:
+they are checked at full sequence length, width and depth on a reduced batch (16 sequences through the
+persistent kernels, 64 / 128 through the per-step path), which is where 16-bit dG summed over a thousand
+time steps could drift."""
 import numpy as np
 import pytest
 import torch
@@ -71,6 +73,47 @@ def test_config4_full_size_inference_slice():
     got = {"y": y[:, rows].float().cpu().numpy(), "hn": hn[:, rows].float().cpu().numpy(), "cn": cn[:, rows].float().cpu().numpy()}
     eng.close()
     ref = run_oracle(Inputs(inp.w_ih, inp.w_hh, inp.b_ih, inp.b_hh, inp.x[:, rows].contiguous(), None, None, None))
+    for k, v in got.items():
+        err = orc.rel_l2_err(v, ref[k])
+        assert err < 1e-2, (k, err)
+
+
+@pytest.mark.parametrize("name,batch,path", [
+    ("c3_bf16_l2_h2048", 16, "persistent"), ("c5_bf16_l4_h1024", 16, "persistent"),
+    ("c3_bf16_l2_h2048", 64, "step"), ("c5_bf16_l4_h1024", 128, "step"),
+])
+def test_bf16_configs_full_length_reduced_batch_all_outputs(name, batch, path):
+    """Configurations 3 and 5 at their own T, I, H and L with a reduced batch: EVERY output, including dW_ih,
+    dW_hh and db of every layer, against the oracle; relative L2 <= 1e-2 (the stated bar for 16-bit runs)."""
+    from flashlstm_poc_b200 import _lib
+    from tests.gpu_helpers import assert_parity, run_engine
+
+    w = WORKLOADS[name].scaled(batch=batch)
+    info = _lib.TcPlanInfo()
+    _lib.check(_lib.load().flstm_tc_plan(w.batch, w.hidden_size, 1, 148, 232448, info))
+    assert bool(info.step_path) == (path == "step")
+    inp = make_inputs(w)
+    got, eng = run_engine(w, inp)
+    assert eng.backend == "tc"
+    eng.close()
+    torch.cuda.empty_cache()
+    report = assert_parity(got, run_oracle(inp), w.dtype)
+    assert set(k.split("[")[0] for k in report) >= {"y", "hn", "cn", "dx", "dh0", "dc0", "dw_ih", "dw_hh", "db"}
+
+
+def test_config4_full_size_single_sequence():
+    """Configuration 4 with B = 1 (the latency case: one sequence, W_hh streamed every step) at full T and H."""
+    w = WORKLOADS["c4_fp16_h4096_b1"]
+    inp = make_inputs(w)
+    dev = torch.device("cuda", 0)
+    eng = Engine(w.dtype, 1, w.batch, w.input_size, w.hidden_size, w.seq_len, training=False, device=dev)
+    assert eng.backend == "tc"
+    eng.set_weights(0, inp.w_ih[0].to(dev), inp.w_hh[0].to(dev), inp.b_ih[0].to(dev), inp.b_hh[0].to(dev))
+    y, hn, cn = eng.forward(inp.x.to(dev, torch.float16))
+    torch.cuda.synchronize()
+    got = {"y": y.float().cpu().numpy(), "hn": hn.float().cpu().numpy(), "cn": cn.float().cpu().numpy()}
+    eng.close()
+    ref = run_oracle(inp)
     for k, v in got.items():
         err = orc.rel_l2_err(v, ref[k])
         assert err < 1e-2, (k, err)
