@@ -19,12 +19,14 @@ ENGINE_SYMBOLS = [
     "flstm_engine_enable_trace", "flstm_engine_read_trace", "flstm_bias_grad", "flstm_tc_plan", "flstm_engine_wait", "flstm_engine_abort_comm",
                   "flstm_engine_set_recompute_interval", "flstm_engine_workspace_bytes",
     "flstm_bias_grad_static", "flstm_engine_set_wait_limit", "flstm_engine_selftest_missing_arrivals",
+    "flstm_engine_backward_segment",
     "flstm_last_error",
     "flstm_version",
 ]
 V1_SYMBOLS = ["lstm_create_buffers", "lstm_destroy_buffers", "lstm_set_execution_mode", "lstm_pack_weights",
               "lstm_forward"]
-V2_SYMBOLS = ["flstm_StreamingLstmForward", "flstm_StreamingLstmBackward", "flstm_last_status"]
+V2_SYMBOLS = ["flstm_StreamingLstmForward", "flstm_StreamingLstmBackward", "flstm_last_status",
+              "flstm_v2_set_weight_version", "flstm_v2_last_call_info"]
 
 STATUS_NAMES = {0: "OK", 1: "INVALID", 2: "CUDA", 3: "TIMEOUT", 4: "UNSUPPORTED", 5: "COMM"}
 DTYPE_CODES = {"f32": 0, "f16": 1, "bf16": 2}
@@ -105,6 +107,7 @@ def load() -> ctypes.CDLL:
     lib.flstm_tc_plan.argtypes = [sz, sz, ci, ci, sz, ctypes.POINTER(TcPlanInfo)]
     lib.flstm_engine_wait.argtypes = [vp, vp, ctypes.c_uint]
     lib.flstm_engine_abort_comm.argtypes = [vp]
+    lib.flstm_engine_backward_segment.argtypes = [vp, sz, ci, ci] + [vp] * 10
     lib.flstm_engine_set_wait_limit.argtypes = [vp, ctypes.c_ulonglong]
     lib.flstm_engine_selftest_missing_arrivals.argtypes = [vp, ctypes.c_uint]
     lib.flstm_engine_set_recompute_interval.argtypes = [vp, sz]
@@ -127,6 +130,10 @@ def load() -> ctypes.CDLL:
     lib.flstm_StreamingLstmBackward.argtypes = [sz] * 5 + [vp, vp, GateCacheHost] + [vp] * 19 + [ctypes.POINTER(StreamingLstmOptions)]
     lib.flstm_StreamingLstmBackward.restype = None
     lib.flstm_last_status.restype = ci
+    lib.flstm_v2_set_weight_version.argtypes = [ctypes.c_ulonglong]
+    lib.flstm_v2_set_weight_version.restype = None
+    lib.flstm_v2_last_call_info.argtypes = [ctypes.POINTER(sz), ctypes.POINTER(ci)]
+    lib.flstm_v2_last_call_info.restype = None
     _lib = lib
     return lib
 

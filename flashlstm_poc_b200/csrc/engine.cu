@@ -460,6 +460,63 @@ int Engine::backward(size_t T, const void *dy, const void *dhn, const void *dcn,
     return backward_range(T, 0, T, dy, dhn, dcn, dx, dh0, dc0, s);
 }
 
+// One segment of a sequence that is streamed through the engine from outside (host streaming): the caller owns
+// x, dY, dX and the h/c checkpoints, the engine holds one segment of gates / states / dG at a time.  Segments are
+// passed from the LAST one to the FIRST.  Per layer the forward of the segment is re-run from the state that
+// entered it (h_in 16-bit, c_in fp32, both (L,B,H)), then the BPTT runs over it with the gradient carries kept
+// inside the engine between calls (dc in dc_layers, dh as dG of the following step in the extra dG slot / the
+// partial sums of the wide-batch path); weight and bias gradients accumulate from call to call and are complete
+// (and reduced over the ranks) after the call with `first_in_time`.
+int Engine::backward_segment(size_t n, bool last_in_time, bool first_in_time, const void *x_seg, const void *h_in,
+                             const float *c_in, const void *dy_seg, const void *dhn, const void *dcn, void *dx_seg,
+                             float *dh0, float *dc0, cudaStream_t s) {
+    const size_t B = cfg.batch, H = cfg.hidden_size, es = dtype_size(cfg.dtype), slab = B * H;
+    const int L = (int)layers.size();
+    if (!cfg.training) return set_error(FLSTM_ERR_INVALID, "engine was created with training = 0");
+    if (backend != FLSTM_BACKEND_TC || !recompute)
+        return set_error(FLSTM_ERR_UNSUPPORTED, "segment backward needs the tensor-core backend with a recompute interval set");
+    if (n == 0 || n > buf_steps) return set_error(FLSTM_ERR_INVALID, "segment of %zu steps does not fit the %zu-step buffers", n, buf_steps);
+    if (!x_seg || !dy_seg) return set_error(FLSTM_ERR_INVALID, "null pointer argument");
+    if (comm_aborted) return set_error(FLSTM_ERR_COMM, "the communicator was aborted after a step missed its deadline; attach a new one");
+    for (auto &l : layers)
+        if (!l.weights_set) return set_error(FLSTM_ERR_INVALID, "weights have not been set for every layer");
+    if (last_in_time) timer.reset();
+    struct Restore { Engine &e; ~Restore() { e.seg = SegmentMode{}; } } restore{*this};
+    seg.active = true;
+    seg.first_segment = last_in_time;   // the first one processed: weight gradients start from zero
+    seg.final_segment = first_in_time;  // the one that starts the sequence: dh0 / dc0 and the allreduce follow it
+    seg.keep_gates = true;
+    // recompute: rebuild gates, h and c of the segment, layer by layer, in the segment buffers
+    for (int li = 0; li < L; ++li) {
+        auto &l = layers[li];
+        if (h_in) FLSTM_CUDA_TRY(cudaMemcpyAsync(l.hs, byte_ptr(h_in) + li * slab * es, slab * es, cudaMemcpyDeviceToDevice, s));
+        else FLSTM_CUDA_TRY(cudaMemsetAsync(l.hs, 0, slab * es, s));
+        if (c_in) FLSTM_CUDA_TRY(cudaMemcpyAsync(l.cs, c_in + li * slab, slab * sizeof(float), cudaMemcpyDeviceToDevice, s));
+        else FLSTM_CUDA_TRY(cudaMemsetAsync(l.cs, 0, slab * sizeof(float), s));
+        const void *x_l = li == 0 ? x_seg : byte_ptr(layers[li - 1].hs) + slab * es;
+        FLSTM_TRY(tc::forward_layer(*this, li, 0, n, x_l, nullptr, s));
+    }
+    const size_t T_loc = last_in_time ? n : n + 1;  // slot n of dG then holds the step after the segment
+    for (int li = L - 1; li >= 0; --li) {
+        auto &l = layers[li];
+        const void *x_l = li == 0 ? x_seg : byte_ptr(layers[li - 1].hs) + slab * es;
+        const void *dy_l = (li == L - 1) ? dy_seg : layers[li + 1].dx;
+        void *dx_l = li == 0 ? dx_seg : l.dx;
+        FLSTM_TRY(tc::backward_layer(*this, li, T_loc, 0, n, x_l, dy_l, dhn ? byte_ptr(dhn) + li * slab * es : nullptr,
+                                     dcn ? byte_ptr(dcn) + li * slab * es : nullptr, dx_l,
+                                     (first_in_time && dh0) ? dh0 + li * slab : nullptr,
+                                     (first_in_time && dc0) ? dc0 + li * slab : nullptr, s));
+        if (!first_in_time)  // dG of the segment's first step: what the segment before it continues from
+            FLSTM_CUDA_TRY(cudaMemcpyAsync(byte_ptr(l.dg) + buf_steps * B * 4 * H * es, l.dg, B * 4 * H * es,
+                                           cudaMemcpyDeviceToDevice, s));
+    }
+    if (comm && first_in_time) {
+        FLSTM_CUDA_TRY(cudaEventRecord(comm_join, comm_stream));
+        FLSTM_CUDA_TRY(cudaStreamWaitEvent(s, comm_join, 0));
+    }
+    return FLSTM_OK;
+}
+
 // Time steps [t0, t1) of the backward pass, in reverse.  Ranges must be issued in descending order,
 // the first one ending at T; dy and dx are base pointers of the whole tensors.  dX of a range is
 // complete when the range's work is; the weight and bias gradients (and their allreduce) are formed
@@ -808,6 +865,15 @@ int flstm_engine_backward_range(flstm_engine *engine, size_t seq_len, size_t t0,
     if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
     DeviceScope scope(engine->impl.device);
     return engine->impl.backward_range(seq_len, t0, t1, dy, d_hn, d_cn, dx, dh0, dc0, static_cast<cudaStream_t>(stream));
+}
+
+int flstm_engine_backward_segment(flstm_engine *engine, size_t steps, int last_in_time, int first_in_time, const void *x_seg,
+                                  const void *h_in, const float *c_in, const void *dy_seg, const void *d_hn, const void *d_cn,
+                                  void *dx_seg, float *dh0, float *dc0, void *stream) {
+    if (!engine) return set_error(FLSTM_ERR_INVALID, "null engine");
+    DeviceScope scope(engine->impl.device);
+    return engine->impl.backward_segment(steps, last_in_time != 0, first_in_time != 0, x_seg, h_in, c_in, dy_seg, d_hn, d_cn,
+                                         dx_seg, dh0, dc0, static_cast<cudaStream_t>(stream));
 }
 
 int flstm_engine_grad_ptrs(flstm_engine *engine, int layer, float **dw_ih, float **dw_hh, float **db) {

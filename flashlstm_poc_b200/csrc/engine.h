@@ -126,6 +126,9 @@ struct Engine {
                              cudaStream_t s);
     int backward_checkpointed(size_t T, const void *dy, const void *dhn, const void *dcn, void *dx, float *dh0, float *dc0,
                               cudaStream_t s);
+    int backward_segment(size_t n, bool last_in_time, bool first_in_time, const void *x_seg, const void *h_in,
+                         const float *c_in, const void *dy_seg, const void *dhn, const void *dcn, void *dx_seg, float *dh0,
+                         float *dc0, cudaStream_t s);
     int set_recompute(size_t R);
     int backward_range(size_t T, size_t t0, size_t t1, const void *dy, const void *dhn, const void *dcn, void *dx,
                        float *dh0, float *dc0, cudaStream_t s);

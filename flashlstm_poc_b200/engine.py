@@ -131,6 +131,19 @@ class Engine:
         check(self.lib.flstm_engine_backward_range(self._h, T, t0, t1, dy.data_ptr(), _ptr(dhn), _ptr(dcn), _ptr(dx),
                                                    _ptr(dh0), _ptr(dc0), self._stream()))
 
+    def backward_segment_into(self, steps: int, last_in_time: bool, first_in_time: bool, x_seg, h_in, c_in, dy_seg, dhn, dcn,
+                              dx_seg, dh0, dc0) -> None:
+        """One segment of a sequence streamed through a segment-sized engine, last segment first
+        (see flstm_engine_backward_segment): h_in (L,B,H) engine dtype and c_in (L,B,H) fp32 are the states
+        that entered the segment."""
+        check(self.lib.flstm_engine_backward_segment(self._h, steps, int(last_in_time), int(first_in_time), x_seg.data_ptr(),
+                                                     _ptr(h_in), _ptr(c_in), dy_seg.data_ptr(), _ptr(dhn), _ptr(dcn),
+                                                     _ptr(dx_seg), _ptr(dh0), _ptr(dc0), self._stream()))
+
+    def set_cell_io_f32(self, on: bool = True) -> None:
+        """c0 / c_n cross the API as fp32 (the engine's own cell-state precision) instead of the engine dtype."""
+        check(self.lib.flstm_engine_set_cell_io_f32(self._h, 1 if on else 0))
+
     def capture_step(self, x, h0, c0, y, hn, cn, dy=None, dx=None, dh0=None, dc0=None) -> "torch.cuda.CUDAGraph":
         """Capture one forward (+ backward when dy is given) over the given, caller-owned tensors into a
         CUDA graph: the projection GEMM, the persistent recurrent kernels (cooperative launches), the

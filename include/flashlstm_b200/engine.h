@@ -126,6 +126,25 @@ int flstm_engine_set_cell_io_f32(flstm_engine *engine, int enabled);
 int flstm_engine_set_recompute_interval(flstm_engine *engine, size_t interval);
 size_t flstm_engine_workspace_bytes(const flstm_engine *engine);
 
+/* Host streaming of sequences that do not fit the device (the reference keeps 2 x 32 steps of x / y / dY / dX on
+ * the GPU and the rest in pinned host memory, flashlstm_v2/src/lstm_forward.cu:515,622-627,673-940,
+ * lstm_backward.cu:496-523,899-1213).  The engine is created with max_seq_len = S and recompute interval S, so
+ * its workspace holds ONE segment of S steps whatever the length of the sequence; the caller streams x, y, dY,
+ * dX and the h/c checkpoints of the segment boundaries.
+ *   forward : call flstm_engine_forward once per segment, in time order, with flstm_engine_set_cell_io_f32 on,
+ *             feeding each call's h_n / c_n (fp32 cell state) to the next call as h0 / c0; the states entering a
+ *             segment are its checkpoint.
+ *   backward: call flstm_engine_backward_segment once per segment, LAST segment first.  x_seg / dy_seg / dx_seg
+ *             are that segment's (steps,B,.) slices, h_in (L,B,H, engine dtype) and c_in (L,B,H, fp32) the
+ *             checkpoint that entered it (NULL = zeros).  The engine re-runs the segment's forward from the
+ *             checkpoint (rebuilding its gate cache), runs the BPTT over it and keeps the dh / dc carries for
+ *             the next call; d_hn / d_cn are read by the call with last_in_time, dh0 / dc0 are written and the
+ *             weight gradients are complete (and reduced over the ranks) after the call with first_in_time.
+ * Results equal a single whole-sequence call up to the fp32 summation order of dW / db.  Tensor-core backend. */
+int flstm_engine_backward_segment(flstm_engine *engine, size_t steps, int last_in_time, int first_in_time, const void *x_seg,
+                                  const void *h_in, const float *c_in, const void *dy_seg, const void *d_hn, const void *d_cn,
+                                  void *dx_seg, float *dh0, float *dc0, void *stream);
+
 /* Which backend the engine resolved to (flstm_backend, never AUTO). */
 int flstm_engine_backend(const flstm_engine *engine);
 

@@ -13,6 +13,11 @@
  *  - x, y, dY, dx and both checkpoint tensors are (pinned) HOST buffers; states, weights and
  *    gradients are DEVICE buffers.  Here a DEVICE pointer is also accepted for any of the
  *    host tensors (detected with cudaPointerGetAttributes) and is then used in place.
+ *  - backward is stateless like the reference's: everything travels by pointer.  When it directly
+ *    follows the forward of the same y tensor it consumes that forward's gate cache (and the weights
+ *    that forward packed); otherwise, and always for sequences too long to stay on the device, it
+ *    restores the state entering each segment from the CALLER'S h/c checkpoints and recomputes the
+ *    segment (flashlstm_v2/src/lstm_backward.cu:496-523,975-1054).
  *  - x/y/dY/dx are fp16 (T,B,.); weights fp32 (4H,.) in gate order i,f,g,o; biases fp32 4H.
  *  - the "gate cache" is a pair of checkpoint tensors (ceil(T/R),B,H): entry k holds the h
  *    (resp. c) state ENTERING step k*R (entry 0 = h0/c0), stored as fp32 or fp16 according
@@ -117,6 +122,20 @@ void flstm_StreamingLstmBackward(size_t time_steps, size_t batch_size, size_t in
 
 /* Status of the last flstm_Streaming* call on this thread (a flstm_status value). */
 int flstm_last_status(void);
+
+/* Additions without a counterpart in the reference.
+ * flstm_v2_set_weight_version: the reference converts and fuses the fp32 weights on every forward and every
+ * backward call (flashlstm_v2/src/lstm_forward.cu:605, lstm_backward.cu:755), because the API passes bare
+ * pointers and cannot know whether an optimiser has updated them in place.  A caller that can tell publishes a
+ * non-zero version here and changes it whenever the weights change; calls then re-pack only when the version
+ * or one of the four parameter pointers differs from the last packing.  Version 0 (the default) restores
+ * "pack on every call".
+ * flstm_v2_last_call_info: device bytes held by the context of the last flstm_Streaming* call on this thread
+ * (engine workspace + staging) and whether it ran in streaming mode (the sequence processed in fixed-size
+ * segments, footprint independent of T) or resident mode.  FLSTM_V2_DEVICE_BUDGET_BYTES caps the memory a
+ * problem may take before streaming mode is chosen; FLSTM_V2_SEGMENT_STEPS fixes the segment length. */
+void flstm_v2_set_weight_version(unsigned long long version);
+void flstm_v2_last_call_info(size_t *device_bytes, int *streaming);
 
 #ifdef __cplusplus
 }

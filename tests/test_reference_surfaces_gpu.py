@@ -196,7 +196,7 @@ def test_v2_c_abi_forward_backward(T, B, I, H, R):
         assert orc.rel_l2_err(got.numpy(), want.numpy()) < 1e-2
     assert torch.equal(G[2], G[3])  # db_ih == db_hh
 
-    # a stateless backward (another forward ran in between) rebuilds the cache and agrees
+    # a stateless backward (another forward ran in between) consumes the caller's checkpoints and agrees
     y2 = torch.empty_like(y).pin_memory()
     lib.flstm_StreamingLstmForward(T, B, I, H, R, x.data_ptr(), h0d.data_ptr(), c0d.data_ptr(), P[0].data_ptr(),
                                    P[1].data_ptr(), P[2].data_ptr(), P[3].data_ptr(), y2.data_ptr(), cache,
@@ -209,7 +209,10 @@ def test_v2_c_abi_forward_backward(T, B, I, H, R):
                                     G2[2].data_ptr(), G2[3].data_ptr(), dh0.data_ptr(), dc0.data_ptr(), s1.cuda_stream,
                                     s2.cuda_stream, s3.cuda_stream, ctypes.byref(opt))
     assert lib.flstm_last_status() == 0
-    assert torch.equal(G2[1], G[1])
+    # this one could not use the forward's gate cache: it restored the states from the caller's checkpoints
+    # (h fp16 = exact, c fp32 = exact) and recomputed; only the fp32 summation order of dW may differ
+    assert orc.rel_l2_err(G2[1].cpu().numpy(), G[1].cpu().numpy()) < 1e-5
+    assert orc.rel_l2_err(G2[0].cpu().numpy(), G[0].cpu().numpy()) < 1e-5
 
 
 def test_v2_rejects_misuse_without_aborting():
