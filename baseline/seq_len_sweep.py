@@ -95,6 +95,24 @@ def main():
         rows.append(row)
         print(json.dumps(row), flush=True)
 
+    # input_proj_chunk_size sweep at T=2048 (what src/tune_projchunksz.cu:56-225 does: chunk in {0, 8, ..., 1024},
+    # 1 warm-up + 5 timed), both libraries through the same calls
+    chunk_rows = []
+    Tc = 2048
+    xc = torch.randn(Tc, B, I, device="cuda")
+    h0c, c0c = torch.zeros(B, H, device="cuda"), torch.zeros(B, H, device="cuda")
+    for chunk in (0, 8, 16, 32, 64, 128, 256, 512, 1024):
+        row = {"chunk": chunk}
+        for name, lib in libs.items():
+            try:
+                r = rg.V1Runner(lib, Tc, B, I, H, params, chunk=chunk)
+                row[name] = rg.time_calls(lambda: r.forward(xc, h0c, c0c), 1, 5) * 1e3
+                r.close()
+            except Exception as exc:
+                row[name] = f"failed: {exc}"
+        chunk_rows.append(row)
+        print(json.dumps(row), flush=True)
+
     # v2: forward + backward at benchmark configuration 2 through both libraries
     v2 = {}
     T2, B2, R = 512, 64, 1
@@ -138,6 +156,12 @@ def main():
         for row in rows:
             f.write(f"| {row['T']} | " + " | ".join(
                 (f"{row[c]:.3f}" if isinstance(row.get(c), float) else str(row.get(c, ""))) for c in cols) + " |\n")
+        f.write("\n## input_proj_chunk_size sweep, T=2048, B=32, I=H=1024 (ms per call, median of 5)\n\n")
+        ccols = [c for c in chunk_rows[0] if c != "chunk"] if chunk_rows else []
+        f.write("| chunk | " + " | ".join(ccols) + " |\n|---|" + "---|" * len(ccols) + "\n")
+        for row in chunk_rows:
+            f.write(f"| {row['chunk']} | " + " | ".join(
+                (f"{row[c]:.3f}" if isinstance(row.get(c), float) else str(row.get(c, ""))) for c in ccols) + " |\n")
         f.write("\n## v2 entry points, forward + backward, FP16, B=64, I=H=1024, T=512, R=1 (pinned host tensors)\n\n")
         for name, r in v2.items():
             f.write(f"* {name}: {json.dumps(r)}\n")

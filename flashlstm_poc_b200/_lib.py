@@ -24,7 +24,7 @@ ENGINE_SYMBOLS = [
     "flstm_version",
 ]
 V1_SYMBOLS = ["lstm_create_buffers", "lstm_destroy_buffers", "lstm_set_execution_mode", "lstm_pack_weights",
-              "lstm_forward"]
+              "lstm_forward", "lstm_graph_replays"]
 V2_SYMBOLS = ["flstm_StreamingLstmForward", "flstm_StreamingLstmBackward", "flstm_last_status",
               "flstm_v2_set_weight_version", "flstm_v2_last_call_info"]
 
@@ -124,6 +124,8 @@ def load() -> ctypes.CDLL:
     lib.lstm_set_execution_mode.argtypes = [ctypes.POINTER(LstmBuffers), ci]
     lib.lstm_pack_weights.argtypes = [ci, vp, vp, sz, sz, ctypes.POINTER(LstmBuffers)]
     lib.lstm_forward.argtypes = [vp] * 8 + [sz] * 4 + [ctypes.POINTER(LstmBuffers), ci]
+    lib.lstm_graph_replays.argtypes = [ctypes.POINTER(LstmBuffers)]
+    lib.lstm_graph_replays.restype = ctypes.c_ulonglong
     # v2 surface
     lib.flstm_StreamingLstmForward.argtypes = [sz] * 5 + [vp] * 8 + [GateCacheHost, ctypes.POINTER(StreamingLstmOptions)] + [vp] * 5
     lib.flstm_StreamingLstmForward.restype = None

@@ -53,6 +53,10 @@ int lstm_destroy_buffers(lstm_buffers *buffers);
 
 int lstm_set_execution_mode(lstm_buffers *buffers, lstm_execution_mode_t mode);
 
+/* Not in the reference: how many lstm_forward calls on this handle were served by replaying the captured
+ * graph of GRAPH mode (the first call with a new seq_len or new tensor addresses runs directly and records). */
+unsigned long long lstm_graph_replays(const lstm_buffers *buffers);
+
 int lstm_pack_weights(lstm_compute_precision_t precision, const float *weight_ih,
                       const float *weight_hh, size_t input_size, size_t hidden_size,
                       lstm_buffers *buffers);

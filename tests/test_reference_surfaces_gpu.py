@@ -64,6 +64,44 @@ def test_v1_c_abi_matches_cpu_lstm(T, B, I, H):
     assert bufs.impl is None
 
 
+@pytest.mark.parametrize("T,B,I,H,chunk", [(48, 32, 256, 256, 0), (48, 32, 256, 256, 16), (12, 4, 24, 16, 5)])
+def test_v1_graph_mode_replays_and_matches_immediate(T, B, I, H, chunk):
+    """lstm_set_execution_mode (src/lstm.cu:869-884): GRAPH captures the call and replays it while the sequence
+    length and the tensors stay the same, re-records when T changes (:2085-2087); IMMEDIATE launches directly.
+    Outputs are bit-identical between the modes and across replays; input_proj_chunk_size splits the sequence
+    into ranges without changing a bit either."""
+    lib = _lib.load()
+    torch.manual_seed(17)
+    lstm = torch.nn.LSTM(I, H).eval()
+    ACC32, IMMEDIATE, GRAPH = 0, 0, 1
+    dev = "cuda"
+    w_ih, w_hh = lstm.weight_ih_l0.detach().to(dev).contiguous(), lstm.weight_hh_l0.detach().to(dev).contiguous()
+    bi, bh = lstm.bias_ih_l0.detach().to(dev), lstm.bias_hh_l0.detach().to(dev)
+    x, h0, c0 = torch.randn(T + 1, B, I, device=dev), torch.randn(B, H, device=dev), torch.randn(B, H, device=dev)
+    results = {}
+    for mode, ck in ((IMMEDIATE, 0), (GRAPH, chunk)):
+        bufs = _lib.LstmBuffers()
+        assert lib.lstm_create_buffers(ACC32, T, B, I, H, ck, ctypes.byref(bufs)) == 0
+        assert lib.lstm_pack_weights(ACC32, w_ih.data_ptr(), w_hh.data_ptr(), I, H, ctypes.byref(bufs)) == 0
+        assert lib.lstm_set_execution_mode(ctypes.byref(bufs), mode) == 0
+        out, hn, cn = torch.empty(T + 1, B, H, device=dev), torch.empty(B, H, device=dev), torch.empty(B, H, device=dev)
+        runs = []
+        for t in (T, T, T, T + 1, T + 1, T):  # replay twice, re-record for T+1, replay, re-record for T
+            out.zero_()
+            assert lib.lstm_forward(x.data_ptr(), bi.data_ptr(), bh.data_ptr(), h0.data_ptr(), c0.data_ptr(), out.data_ptr(),
+                                    hn.data_ptr(), cn.data_ptr(), t, B, I, H, ctypes.byref(bufs), ACC32) == 0
+            runs.append((t, out[:t].clone(), hn.clone(), cn.clone()))
+        replays = lib.lstm_graph_replays(ctypes.byref(bufs))
+        assert replays == (3 if mode == GRAPH else 0)
+        assert lib.lstm_destroy_buffers(ctypes.byref(bufs)) == 0
+        results[mode] = runs
+    for (t, y_i, hn_i, cn_i), (_, y_g, hn_g, cn_g) in zip(results[IMMEDIATE], results[GRAPH]):
+        assert torch.equal(y_i, y_g) and torch.equal(hn_i, hn_g) and torch.equal(cn_i, cn_g)
+    with torch.no_grad():
+        y_ref, _ = lstm(x[:T].cpu(), (h0.cpu().unsqueeze(0), c0.cpu().unsqueeze(0)))
+    np.testing.assert_allclose(results[GRAPH][0][1].cpu().numpy(), y_ref.numpy(), atol=1e-3, rtol=5e-2)
+
+
 def _pinned_half(shape):
     t = torch.empty(shape, dtype=torch.float16, pin_memory=True)
     t.copy_(torch.randn(shape).half())
