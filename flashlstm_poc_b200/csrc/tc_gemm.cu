@@ -9,6 +9,13 @@
 //                          next tile's main loop through the second accumulator
 // The grid is persistent (one CTA per SM, static round-robin over output tiles).
 //
+// Two tile shapes.  gemm_kernel: one CTA per 128 x BN tile (BN 128 / 256).  gemm_pair_kernel: a cluster of two
+// CTAs per 256 x 256 tile (tcgen05 cta_group::2): each CTA stages 128 rows of A and 128 rows of B per K block
+// (32 KB instead of the 48 KB a lone CTA needs for 128 x 256) and the pair's UMMA reads both halves of B, so the
+// shared-memory traffic per FLOP -- what bounds the one-CTA kernel at about 2/3 of the tensor peak -- drops by a
+// third, and so does the L2 traffic.  Every CTA loads its own halves with plain TMA copies (nothing is multicast).
+// The pair kernel is used when M >= 256 and N is a multiple of 256 (FLSTM_GEMM_PAIR=0 turns it off).
+//
 // Used for (shapes at the benchmark configurations, per layer):
 //   input projection  P[T*B,4H]  = X[T*B,I] W_ih^T + b      (K-major x K-major, 16-bit out)
 //   input gradient    dX[T*B,I]  = dG[T*B,4H] W_ih          (K-major x K-major via W_ih^T, 16-bit out)
@@ -314,6 +321,207 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     if (threadIdx.x == 0 && *abort_w) atomicExch(err_word, 1u);
 }
 
+// ------------------------------------------------------------------ CTA-pair kernel (256 x 256 tiles)
+struct PairShape {
+    static constexpr int kBN = 256;         // tile width; each CTA stages kBN / 2 rows of B
+    static constexpr int kStages = 6;
+    static constexpr int kABytes = BM * BK * 2;
+    static constexpr int kBBytes = (kBN / 2) * BK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;  // per CTA
+    static constexpr int kTmemCols = 2 * kBN;
+    static constexpr int kOutTileBytes = 32 * 128;
+    static constexpr int kOutBytes = 4 * 2 * kOutTileBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+// Roles as in gemm_kernel, in both CTAs of the pair, except that only the leader's warp 1 issues UMMAs.
+// Barriers (same offsets in both CTAs):
+//   full[s]   leader only: 1 arrival (its expect_tx) + the bytes of BOTH CTAs' loads of stage s
+//   empty[s]  each CTA: 1 arrival = the leader's commit after the UMMAs that read stage s
+//   tfull[b]  each CTA: 1 arrival = the leader's commit after the last UMMA of a tile (accumulator b complete)
+//   tempty[b] leader only: 8 arrivals = the four epilogue warps of both CTAs have drained accumulator b
+template <int MODE, bool HAS_BIAS, bool A_MN, bool B_MN, bool TMA_OUT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const __grid_constant__ CUtensorMap tm_d, void *__restrict__ D, size_t ldd,
+                 const float *__restrict__ bias, int M, int N, int K, uint32_t idesc, int unperm_h,
+                 unsigned int *__restrict__ err_word, int accumulate) {
+    using S = PairShape;
+    constexpr int BN = S::kBN, BNH = S::kBN / 2;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *s_out = smem + S::kStages * S::kStageBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_out + S::kOutBytes);
+    uint64_t *full = bars, *empty = bars + S::kStages;
+    uint64_t *tfull = bars + 2 * S::kStages, *tempty = tfull + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty + 2);
+    volatile uint32_t *abort_w = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    if (threadIdx.x == 0) {
+        if (TMA_OUT) tma_prefetch_desc(&tm_d);
+        for (int i = 0; i < S::kStages; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&tfull[i], 1);
+            mbar_init(&tempty[i], 8);
+        }
+        *abort_w = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tm_a);
+        tma_prefetch_desc(&tm_b);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, S::kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers and tensor memory exist before anything crosses the pair
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_m = (M + 2 * BM - 1) / (2 * BM), num_n = N / BN;
+    const int tiles = num_m * num_n, kblocks = (K + BK - 1) / BK;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            const uint32_t full0 = map_to_rank(smem_u32(full), 0);  // the leader's "operands landed" barriers
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int tile = pair; tile < tiles; tile += npairs) {
+                const int m0 = (tile / num_n) * 2 * BM + (int)rank * BM, n0 = (tile % num_n) * BN + (int)rank * BNH;
+                bool ok = true;
+                for (int kb = 0; kb < kblocks && ok; ++kb) {
+                    ok = mbar_wait(&empty[stage], phase ^ 1, abort_w);
+                    if (!ok) break;
+                    uint8_t *sa = smem + stage * S::kStageBytes, *sb = sa + S::kABytes;
+                    const uint32_t bar = full0 + 8u * (uint32_t)stage;
+                    if (leader) mbar_expect_tx(&full[stage], 2 * S::kStageBytes);
+                    if (!A_MN) {
+                        tma_load_2d_pair(sa, &tm_a, kb * BK, m0, bar);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * 8192, &tm_a, m0 + j * 64, kb * BK, bar);
+                    }
+                    if (!B_MN) {
+                        tma_load_2d_pair(sb, &tm_b, kb * BK, n0, bar);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(sb + j * 8192, &tm_b, n0 + j * 64, kb * BK, bar);
+                    }
+                    if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (leader && elect_one()) {
+            const uint32_t empty_l = smem_u32(empty), empty_p = map_to_rank(smem_u32(empty), 1);
+            const uint32_t tfull_l = smem_u32(tfull), tfull_p = map_to_rank(smem_u32(tfull), 1);
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            for (int tile = pair; tile < tiles; tile += npairs, ++it) {
+                const int buf = it & 1;
+                const uint32_t bphase = (it >> 1) & 1;
+                if (!mbar_wait_cluster(&tempty[buf], bphase ^ 1, abort_w)) break;
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                bool ok = true;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = mbar_wait(&full[stage], phase, abort_w);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t a_base = smem_u32(smem + stage * S::kStageBytes), b_base = a_base + S::kABytes;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t da = A_MN ? umma_desc_mnmajor_sw128(a_base + k * 2048, 8192)
+                                                 : umma_desc_kmajor_sw128(a_base + k * 32);
+                        const uint64_t db = B_MN ? umma_desc_mnmajor_sw128(b_base + k * 2048, 8192)
+                                                 : umma_desc_kmajor_sw128(b_base + k * 32);
+                        umma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0);
+                    }
+                    // the stage may be refilled in both CTAs once these UMMAs have read it
+                    umma_commit_pair(empty_l + 8u * (uint32_t)stage);
+                    umma_commit_pair(empty_p + 8u * (uint32_t)stage);
+                    if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit_pair(tfull_l + 8u * (uint32_t)buf);
+                umma_commit_pair(tfull_p + 8u * (uint32_t)buf);
+            }
+        }
+    } else {
+        const int q = warp & 3;  // TMEM lane quadrant this warp may access
+        const uint32_t tempty0 = map_to_rank(smem_u32(tempty), 0);
+        int it = 0, out_idx = 0;
+        for (int tile = pair; tile < tiles; tile += npairs, ++it) {
+            const int buf = it & 1;
+            const uint32_t bphase = (it >> 1) & 1;
+            const int m0 = (tile / num_n) * 2 * BM + (int)rank * BM, n0 = (tile % num_n) * BN;
+            if (!mbar_wait(&tfull[buf], bphase, abort_w)) break;
+            tcgen05_fence_after();
+            const int row = m0 + q * 32 + lane;
+            if (TMA_OUT) {
+                const int row0 = m0 + q * 32;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 64) {
+                    uint32_t acc[64];
+                    tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c, *reinterpret_cast<uint32_t(*)[32]>(&acc[0]));
+                    tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c + 32, *reinterpret_cast<uint32_t(*)[32]>(&acc[32]));
+                    tmem_ld_wait();
+                    if (c + 64 >= BN) {  // accumulator drained: the leader may start the tile after next
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(tempty0 + 8u * (uint32_t)buf);
+                    }
+                    const int n_valid = N - (n0 + c);
+                    if (row0 >= M || n_valid <= 0) continue;
+                    uint8_t *tile_s = s_out + (q * 2 + (out_idx & 1)) * S::kOutTileBytes;
+                    if (lane == 0) tma_store_wait_read<1>();  // the store that last used this buffer has read it
+                    __syncwarp();
+                    stage_row64<MODE>(tile_s, lane, acc, HAS_BIAS ? bias : nullptr, n0 + c, n_valid);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tm_d, tile_s, n0 + c, row0);
+                        tma_store_commit();
+                    }
+                    ++out_idx;
+                }
+                continue;
+            }
+            const size_t esz = (MODE == OUT_F32) ? 4 : 2;
+            const int out_row = (unperm_h && row < M) ? unpermute_gate_row(row, unperm_h) : row;
+            char *dst_row = static_cast<char *>(D) + (size_t)out_row * ldd * esz;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t acc[32];
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c, acc);
+                tmem_ld_wait();
+                const int n_valid = N - (n0 + c);
+                if (row < M && n_valid > 0)
+                    store_row32<MODE>(dst_row, n0 + c, acc, HAS_BIAS ? bias : nullptr, n_valid, MODE == OUT_F32 && accumulate);
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty0 + 8u * (uint32_t)buf);
+        }
+        if (TMA_OUT && lane == 0) tma_store_wait_all<0>();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer's shared and tensor memory stay valid until the leader's last UMMA is consumed
+    if (warp == 1) tmem_dealloc_pair(tmem_base, S::kTmemCols);
+    if (threadIdx.x == 0 && *abort_w) atomicExch(err_word, 1u);
+}
+
 struct GemmArgs {
     CUtensorMap ta, tb, td;
     bool tma_out;
@@ -327,7 +535,17 @@ struct GemmArgs {
     int sms;
     int accumulate;
     cudaStream_t s;
+    bool pair;  // 256 x 256 tiles on CTA pairs (gemm_pair_kernel)
 };
+
+bool pair_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char *env = std::getenv("FLSTM_GEMM_PAIR");
+        on = (env && env[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
 
 template <int BN, int MODE, bool HAS_BIAS, bool A_MN, bool B_MN, bool TMA_OUT>
 int launch_one(const GemmArgs &g) {
@@ -343,8 +561,40 @@ int launch_one(const GemmArgs &g) {
     return FLSTM_OK;
 }
 
+template <int MODE, bool HAS_BIAS, bool A_MN, bool B_MN, bool TMA_OUT>
+int launch_pair_one(const GemmArgs &g) {
+    using S = PairShape;
+    auto kern = gemm_pair_kernel<MODE, HAS_BIAS, A_MN, B_MN, TMA_OUT>;
+    FLSTM_CUDA_TRY(ensure_smem_limit(kern, (size_t)S::kSmemBytes));
+    const int tiles = ((g.M + 2 * BM - 1) / (2 * BM)) * (g.N / S::kBN);
+    const int pairs = tiles < g.sms / 2 ? tiles : g.sms / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = S::kSmemBytes;
+    cfg.stream = g.s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, g.ta, g.tb, g.td, g.D, g.ldd, g.bias, g.M, g.N, g.K, g.idesc, g.unperm_h,
+                                       g.err, g.accumulate);
+    if (e != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "tc pair gemm launch failed: %s", cudaGetErrorString(e));
+    return FLSTM_OK;
+}
+
+template <int MODE, bool HAS_BIAS, bool A_MN, bool B_MN>
+int launch_pair(const GemmArgs &g) {
+    if (MODE != OUT_F32 && g.tma_out) return launch_pair_one<MODE, HAS_BIAS, A_MN, B_MN, (MODE != OUT_F32)>(g);
+    return launch_pair_one<MODE, HAS_BIAS, A_MN, B_MN, false>(g);
+}
+
 template <int BN, int MODE, bool HAS_BIAS, bool A_MN, bool B_MN>
 int launch(const GemmArgs &g) {
+    if (g.pair) return launch_pair<MODE, HAS_BIAS, A_MN, B_MN>(g);
     if (MODE != OUT_F32 && g.tma_out) return launch_one<BN, MODE, HAS_BIAS, A_MN, B_MN, (MODE != OUT_F32)>(g);
     return launch_one<BN, MODE, HAS_BIAS, A_MN, B_MN, false>(g);
 }
@@ -393,10 +643,11 @@ int gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, 
         return set_error(FLSTM_ERR_UNSUPPORTED, "tensor-core GEMM needs 16-byte aligned operands and row pitches");
     const int BN = (N > 128) ? 256 : 128;
     GemmArgs g{};
+    g.pair = pair_enabled() && M >= 256 && N % 256 == 0 && sms >= 2;
     // K-major: (rows, K) with K contiguous, box rows x 64.  MN-major: stored (K, rows), 64 x 64 boxes.
     if (!a_mn) FLSTM_TRY(make_tensor_map_2d(&g.ta, A, M, K, lda, BM, BK, true));
     else FLSTM_TRY(make_tensor_map_2d(&g.ta, A, K, M, lda, BK, 64, true));
-    if (!b_mn) FLSTM_TRY(make_tensor_map_2d(&g.tb, B, N, K, ldb, BN, BK, true));
+    if (!b_mn) FLSTM_TRY(make_tensor_map_2d(&g.tb, B, N, K, ldb, g.pair ? 128 : BN, BK, true));
     else FLSTM_TRY(make_tensor_map_2d(&g.tb, B, K, N, ldb, BK, 64, true));
     // 16-bit outputs go out through TMA when D can be described by a tensor map
     g.tma_out = out_dtype != FLSTM_DTYPE_F32 && unperm_h == 0 && N >= 64 && (ldd % 8) == 0 &&
@@ -410,7 +661,7 @@ int gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, 
     g.M = (int)M;
     g.N = (int)N;
     g.K = (int)K;
-    g.idesc = umma_idesc_f16(BM, BN, dtype == FLSTM_DTYPE_BF16 ? 1 : 0, a_mn ? 1 : 0, b_mn ? 1 : 0);
+    g.idesc = umma_idesc_f16(g.pair ? 2 * BM : BM, BN, dtype == FLSTM_DTYPE_BF16 ? 1 : 0, a_mn ? 1 : 0, b_mn ? 1 : 0);
     g.unperm_h = unperm_h;
     g.err = err_word;
     g.sms = sms;

@@ -516,13 +516,23 @@ int plan_bwd(int B, int H, int sms, size_t smem_limit, BwdPlan *plan, bool check
            jt * KS * 2 <= sms)
         KS *= 2;
     if (jt * KS > sms) return set_error(FLSTM_ERR_UNSUPPORTED, "hidden size too large for the persistent BPTT kernel");
-    const int BT = (B >= 128) ? 64 : 32;
-    const int tiles = (B + BT - 1) / BT;
-    int ngroups = sms / (jt * KS);
-    if (ngroups > tiles) ngroups = tiles;
-    if (ngroups < 1) ngroups = 1;
-    int nt = (tiles + ngroups - 1) / ngroups;
-    ngroups = (tiles + nt - 1) / nt;
+    // batch tile width as in plan_fwd: 33..64 sequences are one 64-wide tile when a CTA would otherwise take two
+    int BT = (B >= 128) ? 64 : 32;
+    int tiles = 0, ngroups = 0, nt = 0;
+    auto split = [&](int bt) {
+        tiles = (B + bt - 1) / bt;
+        ngroups = sms / (jt * KS);
+        if (ngroups > tiles) ngroups = tiles;
+        if (ngroups < 1) ngroups = 1;
+        nt = (tiles + ngroups - 1) / ngroups;
+        ngroups = (tiles + nt - 1) / nt;
+    };
+    split(BT);
+    if (BT == 32 && nt == 2 && 2 * jt * KS > sms && wide_tile_enabled()) {
+        split(64);
+        if (nt == 1) BT = 64;
+        else split(32);
+    }
     const int kc_per = kc_total / KS;
     // measured on config 2: one 64 KB copy per step beats 2, 4, 8 or 16 smaller ones (TMA issue cost
     // outweighs the longer exposed UMMA tail), so a stage takes up to 16 chunks

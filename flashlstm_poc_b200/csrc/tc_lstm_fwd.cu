@@ -388,19 +388,37 @@ static int launch_fwd(const CUtensorMap &tw, const CUtensorMap &th, const CUtens
     return FLSTM_OK;
 }
 
+// FLSTM_BT64=0 keeps 32-wide batch tiles for 33..64 sequences (two tiles per CTA when H >= 2048)
+bool wide_tile_enabled() {
+    const char *env = std::getenv("FLSTM_BT64");
+    return !(env && env[0] == '0');
+}
+
 int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan) {
     if (H % 64 != 0 || H < 64) return set_error(FLSTM_ERR_UNSUPPORTED, "hidden size must be a multiple of 64");
     const int R = H / 16;  // row tiles
     int rt = 1;
     while (R / rt > sms || R % rt) ++rt;
     const int cta_rows = R / rt;
-    const int BT = (B >= 128) ? 64 : 32;
-    const int tiles = (B + BT - 1) / BT;
-    int ngroups = sms / cta_rows;
-    if (ngroups > tiles) ngroups = tiles;
-    if (ngroups < 1) ngroups = 1;
-    const int nt = (tiles + ngroups - 1) / ngroups;
-    ngroups = (tiles + nt - 1) / nt;
+    // 32 sequences per batch tile while every batch group then gets its own set of CTAs; when the row tiles
+    // alone fill the machine (H >= 2048) a CTA would take two 32-wide tiles per step and stream its W_hh slice
+    // twice, so 33..64 sequences become ONE 64-wide tile (the UMMA costs the same at N = 32 and N = 64)
+    int BT = (B >= 128) ? 64 : 32;
+    int tiles = 0, ngroups = 0, nt = 0;
+    auto split = [&](int bt) {
+        tiles = (B + bt - 1) / bt;
+        ngroups = sms / cta_rows;
+        if (ngroups > tiles) ngroups = tiles;
+        if (ngroups < 1) ngroups = 1;
+        nt = (tiles + ngroups - 1) / ngroups;
+        ngroups = (tiles + nt - 1) / nt;
+    };
+    split(BT);
+    if (BT == 32 && nt == 2 && 2 * cta_rows > sms && wide_tile_enabled()) {
+        split(64);
+        if (nt == 1) BT = 64;
+        else split(32);
+    }
     // One TMA copy brings `ch` 64-wide K chunks of an h tile; the ring holds a whole tile when it can.
     // The W_hh slice stays resident if it fits next to a ring of at least two stages.
     const int kc = H / 64;

@@ -40,20 +40,6 @@ __device__ __forceinline__ bool named_barrier_or(int id, int threads, bool pred)
         : "memory");
     return out != 0;
 }
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// shared::cta address -> shared::cluster address of the same offset in CTA `rank`
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
-    return r;
-}
 // 16 bytes into a cluster peer's (or this CTA's) shared memory; their arrival is counted on the mbarrier at
 // `bar_addr` (same CTA as `addr`), so the data carries its own completion signal: the sender neither waits for
 // the stores nor sends an arrive after them
@@ -61,36 +47,6 @@ __device__ __forceinline__ void st_async_v4(uint32_t addr, uint32_t a, uint32_t 
     asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
                  ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(bar_addr) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_w,
-                                                  unsigned long long limit_ns = kWaitLimitNs) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    const unsigned long long t0 = global_timer_ns();
-    uint32_t spins = 0;
-    while (!mbar_try_wait_cluster(bar, parity)) {
-        if ((++spins & 255u) == 0) {
-            if (*abort_w) return false;
-            if (global_timer_ns() - t0 > limit_ns) {
-                *abort_w = 1;
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
 // Bounded poll of a monotonic counter written by other CTAs; `code` goes to the error word on expiry.
 __device__ __forceinline__ bool wait_counter(const unsigned int *ctr, unsigned int target, unsigned int *err_word,
                                              volatile uint32_t *abort_w, unsigned int code,

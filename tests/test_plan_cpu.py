@@ -61,12 +61,16 @@ def test_benchmark_configuration_plan(lib):
 
 
 @pytest.mark.parametrize("B,H,step", [(64, 1024, 0), (96, 1024, 1), (128, 1024, 0), (160, 1024, 1), (2048, 1024, 1),
-                                      (32, 2048, 0), (64, 2048, 1), (256, 2048, 1), (8, 4096, 0), (64, 4096, 1)])
+                                      (32, 2048, 0), (64, 2048, 0), (128, 2048, 1), (256, 2048, 1), (8, 4096, 0),
+                                      (64, 4096, 0), (96, 4096, 1)])
 def test_path_choice_follows_the_measured_crossover(lib, B, H, step):
     """Measured on B200: the persistent kernels win while a CTA has one batch tile per step, the per-step GEMM
-    launches win from two tiles per CTA on (these ten shapes were timed both ways)."""
+    launches win from two tiles per CTA on.  Where the row tiles alone fill the machine (H >= 2048), 33..64
+    sequences are one 64-wide tile, so those shapes stay on the persistent kernels."""
     st, p = plan(lib, B, H, training=0 if H == 4096 else 1)
     assert st == 0 and p.step_path == step
+    if not step and H >= 2048 and B > 32:
+        assert p.fwd_batch_tile == 64 and p.fwd_tiles_per_group == 1
 
 
 def test_wide_batch_plans(lib):

@@ -1,6 +1,7 @@
 """The tcgen05/TMEM/TMA dense contraction against a plain fp32/fp64 torch matmul of the same
 (16-bit rounded) operands.  Covers both operand layouts the path uses, both 16-bit types, every
-output type, the bias epilogue, and sizes no tile divides."""
+output type, the bias epilogue, sizes no tile divides, and both tile shapes: one CTA per 128 x BN
+tile, and CTA pairs on 256 x 256 tiles (M >= 256 and N a multiple of 256)."""
 import pytest
 import torch
 
@@ -30,6 +31,7 @@ def _rel(got, want):
 @pytest.mark.parametrize("dtype", ["f16", "bf16"])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 128), (256, 512, 256), (384, 128, 1024),
                                    (200, 136, 72), (64, 64, 64), (1000, 520, 200), (4096, 1024, 512),
+                                   (1000, 512, 200), (8192, 1024, 192),  # CTA-pair tiles: ragged M, many tiles per pair
                                    (300, 100, 64)])  # N=100: row pitch not a multiple of 16 B -> plain-store epilogue
 def test_kmajor_gemm(dtype, M, N, K):
     torch.manual_seed(M + N + K)
@@ -49,7 +51,7 @@ def test_kmajor_gemm(dtype, M, N, K):
 
 @pytest.mark.parametrize("dtype", ["f16", "bf16"])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 128), (256, 128, 1024), (512, 512, 4096),
-                                   (192, 320, 200), (64, 64, 64), (1024, 256, 8192)])
+                                   (192, 320, 200), (64, 64, 64), (1024, 256, 8192), (4096, 2048, 512), (300, 256, 136)])
 def test_mnmajor_gemm(dtype, M, N, K):
     """D = A^T-stored x B^T-stored: A is given as (K,M), B as (K,N); the reduction dim is outermost,
     which is how dG (T*B,4H) and [X|H] (T*B,I) lie in memory for dW = dG^T X."""
