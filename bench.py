@@ -701,8 +701,16 @@ def dp_check(args, eng, w, inp, P, B, dev, td, world, rank):
         t0 = time.perf_counter()
         params = [orc.LayerParams(inp.w_ih[l].numpy(), inp.w_hh[l].numpy(), inp.b_ih[l].numpy(), inp.b_hh[l].numpy())
                   for l in range(L)]
+        # the launcher pins every rank to one BLAS thread; the other ranks idle while rank 0 runs the oracle
+        try:
+            from threadpoolctl import threadpool_limits
+            blas_threads = threadpool_limits(limits=os.cpu_count() or 1)
+        except Exception:
+            blas_threads = None
         fwd = orc.lstm_forward(torch.cat(xs, 1).float().cpu().numpy(), params, None, None)
         bwd = orc.lstm_backward(fwd, params, torch.cat(dys, 1).float().cpu().numpy())
+        if blas_threads is not None:
+            blas_threads.restore_original_limits()
         oracle_s = time.perf_counter() - t0
         worst_oracle = 0.0
         for l in range(L):

@@ -267,8 +267,8 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
 // Two CTAs of a cluster (ranks 0 and 1) drive one UMMA of M = 256: each holds 128 rows of A and N/2 rows of B
 // in its own shared memory at the same offsets, each gets its 128 accumulator rows in its own tensor memory.
 // Only the leader (rank 0) issues the UMMAs and waits on the "operands landed" barrier, which both CTAs' TMA
-// loads complete; it then signals barriers in BOTH CTAs (one commit each) that the operands / the accumulator
-// may be reused / read.  No load is multicast: every CTA fetches its own halves.
+// loads complete; its commits then signal barriers in BOTH CTAs that the operands / the accumulator may be
+// reused / read.  No load is multicast: every CTA fetches its own halves.
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -319,11 +319,17 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, 
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// one arrival on the mbarrier at a shared::cluster address (own or peer CTA) when every UMMA issued so far by
-// this thread has completed
-__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
-                 : "memory");
+// One arrival on the mbarrier at this offset in BOTH CTAs of the pair when every UMMA issued so far by this
+// thread has completed (a commit is a signal, not a load: the operands are never multicast).  Two separate
+// commits, one per CTA, work too but cost the pair kernels 10-40 % of their throughput.
+__device__ __forceinline__ void umma_commit_pair_both(uint32_t bar_local_addr) {
+    asm volatile(
+        "{\n"
+        ".reg .b16 m;\n"
+        "mov.b16 m, 3;\n"
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n"
+        "}\n" ::"r"(bar_local_addr)
+        : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");

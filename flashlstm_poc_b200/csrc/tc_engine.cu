@@ -182,7 +182,7 @@ int on_capacity_change(Engine &e) {
         FLSTM_TRY(make_tensor_map_2d(&t.tm_w, l.w_hh, 4 * H, H, H, 64, 64, true));
         if (st->step.use) {
             FLSTM_TRY(make_tensor_map_3d(&t.tm_hs3, l.hs, cap + 1, B, H, H, B * H, 128, 64, true));
-            FLSTM_TRY(make_tensor_map_2d(&t.tm_wstep, l.w_hh, 4 * H, H, H, st->step.bn_fwd, 64, true));
+            FLSTM_TRY(make_tensor_map_2d(&t.tm_wstep, l.w_hh, 4 * H, H, H, st->step.pair ? st->step.bn_fwd / 2 : st->step.bn_fwd, 64, true));
             FLSTM_TRY(make_tensor_map_3d_tile(&t.tm_g_ep, l.gates, 2, cap, B, 4 * H, 32, 64));
             FLSTM_TRY(make_tensor_map_3d_tile(&t.tm_c_ep, l.cs, 4, cap + 1, B, H, 32, 16));
             FLSTM_TRY(make_tensor_map_3d_tile(&t.tm_h_ep, l.hs, 2, cap + 1, B, H, 32, 16));
@@ -461,6 +461,7 @@ extern "C" int flstm_tc_plan(size_t batch, size_t hidden_size, int training, int
     out->step_bn_fwd = sp.bn_fwd;
     out->step_bn_bwd = sp.bn_bwd;
     out->step_splits = sp.splits;
+    out->step_pair = sp.pair ? 1 : 0;
     if (sp.use) return FLSTM_OK;
     tc::FwdPlan f{};
     FLSTM_TRY(tc::plan_fwd((int)batch, (int)hidden_size, sm_count, smem_limit, &f));

@@ -14,7 +14,8 @@
 // (32 KB instead of the 48 KB a lone CTA needs for 128 x 256) and the pair's UMMA reads both halves of B, so the
 // shared-memory traffic per FLOP -- what bounds the one-CTA kernel at about 2/3 of the tensor peak -- drops by a
 // third, and so does the L2 traffic.  Every CTA loads its own halves with plain TMA copies (nothing is multicast).
-// The pair kernel is used when M >= 256 and N is a multiple of 256 (FLSTM_GEMM_PAIR=0 turns it off).
+// The pair kernel is used for K-major A with K >= 2048, M >= 256 and N a multiple of 256 (FLSTM_GEMM_PAIR=0 turns it
+// off, =2 takes it whenever M >= 256 and N % 256 == 0).
 //
 // Used for (shapes at the benchmark configurations, per layer):
 //   input projection  P[T*B,4H]  = X[T*B,I] W_ih^T + b      (K-major x K-major, 16-bit out)
@@ -422,8 +423,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
     } else if (warp == 1) {
         if (leader && elect_one()) {
-            const uint32_t empty_l = smem_u32(empty), empty_p = map_to_rank(smem_u32(empty), 1);
-            const uint32_t tfull_l = smem_u32(tfull), tfull_p = map_to_rank(smem_u32(tfull), 1);
+            const uint32_t empty_l = smem_u32(empty), tfull_l = smem_u32(tfull);
             int stage = 0;
             uint32_t phase = 0;
             int it = 0;
@@ -448,13 +448,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         umma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0);
                     }
                     // the stage may be refilled in both CTAs once these UMMAs have read it
-                    umma_commit_pair(empty_l + 8u * (uint32_t)stage);
-                    umma_commit_pair(empty_p + 8u * (uint32_t)stage);
+                    umma_commit_pair_both(empty_l + 8u * (uint32_t)stage);
                     if (++stage == S::kStages) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
-                umma_commit_pair(tfull_l + 8u * (uint32_t)buf);
-                umma_commit_pair(tfull_p + 8u * (uint32_t)buf);
+                umma_commit_pair_both(tfull_l + 8u * (uint32_t)buf);
             }
         }
     } else {
@@ -538,13 +536,15 @@ struct GemmArgs {
     bool pair;  // 256 x 256 tiles on CTA pairs (gemm_pair_kernel)
 };
 
+// FLSTM_GEMM_PAIR: 0 = never, 2 = whenever the shape allows (tests), otherwise by the measured rule in gemm().
+// Read on every call, so a test can switch it inside one process.
 bool pair_enabled() {
-    static int on = -1;
-    if (on < 0) {
-        const char *env = std::getenv("FLSTM_GEMM_PAIR");
-        on = (env && env[0] == '0') ? 0 : 1;
-    }
-    return on == 1;
+    const char *env = std::getenv("FLSTM_GEMM_PAIR");
+    return !(env && env[0] == '0');
+}
+bool pair_forced() {
+    const char *env = std::getenv("FLSTM_GEMM_PAIR");
+    return env && env[0] == '2';
 }
 
 template <int BN, int MODE, bool HAS_BIAS, bool A_MN, bool B_MN, bool TMA_OUT>
@@ -643,7 +643,11 @@ int gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, 
         return set_error(FLSTM_ERR_UNSUPPORTED, "tensor-core GEMM needs 16-byte aligned operands and row pitches");
     const int BN = (N > 128) ? 256 : 128;
     GemmArgs g{};
-    g.pair = pair_enabled() && M >= 256 && N % 256 == 0 && sms >= 2;
+    // measured on B200 (bf16): pairs win for K-major A with 16-bit output from K = 2048 on (projection 1465 -> 1529,
+    // input gradient 1304 -> 1451 TFLOP/s, 8192^3 1159 -> 1377); with short K the 256-wide epilogue of both CTAs is
+    // the bottleneck (K = 1024: 1218 -> 753) and the MN-major weight-gradient form does not gain (1367 -> 1230)
+    g.pair = pair_enabled() && !a_mn && K >= 2048 && M >= 256 && N % 256 == 0 && sms >= 2;
+    if (pair_forced()) g.pair = M >= 256 && N % 256 == 0 && sms >= 2;
     // K-major: (rows, K) with K contiguous, box rows x 64.  MN-major: stored (K, rows), 64 x 64 boxes.
     if (!a_mn) FLSTM_TRY(make_tensor_map_2d(&g.ta, A, M, K, lda, BM, BK, true));
     else FLSTM_TRY(make_tensor_map_2d(&g.ta, A, K, M, lda, BK, 64, true));

@@ -110,6 +110,7 @@ struct StepPlan {
     int bn_fwd;   // output-tile width of the forward step GEMM (gate columns): 128 or 256
     int bn_bwd;   // output-tile width of the backward step GEMM (hidden units): 128 or 256
     int splits;   // K = 4H splits of the backward step GEMM (fp32 partial sums, added by the pointwise kernel)
+    bool pair;    // tiles of 256 sequences on CTA pairs (cta_group::2); the forward W_hh map then has bn_fwd / 2 rows per box
 };
 
 struct StepFwdParams {
@@ -120,7 +121,7 @@ struct StepFwdParams {
 };
 
 // Tensor maps of the forward step kernel.  Operands: hs (T+1, B, H) as a 3-D map with 1 x 128 x 64 boxes and
-// W_hh (rows tile-interleaved, (4H, H)) with plan.bn_fwd x 64 boxes, both 128B-swizzled.  Epilogue tiles
+// W_hh (rows tile-interleaved, (4H, H)) with plan.bn_fwd x 64 boxes (plan.bn_fwd / 2 x 64 for CTA pairs), both 128B-swizzled.  Epilogue tiles
 // (make_tensor_map_3d_tile, 32-row boxes): gates (T, B, 4H) 64 columns wide, cs (T+1, B, H) fp32 16 wide,
 // hs_out (T+1, B, H) 16 wide, y = the caller's (T, B, H) output 16 wide or null.
 struct StepFwdMaps {

@@ -401,8 +401,10 @@ int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan) {
     while (R / rt > sms || R % rt) ++rt;
     const int cta_rows = R / rt;
     // 32 sequences per batch tile while every batch group then gets its own set of CTAs; when the row tiles
-    // alone fill the machine (H >= 2048) a CTA would take two 32-wide tiles per step and stream its W_hh slice
-    // twice, so 33..64 sequences become ONE 64-wide tile (the UMMA costs the same at N = 32 and N = 64)
+    // alone fill the machine (H = 2048) a CTA would take two 32-wide tiles per step and stream its W_hh slice
+    // twice, so 33..64 sequences become ONE 64-wide tile (the UMMA costs the same at N = 32 and N = 64).
+    // Measured at B = 64, H = 2048, L = 2, T = 1024 (fwd+bwd): 46.5 ms against 55.6 ms on the per-step path.  With
+    // two row tiles per CTA (H = 4096) the per-step path stays ahead (75.6 against 88.6 ms), so the rule stops there.
     int BT = (B >= 128) ? 64 : 32;
     int tiles = 0, ngroups = 0, nt = 0;
     auto split = [&](int bt) {
@@ -414,7 +416,7 @@ int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan) {
         ngroups = (tiles + nt - 1) / nt;
     };
     split(BT);
-    if (BT == 32 && nt == 2 && 2 * cta_rows > sms && wide_tile_enabled()) {
+    if (BT == 32 && nt == 2 && rt == 1 && 2 * cta_rows > sms && wide_tile_enabled()) {
         split(64);
         if (nt == 1) BT = 64;
         else split(32);

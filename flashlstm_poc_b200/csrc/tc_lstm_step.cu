@@ -43,13 +43,17 @@ enum Epilogue { EPI_LSTM_FWD = 0, EPI_F32_PARTS = 1 };
 constexpr int kEpiPBytes = 32 * 128, kEpiCBytes = 32 * 64, kEpiHBytes = 32 * 32;
 constexpr int kEpiWarpBytes = 2 * kEpiPBytes + 2 * kEpiCBytes + kEpiHBytes;  // 13312, a multiple of 1024
 
-template <int BN, int EPI>
+// PAIR: a cluster of two CTAs works on a 256 x BN tile (tcgen05 cta_group::2): each CTA stages 128 rows of A and
+// BN / 2 rows of B per K block and gets its own 128 accumulator rows, so the shared-memory traffic per FLOP -- what
+// bounds the lone-CTA 128 x 128 tile at half of the tensor rate -- drops by a quarter (BN = 128) or a third (256).
+template <int BN, int EPI, bool PAIR>
 struct StepShape {
-    static constexpr int kStages = (EPI == EPI_LSTM_FWD) ? ((BN == 256) ? 3 : 5) : ((BN == 256) ? 4 : 6);
     static constexpr int kABytes = BM * BK * 2;
-    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kBBytes = (PAIR ? BN / 2 : BN) * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kEpiBytes = (EPI == EPI_LSTM_FWD) ? 4 * kEpiWarpBytes : 0;
+    static constexpr int kStages = PAIR ? ((227 * 1024 - kEpiBytes - 2048) / kStageBytes > 8 ? 8 : (227 * 1024 - kEpiBytes - 2048) / kStageBytes)
+                                        : ((EPI == EPI_LSTM_FWD) ? ((BN == 256) ? 3 : 5) : ((BN == 256) ? 4 : 6));
     static constexpr int kTmemCols = 2 * BN;
     static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
@@ -82,18 +86,31 @@ bool pdl_enabled() {
     return on == 1;
 }
 
+// `cluster` > 1 launches the grid as clusters of that many CTAs (the CTA pairs of cta_group::2).
 template <typename... KArgs, typename... Args>
-cudaError_t launch_chained(void (*kern)(KArgs...), int grid, int block, size_t smem, cudaStream_t s, Args &&...args) {
+cudaError_t launch_chained(void (*kern)(KArgs...), int grid, int block, size_t smem, cudaStream_t s, int cluster,
+                           Args &&...args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(block);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (pdl_enabled()) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (cluster > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = cluster;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = na;
     return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
 }
 
@@ -168,12 +185,14 @@ __device__ __forceinline__ void lstm_cell_16(const uint32_t (&acc)[64], uint8_t 
 // (forward: W_hh rows = gate columns) or MN-major, stored (K, N), 64 x 64 boxes (backward: W_hh as stored).
 // Forward epilogue maps (make_tensor_map_3d_tile, 32-row boxes): tm_g gates (T,B,4H) 64 columns wide, tm_c cell
 // states (T+1,B,H) fp32 16 wide, tm_h hidden states (T+1,B,H) 16 wide, tm_y the caller's y (T,B,H) 16 wide.
-template <int BN, int EPI, bool B_MN, bool BF16>
+template <int BN, int EPI, bool B_MN, bool BF16, bool PAIR>
 __global__ void __launch_bounds__(kStepThreads, 1)
 step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_c,
             const __grid_constant__ CUtensorMap tm_h, const __grid_constant__ CUtensorMap tm_y, const StepArgs a) {
-    using S = StepShape<BN, EPI>;
+    using S = StepShape<BN, EPI, PAIR>;
+    constexpr int BNB = PAIR ? BN / 2 : BN;  // rows of B this CTA stages per K block
+    constexpr int BMT = PAIR ? 2 * BM : BM;  // rows of a tile (both CTAs of a pair)
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *epi = smem + S::kStages * S::kStageBytes;  // 1024-aligned: stage sizes are multiples of 1024
@@ -185,6 +204,10 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     volatile uint32_t *abort_w = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    const bool leader = rank == 0;
+    // tiles are dealt to CTAs (lone) or to CTA pairs
+    const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     // The next kernel of the chain may be scheduled as soon as CTAs of this grid retire (it is never
     // co-resident with one: both need most of the SM's shared memory); it still waits for this whole grid.
     grid_launch_dependents();
@@ -195,7 +218,7 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&tfull[i], 1);
-            mbar_init(&tempty[i], 4);
+            mbar_init(&tempty[i], PAIR ? 8 : 4);  // PAIR: the leader's barrier takes both CTAs' epilogue warps
         }
         for (int i = 0; i < 8; ++i) mbar_init(&ldbars[i], 1);
         *abort_w = 0;
@@ -209,18 +232,24 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, S::kTmemCols);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(tmem_slot, S::kTmemCols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, S::kTmemCols);
+            tmem_relinquish();
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();  // both CTAs' barriers and tensor memory exist before anything crosses the pair
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     // Launched with programmatic stream serialization: everything above overlapped the tail of the previous
     // step's kernel; its results (h, c, dG, partial sums) may be touched only from here on.
     grid_dependency_wait();
 
-    const int num_m = (a.M + BM - 1) / BM, num_n = a.N / BN;
+    const int num_m = (a.M + BMT - 1) / BMT, num_n = a.N / BN;
     const int kblocks = a.K / BK, kper = kblocks / a.splits;
     const int tiles = num_m * num_n * a.splits;
     // tile -> (split, m, n): n fastest, so CTAs that run together share the A tile in L2
@@ -229,21 +258,35 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         if (elect_one()) {
             int stage = 0;
             uint32_t phase = 0;
-            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+            const uint32_t full0 = PAIR ? map_to_rank(smem_u32(full), 0) : 0u;  // the leader's "operands landed" barriers
+            for (int tile = worker; tile < tiles; tile += workers) {
                 const int ks = tile / (num_m * num_n), mn = tile % (num_m * num_n);
-                const int m0 = (mn / num_n) * BM, n0 = (mn % num_n) * BN;
+                const int m0 = (mn / num_n) * BMT + (int)rank * BM, n0 = (mn % num_n) * BN + (int)rank * BNB;
                 bool ok = true;
                 for (int kb = ks * kper; kb < (ks + 1) * kper && ok; ++kb) {
                     ok = mbar_wait(&empty[stage], phase ^ 1, abort_w);
                     if (!ok) break;
                     uint8_t *sa = smem + stage * S::kStageBytes, *sb = sa + S::kABytes;
-                    mbar_expect_tx(&full[stage], S::kStageBytes);
-                    tma_load_3d(sa, &tm_a, kb * BK, m0, a.a_z, &full[stage]);
-                    if (!B_MN) {
-                        tma_load_2d(sb, &tm_b, kb * BK, n0, &full[stage]);
-                    } else {
+                    if (PAIR) {
+                        // each CTA fetches its own halves; the bytes of both are counted on the leader's barrier
+                        const uint32_t bar = full0 + 8u * (uint32_t)stage;
+                        if (leader) mbar_expect_tx(&full[stage], 2 * S::kStageBytes);
+                        tma_load_3d_pair(sa, &tm_a, kb * BK, m0, a.a_z, bar);
+                        if (!B_MN) {
+                            tma_load_2d_pair(sb, &tm_b, kb * BK, n0, bar);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tm_b, n0 + j * 64, kb * BK, &full[stage]);
+                            for (int j = 0; j < BNB / 64; ++j) tma_load_2d_pair(sb + j * 8192, &tm_b, n0 + j * 64, kb * BK, bar);
+                        }
+                    } else {
+                        mbar_expect_tx(&full[stage], S::kStageBytes);
+                        tma_load_3d(sa, &tm_a, kb * BK, m0, a.a_z, &full[stage]);
+                        if (!B_MN) {
+                            tma_load_2d(sb, &tm_b, kb * BK, n0, &full[stage]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tm_b, n0 + j * 64, kb * BK, &full[stage]);
+                        }
                     }
                     if (++stage == S::kStages) { stage = 0; phase ^= 1; }
                 }
@@ -251,14 +294,15 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             }
         }
     } else if (warp == 1) {
-        if (elect_one()) {
+        if (leader && elect_one()) {  // in a pair only the leader issues UMMAs; they write both CTAs' accumulators
+            const uint32_t empty_l = smem_u32(empty), tfull_l = smem_u32(tfull);
             int stage = 0;
             uint32_t phase = 0;
             int it = 0;
-            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+            for (int tile = worker; tile < tiles; tile += workers, ++it) {
                 const int buf = it & 1;
                 const uint32_t bphase = (it >> 1) & 1;
-                if (!mbar_wait(&tempty[buf], bphase ^ 1, abort_w)) break;
+                if (!(PAIR ? mbar_wait_cluster(&tempty[buf], bphase ^ 1, abort_w) : mbar_wait(&tempty[buf], bphase ^ 1, abort_w))) break;
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 bool ok = true;
@@ -272,17 +316,32 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         const uint64_t da = umma_desc_kmajor_sw128(a_base + k * 32);
                         const uint64_t db = B_MN ? umma_desc_mnmajor_sw128(b_base + k * 2048, 8192)
                                                  : umma_desc_kmajor_sw128(b_base + k * 32);
-                        umma_f16(d_tmem, da, db, a.idesc, (kb | k) != 0);
+                        if (PAIR) umma_f16_pair(d_tmem, da, db, a.idesc, (kb | k) != 0);
+                        else umma_f16(d_tmem, da, db, a.idesc, (kb | k) != 0);
                     }
-                    umma_commit(&empty[stage]);
+                    if (PAIR) {  // the stage may be refilled in both CTAs once these UMMAs have read it
+                        umma_commit_pair_both(empty_l + 8u * (uint32_t)stage);
+                    } else {
+                        umma_commit(&empty[stage]);
+                    }
                     if (++stage == S::kStages) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
-                umma_commit(&tfull[buf]);
+                if (PAIR) {
+                    umma_commit_pair_both(tfull_l + 8u * (uint32_t)buf);
+                } else {
+                    umma_commit(&tfull[buf]);
+                }
             }
         }
     } else {
         const int q = warp & 3;  // TMEM lane quadrant this warp may access
+        const uint32_t tempty0 = PAIR ? map_to_rank(smem_u32(tempty), 0) : 0u;
+        // this warp is done with accumulator `b`: tell the UMMA issuer (in a pair: the leader's barrier)
+        auto release_accumulator = [&](int b) {
+            if (PAIR) mbar_arrive_cluster(tempty0 + 8u * (uint32_t)b);
+            else mbar_arrive(&tempty[b]);
+        };
         if (EPI == EPI_LSTM_FWD) {
             // Items = (tile, 64-column unit group) pairs in order.  Lane 0 keeps the loads of the next item in
             // flight while the warp works on the current one; outputs leave through TMA stores from the same tiles.
@@ -290,11 +349,11 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             uint8_t *wb = epi + q * kEpiWarpBytes;
             uint8_t *sH = wb + 2 * kEpiPBytes + 2 * kEpiCBytes;
             uint64_t *ldbar = ldbars + q * 2;
-            const int my_tiles = (tiles > (int)blockIdx.x) ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+            const int my_tiles = (tiles > worker) ? (tiles - worker + workers - 1) / workers : 0;
             const int items = my_tiles * kGroups;
             auto item_coords = [&](int idx, int &row0, int &col0) {
-                const int tl = blockIdx.x + (idx / kGroups) * gridDim.x;
-                row0 = (tl / num_n) * BM + q * 32;
+                const int tl = worker + (idx / kGroups) * workers;
+                row0 = (tl / num_n) * BMT + (int)rank * BM + q * 32;
                 col0 = (tl % num_n) * BN + (idx % kGroups) * 64;
             };
             auto issue_loads = [&](int idx) {  // one lane
@@ -310,7 +369,7 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             uint32_t ldphase = 0;  // bit b: parity of the next completion of ldbar[b]
             int item = 0, it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++it) {
+            for (int tile = worker; tile < tiles && ok; tile += workers, ++it) {
                 const int tbuf = it & 1;
                 if (!mbar_wait(&tfull[tbuf], (it >> 1) & 1, abort_w)) break;
                 tcgen05_fence_after();
@@ -332,7 +391,7 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     if (g == kGroups - 1) {  // the accumulator is in registers: hand it back to the UMMA warp
                         tcgen05_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(&tempty[tbuf]);
+                        if (lane == 0) release_accumulator(tbuf);
                     }
                     if (row0 >= a.M) continue;
                     ok = mbar_wait(&ldbar[buf], (ldphase >> buf) & 1u, abort_w);
@@ -354,10 +413,10 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             if (lane == 0) tma_store_wait_all<0>();
         } else {
             int it = 0;
-            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+            for (int tile = worker; tile < tiles; tile += workers, ++it) {
                 const int buf = it & 1;
                 const int ks = tile / (num_m * num_n), mn = tile % (num_m * num_n);
-                const int m0 = (mn / num_n) * BM, n0 = (mn % num_n) * BN;
+                const int m0 = (mn / num_n) * BMT + (int)rank * BM, n0 = (mn % num_n) * BN;
                 if (!mbar_wait(&tfull[buf], (it >> 1) & 1, abort_w)) break;
                 tcgen05_fence_after();
                 const int row = m0 + q * 32 + lane;  // sequence index
@@ -378,13 +437,18 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
                 tcgen05_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&tempty[buf]);
+                if (lane == 0) release_accumulator(buf);
             }
         }
     }
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, S::kTmemCols);
+    if (PAIR) {
+        cluster_sync_all();  // the peer's shared and tensor memory stay valid until the leader's last UMMA is consumed
+        if (warp == 1) tmem_dealloc_pair(tmem_base, S::kTmemCols);
+    } else if (warp == 1) {
+        tmem_dealloc(tmem_base, S::kTmemCols);
+    }
     if (threadIdx.x == 0 && *abort_w) atomicExch(a.err, 1u);
 }
 
@@ -459,26 +523,49 @@ struct EpilogueMaps {
     const CUtensorMap *g, *c, *h, *y;
 };
 
-template <int BN, int EPI, bool B_MN, bool BF16>
-int launch_step(const CUtensorMap &ta, const CUtensorMap &tb, const EpilogueMaps &em, const StepArgs &a, int sms,
-                cudaStream_t s) {
-    using S = StepShape<BN, EPI>;
-    auto kern = step_kernel<BN, EPI, B_MN, BF16>;
+template <int BN, int EPI, bool B_MN, bool BF16, bool PAIR>
+int launch_step_one(const CUtensorMap &ta, const CUtensorMap &tb, const EpilogueMaps &em, const StepArgs &a, int sms,
+                    cudaStream_t s) {
+    using S = StepShape<BN, EPI, PAIR>;
+    auto kern = step_kernel<BN, EPI, B_MN, BF16, PAIR>;
     FLSTM_CUDA_TRY(ensure_smem_limit(kern, (size_t)S::kSmemBytes));
-    const int tiles = ((a.M + BM - 1) / BM) * (a.N / BN) * a.splits;
-    const int grid = tiles < sms ? tiles : sms;
-    cudaError_t e = launch_chained(kern, grid, kStepThreads, S::kSmemBytes, s, ta, tb, *em.g, *em.c, *em.h, *em.y, a);
+    const int rows = PAIR ? 2 * BM : BM;
+    const int tiles = ((a.M + rows - 1) / rows) * (a.N / BN) * a.splits;
+    const int workers = PAIR ? sms / 2 : sms;
+    const int grid = (tiles < workers ? tiles : workers) * (PAIR ? 2 : 1);
+    cudaError_t e = launch_chained(kern, grid, kStepThreads, S::kSmemBytes, s, PAIR ? 2 : 1, ta, tb, *em.g, *em.c, *em.h,
+                                   *em.y, a);
     if (e != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "step kernel launch failed: %s", cudaGetErrorString(e));
     return FLSTM_OK;
 }
 
+template <int BN, int EPI, bool B_MN, bool BF16>
+int launch_step(bool pair, const CUtensorMap &ta, const CUtensorMap &tb, const EpilogueMaps &em, const StepArgs &a, int sms,
+                cudaStream_t s) {
+    return pair ? launch_step_one<BN, EPI, B_MN, BF16, true>(ta, tb, em, a, sms, s)
+                : launch_step_one<BN, EPI, B_MN, BF16, false>(ta, tb, em, a, sms, s);
+}
+
 // Cost model for the tile width: rounds of the persistent tile loop times the shared-memory-bound
-// cost of one K step (a 128 x BN x 16 UMMA reads 4 KB + BN*32 B of operands).
-int pick_bn(int m_tiles, int N, int splits, int sms) {
+// cost of one K step (a 128 x BN x 16 UMMA reads 4 KB + BN*32 B of operands).  For CTA pairs (m_tiles counts
+// 256-row tiles, sms / 2 workers) a K block of a 256 x 128 tile costs 3/8 and of a 256 x 256 tile 4/8 of what a
+// lone 128 x 256 tile costs: each CTA stages 24 KB resp. 32 KB instead of 48 KB.
+int pick_bn(int m_tiles, int N, int splits, int sms, bool pair = false) {
     if (N % 256) return 128;
+    const int workers = pair ? sms / 2 : sms;
     const int t128 = m_tiles * (N / 128) * splits, t256 = m_tiles * (N / 256) * splits;
-    const int cost128 = ((t128 + sms - 1) / sms) * 2, cost256 = ((t256 + sms - 1) / sms) * 3;
+    const int cost128 = ((t128 + workers - 1) / workers) * (pair ? 3 : 2), cost256 = ((t256 + workers - 1) / workers) * (pair ? 4 : 3);
     return cost256 < cost128 ? 256 : 128;
+}
+
+// FLSTM_STEP_PAIR=1 turns the CTA-pair tiles on (off by default until measured)
+bool step_pair_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char *env = std::getenv("FLSTM_STEP_PAIR");
+        on = (env && env[0] == '1') ? 1 : 0;
+    }
+    return on == 1;
 }
 
 }  // namespace
@@ -498,15 +585,24 @@ int plan_step(int B, int H, int sms, size_t smem_limit, StepPlan *plan) {
         use = plan_fwd(B, H, sms, smem_limit, &fp) != FLSTM_OK || fp.nt > 1;
     }
     plan->use = use && H % 128 == 0;  // the backward tiles are 128 or 256 units wide
-    const int m_tiles = (B + BM - 1) / BM;
-    plan->bn_fwd = pick_bn(m_tiles, 4 * H, 1, sms);
+    // from 256 sequences on a tile is 256 rows on a CTA pair (cta_group::2)
+    plan->pair = B >= 2 * BM && sms >= 2 && step_pair_enabled();
+    const int rows = plan->pair ? 2 * BM : BM, workers = plan->pair ? sms / 2 : sms;
+    const int m_tiles = (B + rows - 1) / rows;
+    plan->bn_fwd = pick_bn(m_tiles, 4 * H, 1, sms, plan->pair);
     // backward: K = 4H is long and N = H short; split K until the tiles fill the machine
     int splits = 1;
-    while (splits < 8 && m_tiles * (H / 128) * splits * 2 <= sms && ((4 * H / BK) % (splits * 2)) == 0) splits *= 2;
+    while (splits < 8 && m_tiles * (H / 128) * splits * 2 <= workers && ((4 * H / BK) % (splits * 2)) == 0) splits *= 2;
     plan->splits = splits;
-    plan->bn_bwd = pick_bn(m_tiles, H, splits, sms);
-    const size_t need_fwd = plan->bn_fwd == 256 ? StepShape<256, EPI_LSTM_FWD>::kSmemBytes : StepShape<128, EPI_LSTM_FWD>::kSmemBytes;
-    const size_t need_bwd = plan->bn_bwd == 256 ? StepShape<256, EPI_F32_PARTS>::kSmemBytes : StepShape<128, EPI_F32_PARTS>::kSmemBytes;
+    plan->bn_bwd = pick_bn(m_tiles, H, splits, sms, plan->pair);
+    size_t need_fwd, need_bwd;
+    if (plan->pair) {
+        need_fwd = plan->bn_fwd == 256 ? StepShape<256, EPI_LSTM_FWD, true>::kSmemBytes : StepShape<128, EPI_LSTM_FWD, true>::kSmemBytes;
+        need_bwd = plan->bn_bwd == 256 ? StepShape<256, EPI_F32_PARTS, true>::kSmemBytes : StepShape<128, EPI_F32_PARTS, true>::kSmemBytes;
+    } else {
+        need_fwd = plan->bn_fwd == 256 ? StepShape<256, EPI_LSTM_FWD, false>::kSmemBytes : StepShape<128, EPI_LSTM_FWD, false>::kSmemBytes;
+        need_bwd = plan->bn_bwd == 256 ? StepShape<256, EPI_F32_PARTS, false>::kSmemBytes : StepShape<128, EPI_F32_PARTS, false>::kSmemBytes;
+    }
     if (need_fwd > smem_limit || need_bwd > smem_limit) plan->use = false;  // the step kernels do not fit this device
     return FLSTM_OK;
 }
@@ -520,17 +616,17 @@ int lstm_step_forward(int dtype, const StepPlan &plan, const StepFwdMaps &m, con
     a.K = p.H;
     a.a_z = p.t;
     a.splits = 1;
-    a.idesc = umma_idesc_f16(BM, plan.bn_fwd, bf16 ? 1 : 0, 0, 0);
+    a.idesc = umma_idesc_f16(plan.pair ? 2 * BM : BM, plan.bn_fwd, bf16 ? 1 : 0, 0, 0);
     a.err = p.err;
     a.t = p.t;
     a.has_y = m.y ? 1 : 0;
     a.store_gates = p.store_gates;
     const EpilogueMaps em{m.gates, m.cs, m.hs_out, m.y ? m.y : m.hs_out};
     if (plan.bn_fwd == 256)
-        return bf16 ? launch_step<256, EPI_LSTM_FWD, false, true>(*m.hs, *m.w, em, a, sms, s)
-                    : launch_step<256, EPI_LSTM_FWD, false, false>(*m.hs, *m.w, em, a, sms, s);
-    return bf16 ? launch_step<128, EPI_LSTM_FWD, false, true>(*m.hs, *m.w, em, a, sms, s)
-                : launch_step<128, EPI_LSTM_FWD, false, false>(*m.hs, *m.w, em, a, sms, s);
+        return bf16 ? launch_step<256, EPI_LSTM_FWD, false, true>(plan.pair, *m.hs, *m.w, em, a, sms, s)
+                    : launch_step<256, EPI_LSTM_FWD, false, false>(plan.pair, *m.hs, *m.w, em, a, sms, s);
+    return bf16 ? launch_step<128, EPI_LSTM_FWD, false, true>(plan.pair, *m.hs, *m.w, em, a, sms, s)
+                : launch_step<128, EPI_LSTM_FWD, false, false>(plan.pair, *m.hs, *m.w, em, a, sms, s);
 }
 
 int lstm_step_backward_gemm(int dtype, const StepPlan &plan, const CUtensorMap &tm_dg, const CUtensorMap &tm_w64, int t,
@@ -542,12 +638,12 @@ int lstm_step_backward_gemm(int dtype, const StepPlan &plan, const CUtensorMap &
     a.K = 4 * H;
     a.a_z = t;
     a.splits = plan.splits;
-    a.idesc = umma_idesc_f16(BM, plan.bn_bwd, bf16 ? 1 : 0, 0, 1);
+    a.idesc = umma_idesc_f16(plan.pair ? 2 * BM : BM, plan.bn_bwd, bf16 ? 1 : 0, 0, 1);
     a.err = err;
     a.parts = parts;
     const EpilogueMaps em{&tm_dg, &tm_dg, &tm_dg, &tm_dg};  // unused by this epilogue
-    if (plan.bn_bwd == 256) return launch_step<256, EPI_F32_PARTS, true, false>(tm_dg, tm_w64, em, a, sms, s);
-    return launch_step<128, EPI_F32_PARTS, true, false>(tm_dg, tm_w64, em, a, sms, s);
+    if (plan.bn_bwd == 256) return launch_step<256, EPI_F32_PARTS, true, false>(plan.pair, tm_dg, tm_w64, em, a, sms, s);
+    return launch_step<128, EPI_F32_PARTS, true, false>(plan.pair, tm_dg, tm_w64, em, a, sms, s);
 }
 
 int lstm_step_backward_pointwise(int dtype, const void *gates_t, const float *c_t, const float *c_prev, const void *dy_t,
@@ -558,8 +654,8 @@ int lstm_step_backward_pointwise(int dtype, const void *gates_t, const float *c_
     const uint16_t *g16 = static_cast<const uint16_t *>(gates_t), *dy16 = static_cast<const uint16_t *>(dy_t);
     uint16_t *dg16 = static_cast<uint16_t *>(dg_t);
     cudaError_t e = dtype == FLSTM_DTYPE_BF16
-                        ? launch_chained(step_bwd_pointwise_kernel<true>, grid, 256, 0, s, g16, c_t, c_prev, dy16, parts, nparts, dc, dg16, B, H)
-                        : launch_chained(step_bwd_pointwise_kernel<false>, grid, 256, 0, s, g16, c_t, c_prev, dy16, parts, nparts, dc, dg16, B, H);
+                        ? launch_chained(step_bwd_pointwise_kernel<true>, grid, 256, 0, s, 1, g16, c_t, c_prev, dy16, parts, nparts, dc, dg16, B, H)
+                        : launch_chained(step_bwd_pointwise_kernel<false>, grid, 256, 0, s, 1, g16, c_t, c_prev, dy16, parts, nparts, dc, dg16, B, H);
     if (e != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "step pointwise launch failed: %s", cudaGetErrorString(e));
     return FLSTM_OK;
 }

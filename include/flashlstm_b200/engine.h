@@ -203,6 +203,7 @@ typedef struct {
     int bwd_stages, bwd_chunks_per_stage, bwd_weights_resident, bwd_smem_bytes;
     /* wide batches run one GEMM launch per time step instead (then the fields above are zero) */
     int step_path, step_bn_fwd, step_bn_bwd, step_splits;
+    int step_pair; /* the per-step GEMMs run on CTA pairs (256-sequence tiles, tcgen05 cta_group::2) */
 } flstm_tc_plan_info;
 int flstm_tc_plan(size_t batch, size_t hidden_size, int training, int sm_count, size_t smem_limit,
                   flstm_tc_plan_info *out);

@@ -4,7 +4,7 @@ Sequences are independent across the batch in the forward pass and in dx / dh0 /
 BF16 configurations the CPU oracle is run on a few rows of the batch only (seconds instead of minutes) and
 compared with the same rows of the engine's full-size run.  Weight and bias gradients sum over time and batch:
 they are checked at full sequence length, width and depth on a reduced batch (16 sequences through the
-persistent kernels, 64 / 160 through the per-step path), which is where 16-bit dG summed over a thousand
+persistent kernels with 32- and 64-wide batch tiles, 160 through the per-step path), which is where 16-bit dG summed over a thousand
 time steps could drift."""
 import numpy as np
 import pytest
@@ -80,7 +80,7 @@ def test_config4_full_size_inference_slice():
 
 @pytest.mark.parametrize("name,batch,path", [
     ("c3_bf16_l2_h2048", 16, "persistent"), ("c5_bf16_l4_h1024", 16, "persistent"),
-    ("c3_bf16_l2_h2048", 64, "step"), ("c5_bf16_l4_h1024", 160, "step"),
+    ("c3_bf16_l2_h2048", 64, "persistent"), ("c5_bf16_l4_h1024", 160, "step"),
 ])
 def test_bf16_configs_full_length_reduced_batch_all_outputs(name, batch, path):
     """Configurations 3 and 5 at their own T, I, H and L with a reduced batch: EVERY output, including dW_ih,
