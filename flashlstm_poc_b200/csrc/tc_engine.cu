@@ -239,6 +239,26 @@ int forward_layer(Engine &e, int li, size_t t0, size_t t1, const void *x_l, void
         CUtensorMap tm_y;
         if (y_out) FLSTM_TRY(make_tensor_map_3d_tile(&tm_y, y_out, 2, t1, B, H, 32, 16));
         const StepFwdMaps maps{&t.tm_hs3, &t.tm_wstep, &t.tm_g_ep, &t.tm_c_ep, &t.tm_h_ep, y_out ? &tm_y : nullptr};
+        if (st->step.fwd_persistent) {
+            FLSTM_CUDA_TRY(cudaMemsetAsync(e.sync_words + 1, 0, sizeof(unsigned int), s));
+            WideFwdParams wp{};
+            wp.err = err;
+            wp.counter = e.sync_words + 1;
+            wp.t0 = (int)t0;
+            wp.nsteps = (int)n;
+            wp.B = (int)B;
+            wp.H = (int)H;
+            wp.store_gates = (e.cfg.training && e.seg.keep_gates) ? 1 : 0;
+            wp.wait_ns = e.wait_limit_ns;
+            wp.extra_arrivals = e.selftest_missing_arrivals;
+            FLSTM_TRY(lstm_wide_forward(e.cfg.dtype, st->step, maps, wp, st->sms, s));
+            size_t m2 = e.timer.mark(s);
+            e.timer.span(PH_PROJ, m0, m1);
+            e.timer.span(PH_RECUR_FWD, m1, m2);
+            e.launches += 2;
+            FLSTM_CUDA_TRY(cudaMemcpyAsync(st->err_host, err, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
+            return FLSTM_OK;
+        }
         for (size_t step = t0; step < t1; ++step) {
             StepFwdParams sp{};
             sp.err = err;

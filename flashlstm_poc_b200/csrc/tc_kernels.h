@@ -111,6 +111,7 @@ struct StepPlan {
     int bn_bwd;   // output-tile width of the backward step GEMM (hidden units): 128 or 256
     int splits;   // K = 4H splits of the backward step GEMM (fp32 partial sums, added by the pointwise kernel)
     bool pair;    // tiles of 256 sequences on CTA pairs (cta_group::2); the forward W_hh map then has bn_fwd / 2 rows per box
+    bool fwd_persistent;  // forward: one cooperative launch per range of steps (lstm_wide_forward) instead of one per step
 };
 
 struct StepFwdParams {
@@ -127,6 +128,19 @@ struct StepFwdParams {
 struct StepFwdMaps {
     const CUtensorMap *hs, *w, *gates, *cs, *hs_out, *y;
 };
+
+// All steps [t0, t0 + nsteps) of the forward step GEMM in ONE cooperative launch: the CTAs keep their output tiles,
+// a counter barrier in global memory separates the steps (same tensor maps as lstm_step_forward).
+struct WideFwdParams {
+    unsigned int *err;
+    unsigned int *counter;  // zeroed before the launch
+    int t0, nsteps;
+    int B, H;
+    int store_gates;
+    unsigned long long wait_ns;
+    unsigned int extra_arrivals;
+};
+int lstm_wide_forward(int dtype, const StepPlan &plan, const StepFwdMaps &m, const WideFwdParams &p, int sms, cudaStream_t s);
 
 int plan_step(int B, int H, int sms, size_t smem_limit, StepPlan *plan);
 int lstm_step_forward(int dtype, const StepPlan &plan, const StepFwdMaps &m, const StepFwdParams &p, int sms,

@@ -26,6 +26,7 @@
 #include "common.cuh"
 #include "tc_common.cuh"
 #include "tc_kernels.h"
+#include "tc_recurrent.cuh"
 
 namespace flstm_b200 {
 namespace tc {
@@ -452,6 +453,269 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     if (threadIdx.x == 0 && *abort_w) atomicExch(a.err, 1u);
 }
 
+// ------------------------------------------------------------------ all time steps in one launch
+// The forward step GEMM as a persistent kernel: ONE cooperative launch runs the steps [t0, t0 + nsteps) of a layer.
+// A kernel boundary per step costs more than the step's UMMAs (the per-step launches spend two thirds of their
+// time on dependency resolution, pipeline fill and drain); here a CTA keeps its output tiles for the whole range,
+// the steps are separated by a counter barrier in global memory (release add by every CTA once its h_t tiles
+// are stored, acquire poll by the producers), and what does not depend on the recurrence is fetched ahead of
+// the barrier: the W_hh blocks of the first ring stages and the projection / cell-state tiles of the epilogue.
+//   warp 0   producer: per step, W_hh blocks for the free stages -> wait for h_{t-1} -> h blocks -> the rest
+//   warp 1   UMMA issuer (as in step_kernel), warps 2-5 fused LSTM epilogue (as in step_kernel)
+// Every wait is bounded; the four epilogue warps agree on failure at the named barrier that precedes the
+// release (barrier.cta.red.or), so none of them is left behind.
+struct WideFwdArgs {
+    int M, N, K;       // batch, 4H, H
+    int t0, nsteps;    // first absolute time step and number of steps of this launch
+    uint32_t idesc;
+    unsigned int *err;
+    unsigned int *counter;        // step barrier, zeroed before the launch
+    int has_y, store_gates;
+    unsigned long long wait_ns;   // limit of every wait (0 = the 2 s default)
+    unsigned int extra_arrivals;  // self-test of the timeout path: arrivals nobody makes
+};
+
+template <int BN, bool BF16>
+__global__ void __launch_bounds__(kStepThreads, 1)
+wide_fwd_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_c,
+                const __grid_constant__ CUtensorMap tm_h, const __grid_constant__ CUtensorMap tm_y, const WideFwdArgs a) {
+    using S = StepShape<BN, EPI_LSTM_FWD, false>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *epi = smem + S::kStages * S::kStageBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(epi + S::kEpiBytes);
+    uint64_t *full = bars, *empty = bars + S::kStages;
+    uint64_t *tfull = bars + 2 * S::kStages, *tempty = tfull + 2;
+    uint64_t *ldbars = tempty + 2;  // 2 per epilogue warp
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(ldbars + 8);
+    volatile uint32_t *abort_w = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned long long wait_ns = a.wait_ns ? a.wait_ns : kWaitLimitNs;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < S::kStages; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&tfull[i], 1);
+            mbar_init(&tempty[i], 4);
+        }
+        for (int i = 0; i < 8; ++i) mbar_init(&ldbars[i], 1);
+        *abort_w = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tm_a);
+        tma_prefetch_desc(&tm_b);
+        tma_prefetch_desc(&tm_g);
+        tma_prefetch_desc(&tm_c);
+        tma_prefetch_desc(&tm_h);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, S::kTmemCols);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_m = (a.M + BM - 1) / BM, num_n = a.N / BN;
+    const int tiles = num_m * num_n, kblocks = a.K / BK;
+    const int my_tiles = (tiles > (int)blockIdx.x) ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    // k-blocks a CTA streams per step, in order: tile after tile
+    const int blocks_per_step = my_tiles * kblocks;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t issued = 0, parity = 0;  // the last copy started into every stage (drained on the way out)
+            bool ok = true;
+            auto coords = [&](int blk, int &m0, int &n0, int &kb) {
+                const int tile = blockIdx.x + (blk / kblocks) * gridDim.x;
+                m0 = (tile / num_n) * BM;
+                n0 = (tile % num_n) * BN;
+                kb = blk % kblocks;
+            };
+            for (int tt = 0; tt < a.nsteps && ok; ++tt) {
+                const int t = a.t0 + tt;
+                // 1. W_hh blocks of as many k-blocks as the ring takes, before h_{t-1} is known to be complete
+                const int npre = blocks_per_step < S::kStages ? blocks_per_step : S::kStages;
+                int pre_stage[S::kStages];
+                for (int b = 0; b < npre && ok; ++b) {
+                    int m0, n0, kb;
+                    coords(b, m0, n0, kb);
+                    ok = mbar_wait(&empty[stage], phase ^ 1, abort_w, wait_ns);
+                    if (!ok) break;
+                    uint8_t *sb = smem + stage * S::kStageBytes + S::kABytes;
+                    mbar_expect_tx(&full[stage], S::kStageBytes);
+                    issued |= 1u << stage;
+                    parity = (parity & ~(1u << stage)) | (phase << stage);
+                    tma_load_2d(sb, &tm_b, kb * BK, n0, &full[stage]);
+                    pre_stage[b] = stage;
+                    if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                // 2. h_{t-1} is complete when every CTA has arrived tt times in this launch
+                if (tt > 0) {
+                    ok = wait_counter(a.counter, gridDim.x * (unsigned)tt + a.extra_arrivals, a.err, abort_w, 7u, wait_ns);
+                    if (!ok) break;
+                    fence_proxy_async_global();
+                }
+                for (int b = 0; b < npre; ++b) {
+                    int m0, n0, kb;
+                    coords(b, m0, n0, kb);
+                    tma_load_3d(smem + pre_stage[b] * S::kStageBytes, &tm_a, kb * BK, m0, t, &full[pre_stage[b]]);
+                }
+                // 3. the rest of the step
+                for (int b = npre; b < blocks_per_step && ok; ++b) {
+                    int m0, n0, kb;
+                    coords(b, m0, n0, kb);
+                    ok = mbar_wait(&empty[stage], phase ^ 1, abort_w, wait_ns);
+                    if (!ok) break;
+                    uint8_t *sa = smem + stage * S::kStageBytes, *sb = sa + S::kABytes;
+                    mbar_expect_tx(&full[stage], S::kStageBytes);
+                    issued |= 1u << stage;
+                    parity = (parity & ~(1u << stage)) | (phase << stage);
+                    tma_load_3d(sa, &tm_a, kb * BK, m0, t, &full[stage]);
+                    tma_load_2d(sb, &tm_b, kb * BK, n0, &full[stage]);
+                    if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+            // way out: every copy this thread started has landed before the CTA exits.  A stage whose W_hh block was
+            // fetched ahead of a barrier that then failed never gets its h block: that wait runs into its limit.
+            for (int i = 0; i < S::kStages; ++i)
+                if (issued >> i & 1u) mbar_drain(&full[i], parity >> i & 1u, ok ? wait_ns : 20000ull);
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0, last_commit = -1;
+            bool ok = true;
+            for (int tt = 0; tt < a.nsteps && ok; ++tt) {
+                for (int i = 0; i < my_tiles && ok; ++i, ++it) {
+                    const int buf = it & 1;
+                    ok = mbar_wait(&tempty[buf], ((it >> 1) & 1) ^ 1, abort_w, wait_ns);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t d_tmem = tmem_base + buf * BN;
+                    for (int kb = 0; kb < kblocks; ++kb) {
+                        ok = mbar_wait(&full[stage], phase, abort_w, wait_ns);
+                        if (!ok) break;
+                        tcgen05_fence_after();
+                        const uint32_t a_base = smem_u32(smem + stage * S::kStageBytes), b_base = a_base + S::kABytes;
+#pragma unroll
+                        for (int k = 0; k < BK / 16; ++k)
+                            umma_f16(d_tmem, umma_desc_kmajor_sw128(a_base + k * 32), umma_desc_kmajor_sw128(b_base + k * 32),
+                                     a.idesc, (kb | k) != 0);
+                        umma_commit(&empty[stage]);
+                        if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+                    }
+                    if (!ok) break;
+                    umma_commit(&tfull[buf]);
+                    last_commit = it;
+                }
+            }
+            if (last_commit >= 0) mbar_drain(&tfull[last_commit & 1], (uint32_t)(last_commit >> 1) & 1u, wait_ns);
+        }
+    } else {
+        const int q = warp & 3;  // TMEM lane quadrant this warp may access
+        constexpr int kGroups = BN / 64;
+        uint8_t *wb = epi + q * kEpiWarpBytes;
+        uint8_t *sH = wb + 2 * kEpiPBytes + 2 * kEpiCBytes;
+        uint64_t *ldbar = ldbars + q * 2;
+        const int items_per_step = my_tiles * kGroups;
+        auto item_coords = [&](int idx, int &row0, int &col0) {  // idx within a step
+            const int tl = blockIdx.x + (idx / kGroups) * gridDim.x;
+            row0 = (tl / num_n) * BM + q * 32;
+            col0 = (tl % num_n) * BN + (idx % kGroups) * 64;
+        };
+        // Items (tile, 64-column unit group) are numbered through the whole launch: item n stages its tiles in
+        // buffer n & 1, and lane 0 keeps the loads of item n + 1 in flight while the warp works on item n.
+        auto issue_loads = [&](int idx, int t, int buf) {  // one lane; idx = item within its step
+            int row0, col0;
+            item_coords(idx, row0, col0);
+            if (row0 >= a.M) return;  // nothing of this block is a real sequence
+            mbar_expect_tx(&ldbar[buf], kEpiPBytes + kEpiCBytes);
+            tma_load_3d(wb + buf * kEpiPBytes, &tm_g, col0, row0, t, &ldbar[buf]);
+            tma_load_3d(wb + 2 * kEpiPBytes + buf * kEpiCBytes, &tm_c, col0 >> 2, row0, t, &ldbar[buf]);
+        };
+        if (lane == 0 && items_per_step > 0) issue_loads(0, a.t0, 0);
+        uint32_t ldphase = 0;  // bit b: parity of the next completion of ldbar[b]
+        int it = 0, gitem = 0;
+        bool ok = true;
+        for (int tt = 0; tt < a.nsteps && ok; ++tt) {
+            const int t = a.t0 + tt;
+            bool good = true;  // warp-uniform: every wait of this step returned in time
+            int item = 0;
+            for (int i = 0; i < my_tiles; ++i, ++it) {
+                const int tbuf = it & 1;
+                if (good) good = __all_sync(0xffffffffu, mbar_wait(&tfull[tbuf], (it >> 1) & 1, abort_w, wait_ns));
+                tcgen05_fence_after();
+                const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + tbuf * BN;
+#pragma unroll 1
+                for (int g = 0; g < kGroups; ++g, ++item, ++gitem) {
+                    const int buf = gitem & 1;
+                    int row0, col0;
+                    item_coords(item, row0, col0);
+                    if (lane == 0 && good) {
+                        tma_store_wait_read<0>();  // earlier stores have read the other buffer and sH
+                        // the next item of THIS step; the first item of the next step waits for this step's own
+                        // stores to complete (its cell-state tile is one of them), see the end of the step
+                        if (item + 1 < items_per_step) issue_loads(item + 1, t, (gitem + 1) & 1);
+                    }
+                    __syncwarp();
+                    uint32_t acc[64];
+                    if (good) {
+                        tmem_ld_32x32b_x32(t_row + g * 64, *reinterpret_cast<uint32_t(*)[32]>(&acc[0]));
+                        tmem_ld_32x32b_x32(t_row + g * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&acc[32]));
+                        tmem_ld_wait();
+                    }
+                    if (g == kGroups - 1) {  // the accumulator is in registers: hand it back to the UMMA warp
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tempty[tbuf]);
+                    }
+                    if (row0 >= a.M || !good) continue;
+                    good = __all_sync(0xffffffffu, mbar_wait(&ldbar[buf], (ldphase >> buf) & 1u, abort_w, wait_ns));
+                    if (!good) continue;
+                    ldphase ^= 1u << buf;
+                    uint8_t *sP = wb + buf * kEpiPBytes, *sC = wb + 2 * kEpiPBytes + buf * kEpiCBytes;
+                    lstm_cell_16<BF16>(acc, sP, sC, sH, lane, a.store_gates);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (a.store_gates) tma_store_3d(&tm_g, sP, col0, row0, t);
+                        tma_store_3d(&tm_c, sC, col0 >> 2, row0, t + 1);
+                        tma_store_3d(&tm_h, sH, col0 >> 2, row0, t + 1);
+                        if (a.has_y) tma_store_3d(&tm_y, sH, col0 >> 2, row0, t);
+                        tma_store_commit();
+                    }
+                }
+            }
+            // h_t, c_t of this warp's rows are in global memory before the CTA arrives at the step barrier
+            if (lane == 0) tma_store_wait_all<0>();
+            __syncwarp();
+            if (named_barrier_or(1, 128, !good)) {
+                ok = false;
+                break;
+            }
+            if (warp == 2 && lane == 0) {
+                fence_proxy_async_global();  // the tiles were written through the async proxy
+                red_release_gpu_add(a.counter, 1u);
+            }
+            if (lane == 0 && tt + 1 < a.nsteps && items_per_step > 0) issue_loads(0, t + 1, gitem & 1);
+        }
+        if (lane == 0) tma_store_wait_all<0>();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, S::kTmemCols);
+    if (threadIdx.x == 0 && *abort_w) atomicCAS(a.err, 0u, 1u);
+}
+
 // Pointwise backward of one time step for 4 hidden units of one sequence per thread:
 //   dh = dy_t + sum of the fp32 partial products dG_{t+1} W_hh;  dc, dG_t as in the persistent BPTT kernel.
 template <bool BF16>
@@ -604,6 +868,9 @@ int plan_step(int B, int H, int sms, size_t smem_limit, StepPlan *plan) {
         need_bwd = plan->bn_bwd == 256 ? StepShape<256, EPI_F32_PARTS, false>::kSmemBytes : StepShape<128, EPI_F32_PARTS, false>::kSmemBytes;
     }
     if (need_fwd > smem_limit || need_bwd > smem_limit) plan->use = false;  // the step kernels do not fit this device
+    // forward: all steps of a range in one cooperative launch (lone-CTA tiles); FLSTM_WIDE_PERSIST=0 = one launch per step
+    const char *wp = std::getenv("FLSTM_WIDE_PERSIST");
+    plan->fwd_persistent = plan->use && !plan->pair && !(wp && wp[0] == '0');
     return FLSTM_OK;
 }
 
@@ -627,6 +894,46 @@ int lstm_step_forward(int dtype, const StepPlan &plan, const StepFwdMaps &m, con
                     : launch_step<256, EPI_LSTM_FWD, false, false>(plan.pair, *m.hs, *m.w, em, a, sms, s);
     return bf16 ? launch_step<128, EPI_LSTM_FWD, false, true>(plan.pair, *m.hs, *m.w, em, a, sms, s)
                 : launch_step<128, EPI_LSTM_FWD, false, false>(plan.pair, *m.hs, *m.w, em, a, sms, s);
+}
+
+template <int BN, bool BF16>
+static int launch_wide_fwd(const StepFwdMaps &m, const WideFwdArgs &a, int sms, cudaStream_t s) {
+    using S = StepShape<BN, EPI_LSTM_FWD, false>;
+    auto kern = wide_fwd_kernel<BN, BF16>;
+    FLSTM_CUDA_TRY(ensure_smem_limit(kern, (size_t)S::kSmemBytes));
+    const int tiles = ((a.M + BM - 1) / BM) * (a.N / BN);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles < sms ? tiles : sms);
+    cfg.blockDim = dim3(kStepThreads);
+    cfg.dynamicSmemBytes = S::kSmemBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;  // the CTAs wait on one another: all of them must be resident
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *m.hs, *m.w, *m.gates, *m.cs, *m.hs_out, m.y ? *m.y : *m.hs_out, a);
+    if (e != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "wide-batch forward launch failed: %s", cudaGetErrorString(e));
+    return FLSTM_OK;
+}
+
+int lstm_wide_forward(int dtype, const StepPlan &plan, const StepFwdMaps &m, const WideFwdParams &p, int sms, cudaStream_t s) {
+    const bool bf16 = dtype == FLSTM_DTYPE_BF16;
+    WideFwdArgs a{};
+    a.M = p.B;
+    a.N = 4 * p.H;
+    a.K = p.H;
+    a.t0 = p.t0;
+    a.nsteps = p.nsteps;
+    a.idesc = umma_idesc_f16(BM, plan.bn_fwd, bf16 ? 1 : 0, 0, 0);
+    a.err = p.err;
+    a.counter = p.counter;
+    a.has_y = m.y ? 1 : 0;
+    a.store_gates = p.store_gates;
+    a.wait_ns = p.wait_ns;
+    a.extra_arrivals = p.extra_arrivals;
+    if (plan.bn_fwd == 256) return bf16 ? launch_wide_fwd<256, true>(m, a, sms, s) : launch_wide_fwd<256, false>(m, a, sms, s);
+    return bf16 ? launch_wide_fwd<128, true>(m, a, sms, s) : launch_wide_fwd<128, false>(m, a, sms, s);
 }
 
 int lstm_step_backward_gemm(int dtype, const StepPlan &plan, const CUtensorMap &tm_dg, const CUtensorMap &tm_w64, int t,
