@@ -239,7 +239,10 @@ int forward_layer(Engine &e, int li, size_t t0, size_t t1, const void *x_l, void
         CUtensorMap tm_y;
         if (y_out) FLSTM_TRY(make_tensor_map_3d_tile(&tm_y, y_out, 2, t1, B, H, 32, 16));
         const StepFwdMaps maps{&t.tm_hs3, &t.tm_wstep, &t.tm_g_ep, &t.tm_c_ep, &t.tm_h_ep, y_out ? &tm_y : nullptr};
-        if (st->step.fwd_persistent) {
+        // one cooperative launch for the whole range, unless layers run concurrently on their own streams (the
+        // cross-layer wavefront): two cooperative grids that each need most of the machine must not be in flight
+        // at once, each could hold SMs the other is waiting for
+        if (st->step.fwd_persistent && wavefront_chunk(e, (size_t)-1) == 0) {
             FLSTM_CUDA_TRY(cudaMemsetAsync(e.sync_words + 1, 0, sizeof(unsigned int), s));
             WideFwdParams wp{};
             wp.err = err;
