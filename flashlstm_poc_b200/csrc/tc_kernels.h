@@ -55,7 +55,8 @@ struct FwdParams {
 };
 
 int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan);
-bool wide_tile_enabled();  // 33..64 sequences as one 64-wide batch tile when a CTA would otherwise take two
+bool wide_tile_enabled();   // 33..64 sequences as one 64-wide batch tile when a CTA would otherwise take two
+bool wider_tile_enabled();  // 65..128 sequences as one 128-wide batch tile likewise
 // tm_w: W_hh rows tile-interleaved (4H, H), box 64x64, 128B swizzle.  tm_h: hidden states as a
 // chunked map (make_tensor_map_chunked) with box rows BT and plan.ch chunks.  tm_g: projection as
 // (T, B, 4H), box 1 x BT x 64, no swizzle.

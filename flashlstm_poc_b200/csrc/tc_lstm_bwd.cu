@@ -503,6 +503,7 @@ static int query_clusters(const BwdPlan &pl) {
     if (pl.BT == BT_ && pl.KS == KS_ && pl.resident == RES_) return max_clusters<BT_, KS_, RES_>(pl.smem_bytes, pl.grid);
     FLSTM_BWD_Q(32, 2, true) FLSTM_BWD_Q(32, 2, false) FLSTM_BWD_Q(32, 4, true) FLSTM_BWD_Q(32, 4, false)
     FLSTM_BWD_Q(64, 2, true) FLSTM_BWD_Q(64, 2, false) FLSTM_BWD_Q(64, 4, true) FLSTM_BWD_Q(64, 4, false)
+    FLSTM_BWD_Q(128, 4, true) FLSTM_BWD_Q(128, 4, false)
 #undef FLSTM_BWD_Q
     return -1;
 }
@@ -528,10 +529,21 @@ int plan_bwd(int B, int H, int sms, size_t smem_limit, BwdPlan *plan, bool check
         ngroups = (tiles + nt - 1) / nt;
     };
     split(BT);
-    if (BT == 32 && nt == 2 && 2 * jt * KS > sms && wide_tile_enabled()) {
-        split(64);
-        if (nt == 1) BT = 64;
-        else split(32);
+    if (nt > 1) {
+        const int max_groups = sms / (jt * KS) < 1 ? 1 : sms / (jt * KS);
+        const int first = BT == 32 ? 64 : 128;
+        bool found = false;
+        for (int bt = first; bt <= 128 && !found; bt *= 2) {
+            if (bt == 64 && !(max_groups == 1 && wide_tile_enabled())) continue;
+            // 128-wide tiles exist for clusters of 4 only, and pay when two or more batch groups work side by side
+            if (bt == 128 && !(KS == 4 && max_groups >= 2 && wider_tile_enabled())) continue;
+            split(bt);
+            if (nt == 1 && ngroups == max_groups) {  // and no batch group's CTAs are left idle
+                BT = bt;
+                found = true;
+            }
+        }
+        if (!found) split(BT);
     }
     const int kc_per = kc_total / KS;
     // measured on config 2: one 64 KB copy per step beats 2, 4, 8 or 16 smaller ones (TMA issue cost
@@ -552,6 +564,14 @@ int plan_bwd(int B, int H, int sms, size_t smem_limit, BwdPlan *plan, bool check
         stages = kc_per / ch < 4 ? kc_per / ch : 4;
         l = bwd_smem_layout(BT, H, KS, false, stages, ch);
         while ((size_t)l.total > smem_limit && stages > 1) l = bwd_smem_layout(BT, H, KS, false, --stages, ch);
+        // a single stage cannot overlap the copy with the UMMAs: rather two stages of half the chunks
+        while (stages < 2 && ch > 1 && kc_per / (ch / 2) >= 2) {
+            ch /= 2;
+            stages = 2;
+            l = bwd_smem_layout(BT, H, KS, false, stages, ch);
+            if ((size_t)l.total > smem_limit) stages = 1;
+        }
+        l = bwd_smem_layout(BT, H, KS, false, stages, ch);
         while ((size_t)l.total > smem_limit && ch > 1) {
             --ch;
             while (kc_per % ch) --ch;
@@ -604,6 +624,7 @@ int lstm_backward_persistent(int dtype, const BwdPlan &plan, const CUtensorMap &
     FLSTM_BWD_CASE(32, 1, true) FLSTM_BWD_CASE(32, 1, false) FLSTM_BWD_CASE(32, 2, true) FLSTM_BWD_CASE(32, 2, false)
     FLSTM_BWD_CASE(32, 4, true) FLSTM_BWD_CASE(32, 4, false) FLSTM_BWD_CASE(64, 1, true) FLSTM_BWD_CASE(64, 1, false)
     FLSTM_BWD_CASE(64, 2, true) FLSTM_BWD_CASE(64, 2, false) FLSTM_BWD_CASE(64, 4, true) FLSTM_BWD_CASE(64, 4, false)
+    FLSTM_BWD_CASE(128, 4, true) FLSTM_BWD_CASE(128, 4, false)
 #undef FLSTM_BWD_CASE
     return set_error(FLSTM_ERR_UNSUPPORTED, "no BPTT kernel for this plan");
 }

@@ -394,6 +394,11 @@ bool wide_tile_enabled() {
     return !(env && env[0] == '0');
 }
 
+bool wider_tile_enabled() {
+    const char *env = std::getenv("FLSTM_BT128");
+    return !(env && env[0] == '0');
+}
+
 int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan) {
     if (H % 64 != 0 || H < 64) return set_error(FLSTM_ERR_UNSUPPORTED, "hidden size must be a multiple of 64");
     const int R = H / 16;  // row tiles
@@ -402,7 +407,8 @@ int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan) {
     const int cta_rows = R / rt;
     // 32 sequences per batch tile while every batch group then gets its own set of CTAs; when the row tiles
     // alone fill the machine (H = 2048) a CTA would take two 32-wide tiles per step and stream its W_hh slice
-    // twice, so 33..64 sequences become ONE 64-wide tile (the UMMA costs the same at N = 32 and N = 64).
+    // twice, so 33..64 sequences become ONE 64-wide tile (the UMMA costs the same at N = 32 and N = 64), and
+    // 65..128 sequences per batch group ONE 128-wide tile.
     // Measured at B = 64, H = 2048, L = 2, T = 1024 (fwd+bwd): 46.5 ms against 55.6 ms on the per-step path.  With
     // two row tiles per CTA (H = 4096) the per-step path stays ahead (75.6 against 88.6 ms), so the rule stops there.
     int BT = (B >= 128) ? 64 : 32;
@@ -416,10 +422,23 @@ int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan) {
         ngroups = (tiles + nt - 1) / nt;
     };
     split(BT);
-    if (BT == 32 && nt == 2 && rt == 1 && 2 * cta_rows > sms && wide_tile_enabled()) {
-        split(64);
-        if (nt == 1) BT = 64;
-        else split(32);
+    if (nt > 1 && rt == 1) {
+        // the narrowest wider tile that leaves every CTA a single batch tile per step
+        const int max_groups = sms / cta_rows < 1 ? 1 : sms / cta_rows;
+        const int first = BT == 32 ? 64 : 128;
+        bool found = false;
+        for (int bt = first; bt <= 128 && !found; bt *= 2) {
+            if (bt == 64 && !(max_groups == 1 && wide_tile_enabled())) continue;
+            // 128-wide tiles pay when two or more batch groups work side by side (H <= 1024); measured at
+            // H = 2048, B = 128 the per-step path stays ahead over forward + backward (79.8 against 82.2 ms)
+            if (bt == 128 && !(max_groups >= 2 && wider_tile_enabled())) continue;
+            split(bt);
+            if (nt == 1 && ngroups == max_groups) {  // and no batch group's CTAs are left idle
+                BT = bt;
+                found = true;
+            }
+        }
+        if (!found) split(BT);
     }
     // One TMA copy brings `ch` 64-wide K chunks of an h tile; the ring holds a whole tile when it can.
     // The W_hh slice stays resident if it fits next to a ring of at least two stages.
@@ -442,6 +461,14 @@ int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan) {
         stages = kc / ch < 4 ? kc / ch : 4;
         l = fwd_smem_layout(BT, H, rt, false, stages, ch);
         while ((size_t)l.total > smem_limit && stages > 1) l = fwd_smem_layout(BT, H, rt, false, --stages, ch);
+        // a single stage cannot overlap the copy with the UMMAs: rather two stages of half the chunks
+        while (stages < 2 && ch > 1 && kc / (ch / 2) >= 2) {
+            ch /= 2;
+            stages = 2;
+            l = fwd_smem_layout(BT, H, rt, false, stages, ch);
+            if ((size_t)l.total > smem_limit) stages = 1;
+        }
+        l = fwd_smem_layout(BT, H, rt, false, stages, ch);
         while ((size_t)l.total > smem_limit && ch > 1) {
             --ch;
             while (kc % ch) --ch;
@@ -479,6 +506,8 @@ int lstm_forward_persistent(int dtype, const FwdPlan &plan, const CUtensorMap &t
     FLSTM_FWD_CASE(32, false)
     FLSTM_FWD_CASE(64, true)
     FLSTM_FWD_CASE(64, false)
+    FLSTM_FWD_CASE(128, true)
+    FLSTM_FWD_CASE(128, false)
 #undef FLSTM_FWD_CASE
     return set_error(FLSTM_ERR_UNSUPPORTED, "no recurrent forward kernel for this plan");
 }

@@ -77,7 +77,11 @@ def test_scaled_baseline_configs(name, scale):
     ("bf16", 2, 5, 32, 2048, 2048, True, "auto"),    # config 3's width: W_hh slices do not fit shared memory -> streamed from L2
     ("f16", 1, 4, 8, 4096, 4096, False, "auto"),     # config 4: two row tiles per CTA, streamed weights, inference
     ("f16", 1, 3, 1, 4096, 4096, False, "auto"),     # config 4 at batch 1
-    ("bf16", 2, 4, 256, 256, 1024, True, "auto"),    # wide batch (config 5's regime): one GEMM launch per step, no K split
+    ("bf16", 2, 4, 256, 256, 1024, True, "auto"),    # 256 sequences at H=1024: two batch groups, one 128-wide tile each
+    ("f16", 1, 5, 160, 128, 1024, True, "auto"),     # 128-wide tiles, the second one ragged (32 of 128 sequences)
+    ("bf16", 1, 4, 192, 64, 512, False, "auto"),     # 128-wide tiles, inference, H=512
+    ("bf16", 2, 4, 512, 256, 1024, True, "auto"),    # wide batch (config 5's regime): one GEMM launch per step, no K split
+    ("bf16", 1, 4, 96, 128, 1024, True, "auto"),     # 96 sequences at H=1024: per-step path, one ragged 128-row tile
     ("bf16", 1, 3, 64, 256, 2048, True, "auto"),     # two batch tiles per CTA at H=2048: the planner takes the per-step path
     ("f16", 1, 5, 300, 128, 256, True, "step"),      # per-step path, ragged last 128-row tile, backward K split 8 ways
     ("bf16", 1, 3, 256, 128, 512, False, "step"),    # per-step path, inference

@@ -60,7 +60,8 @@ def test_benchmark_configuration_plan(lib):
     assert (p.bwd_grid, p.bwd_cluster_size, p.bwd_weights_resident) == (128, 4, 1)
 
 
-@pytest.mark.parametrize("B,H,step", [(64, 1024, 0), (96, 1024, 1), (128, 1024, 0), (160, 1024, 1), (2048, 1024, 1),
+@pytest.mark.parametrize("B,H,step", [(64, 1024, 0), (96, 1024, 1), (128, 1024, 0), (160, 1024, 0), (256, 1024, 0),
+                                      (512, 1024, 1), (2048, 1024, 1),
                                       (32, 2048, 0), (64, 2048, 0), (128, 2048, 1), (256, 2048, 1), (8, 4096, 0),
                                       (64, 4096, 1), (96, 4096, 1)])
 def test_path_choice_follows_the_measured_crossover(lib, B, H, step):
@@ -72,6 +73,25 @@ def test_path_choice_follows_the_measured_crossover(lib, B, H, step):
     assert st == 0 and p.step_path == step
     if not step and H >= 2048 and B > 32:
         assert p.fwd_batch_tile == 64 and p.fwd_tiles_per_group == 1
+    if not step and H == 1024 and B > 128:  # two batch groups side by side, each on one 128-wide tile
+        assert (p.fwd_batch_tile, p.fwd_batch_groups, p.fwd_tiles_per_group) == (128, 2, 1)
+        assert (p.bwd_batch_tile, p.bwd_batch_groups, p.bwd_tiles_per_group) == (128, 2, 1)
+
+
+@pytest.mark.parametrize("H", [64, 256, 512, 768, 1024, 1536, 2048, 4096])
+def test_persistent_plans_cover_every_sequence(lib, H):
+    """Whatever tile width the planner settles on, groups x tiles per group x tile width reaches the whole batch
+    (a plan that covered fewer sequences would leave rows of every output unwritten)."""
+    for B in list(range(1, 66)) + [95, 96, 97, 127, 128, 129, 160, 192, 255, 256, 257, 512, 1000, 2048]:
+        for training in (0, 1):
+            st, p = plan(lib, B, H, training=training)
+            if st != 0 or p.step_path:
+                continue
+            assert p.fwd_batch_groups * p.fwd_tiles_per_group * p.fwd_batch_tile >= B, (B, H)
+            assert p.fwd_grid <= 148
+            if training:
+                assert p.bwd_batch_groups * p.bwd_tiles_per_group * p.bwd_batch_tile >= B, (B, H)
+                assert p.bwd_grid <= 148
 
 
 def test_wide_batch_plans(lib):

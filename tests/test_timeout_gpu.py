@@ -51,6 +51,7 @@ def test_step_barrier_timeout_returns_and_engine_recovers(dtype, backend, where)
     eng, dev = _engine(w, inp, backend)
     assert eng.backend == backend
     before = _step(eng, inp, dev, td)
+    assert all(np.isfinite(a).all() for a in before) and np.abs(before[0]).max() <= 1.0  # every row of y was written
 
     eng.set_wait_limit(LIMIT_US)
     x, h0, c0, dy = (t.to(dev, td) for t in (inp.x, inp.h0, inp.c0, inp.dy))
