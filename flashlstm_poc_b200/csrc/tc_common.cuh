@@ -16,6 +16,10 @@ namespace flstm_b200 {
 namespace tc {
 
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s: the default limit of every device-side wait
+// After an abort a producer still waits this long for ring stages whose copies can no longer complete (one half of a
+// stage was fetched ahead of a barrier that then failed); copies that were started land well within it.
+constexpr unsigned long long kAbortDrainNs = 20000ull;
+constexpr int kMaxRingStages = 32;  // ring stages are tracked in 32-bit masks
 
 // ------------------------------------------------------------------ small utilities
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {

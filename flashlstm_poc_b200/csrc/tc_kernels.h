@@ -108,7 +108,7 @@ int lstm_backward_persistent(int dtype, const BwdPlan &plan, const CUtensorMap &
 // ------------------------------------------------------------------ wide-batch path: one GEMM launch per step
 struct StepPlan {
     bool use;     // the engine takes this path instead of the persistent kernels
-    int bn_fwd;   // output-tile width of the forward step GEMM (gate columns): 128 or 256
+    int bn_fwd;   // output-tile width of the forward step GEMM (gate columns): 64, 128 or 256
     int bn_bwd;   // output-tile width of the backward step GEMM (hidden units): 128 or 256
     int splits;   // K = 4H splits of the backward step GEMM (fp32 partial sums, added by the pointwise kernel)
     bool pair;    // tiles of 256 sequences on CTA pairs (cta_group::2); the forward W_hh map then has bn_fwd / 2 rows per box

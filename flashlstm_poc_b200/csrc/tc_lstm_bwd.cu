@@ -148,6 +148,28 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             // the self-test of the timeout path, where it asks for arrivals that nobody makes.
             for (int s = (p.s0 > 1 ? p.s0 : 1); s < p.s1 && ok; ++s) {
                 const int t_src = p.T - s;  // dG_{t+1} with t = T-1-s
+                // Streamed weights: the W_hh chunks of the iteration's first loads do not depend on dG_{t+1}, so they
+                // go into the ring AHEAD of the step barrier (the stage's byte count covers both copies; the dG
+                // chunks follow once the barrier has been passed).
+                int npre = 0;
+                int pre_stage[kMaxRingStages];
+                if (!W_RESIDENT && s > p.s0) {
+                    npre = NLOAD < L.stages ? NLOAD : L.stages;
+                    for (int ld = 0; ld < npre; ++ld) {
+                        ok = mbar_wait(&empty[stage], phase ^ 1, abort_w, wait_ns);
+                        if (!ok) break;
+                        uint8_t *sd = s_ring + stage * L.ring_stage_bytes;
+                        mbar_expect_tx(&full[stage], (uint32_t)L.ring_stage_bytes);
+                        ring_issued |= 1u << stage;
+                        ring_parity = (ring_parity & ~(1u << stage)) | (phase << stage);
+                        for (int c = 0; c < CH; ++c)
+                            tma_load_2d(sd + CH * BT * 128 + c * kChunkBytesW, &tm_w, j * 64, (c_first + ld * CH + c) * 64,
+                                        &full[stage]);
+                        pre_stage[ld] = stage;
+                        if (++stage == L.stages) { stage = 0; phase ^= 1; }
+                    }
+                    if (!ok) break;
+                }
                 if (s > p.s0)
                     ok = wait_counter(counter, (unsigned)(p.jt * KS) * (unsigned)(s - p.s0) + p.extra_arrivals, p.err, abort_w,
                                       3u, wait_ns);
@@ -156,7 +178,11 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 FLSTM_STAMP(s - p.s0, 0);
                 for (int n = 0; n < nt_count && ok; ++n) {
                     const int b0 = (ng * nt_count + n) * BT;
-                    for (int ld = 0; ld < NLOAD; ++ld) {
+                    const int skip = n == 0 ? npre : 0;
+                    for (int ld = 0; ld < skip; ++ld)
+                        tma_load_4d(s_ring + pre_stage[ld] * L.ring_stage_bytes, &tm_dg, 0, b0, c_first + ld * CH, t_src,
+                                    &full[pre_stage[ld]]);
+                    for (int ld = skip; ld < NLOAD; ++ld) {
                         ok = mbar_wait(&empty[stage], phase ^ 1, abort_w, wait_ns);
                         if (!ok) break;
                         uint8_t *sd = s_ring + stage * L.ring_stage_bytes;
@@ -175,9 +201,11 @@ lstm_bwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 FLSTM_STAMP(s - p.s0, 1);
             }
             // way out (normal or aborted): every copy this thread started must have landed before the CTA exits
+            // (a stage whose W_hh chunks went ahead of a barrier that then failed never gets its dG chunks: after an
+            // abort the wait for it is cut short, long after the chunks that were started have landed)
             if (W_RESIDENT) mbar_drain(wbar, 0, wait_ns);
             for (int i = 0; i < L.stages; ++i)
-                if (ring_issued >> i & 1u) mbar_drain(&full[i], ring_parity >> i & 1u, wait_ns);
+                if (ring_issued >> i & 1u) mbar_drain(&full[i], ring_parity >> i & 1u, ok ? wait_ns : kAbortDrainNs);
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------ MMA issuer

@@ -156,6 +156,28 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         tma_load_3d(s_p + pb * BT * 128, &tm_g, j * 64, b0, t, &pfull[pb]);
                         p_issued |= 1u << pb;
                         p_parity = (p_parity & ~(1u << pb)) | (((wi >> 1) & 1u) << pb);
+                        // Streamed weights: the W_hh chunks of a step's first loads do not depend on h_{t-1}, so they
+                        // go into the ring AHEAD of the step barrier (the stage's byte count covers both copies; the
+                        // h chunks follow once the barrier has been passed).
+                        int npre = 0;
+                        int pre_stage[kMaxRingStages];
+                        if (!W_RESIDENT && first && tt > 0) {
+                            npre = NLOAD < L.stages ? NLOAD : L.stages;
+                            for (int ld = 0; ld < npre; ++ld) {
+                                ok = mbar_wait(&empty[stage], phase ^ 1, abort_w, wait_ns);
+                                if (!ok) break;
+                                uint8_t *sh = s_ring + stage * L.ring_stage_bytes;
+                                mbar_expect_tx(&full[stage], (uint32_t)L.ring_stage_bytes);
+                                ring_issued |= 1u << stage;
+                                ring_parity = (ring_parity & ~(1u << stage)) | (phase << stage);
+                                for (int c = 0; c < CH; ++c)
+                                    tma_load_2d(sh + CH * BT * 128 + c * kChunkBytesW, &tm_w, (ld * CH + c) * 64, j * 64,
+                                                &full[stage]);
+                                pre_stage[ld] = stage;
+                                if (++stage == L.stages) { stage = 0; phase ^= 1; }
+                            }
+                            if (!ok) break;
+                        }
                         if (first && tt > 0) {
                             // h_{t-1} of this batch group is complete when every CTA of the group has
                             // arrived tt times in this launch (once per step each); the state a launch
@@ -168,7 +190,10 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         }
                         if (first) FLSTM_STAMP(tt, 0);
                         first = false;
-                        for (int ld = 0; ld < NLOAD; ++ld) {
+                        for (int ld = 0; ld < npre; ++ld)
+                            tma_load_4d(s_ring + pre_stage[ld] * L.ring_stage_bytes, &tm_h, 0, b0, ld * CH, t,
+                                        &full[pre_stage[ld]]);
+                        for (int ld = npre; ld < NLOAD; ++ld) {
                             ok = mbar_wait(&empty[stage], phase ^ 1, abort_w, wait_ns);
                             if (!ok) break;
                             uint8_t *sh = s_ring + stage * L.ring_stage_bytes;
@@ -189,9 +214,11 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             }
             // Way out (normal or aborted): every copy this thread started must have landed before the CTA
             // exits.  After a normal run the consumers have already waited for all of them, so this costs nothing.
+            // (a stage whose W_hh chunks went ahead of a barrier that then failed never gets its h chunks: after an
+            // abort the wait for it is cut short, long after the chunks that were started have landed)
             if (W_RESIDENT) mbar_drain(wbar, 0, wait_ns);
             for (int i = 0; i < L.stages; ++i)
-                if (ring_issued >> i & 1u) mbar_drain(&full[i], ring_parity >> i & 1u, wait_ns);
+                if (ring_issued >> i & 1u) mbar_drain(&full[i], ring_parity >> i & 1u, ok ? wait_ns : kAbortDrainNs);
             for (int i = 0; i < 2; ++i)
                 if (p_issued >> i & 1u) mbar_drain(&pfull[i], p_parity >> i & 1u, wait_ns);
         }

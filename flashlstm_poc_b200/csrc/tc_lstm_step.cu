@@ -54,7 +54,7 @@ struct StepShape {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kEpiBytes = (EPI == EPI_LSTM_FWD) ? 4 * kEpiWarpBytes : 0;
     static constexpr int kStages = PAIR ? ((227 * 1024 - kEpiBytes - 2048) / kStageBytes > 8 ? 8 : (227 * 1024 - kEpiBytes - 2048) / kStageBytes)
-                                        : ((EPI == EPI_LSTM_FWD) ? ((BN == 256) ? 3 : 5) : ((BN == 256) ? 4 : 6));
+                                        : ((EPI == EPI_LSTM_FWD) ? ((BN == 256) ? 3 : (BN == 128) ? 5 : 6) : ((BN == 256) ? 4 : 6));
     static constexpr int kTmemCols = 2 * BN;
     static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
@@ -586,7 +586,7 @@ wide_fwd_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             // way out: every copy this thread started has landed before the CTA exits.  A stage whose W_hh block was
             // fetched ahead of a barrier that then failed never gets its h block: that wait runs into its limit.
             for (int i = 0; i < S::kStages; ++i)
-                if (issued >> i & 1u) mbar_drain(&full[i], parity >> i & 1u, ok ? wait_ns : 20000ull);
+                if (issued >> i & 1u) mbar_drain(&full[i], parity >> i & 1u, ok ? wait_ns : kAbortDrainNs);
         }
     } else if (warp == 1) {
         if (elect_one()) {
@@ -814,11 +814,14 @@ int launch_step(bool pair, const CUtensorMap &ta, const CUtensorMap &tb, const E
 // cost of one K step (a 128 x BN x 16 UMMA reads 4 KB + BN*32 B of operands).  For CTA pairs (m_tiles counts
 // 256-row tiles, sms / 2 workers) a K block of a 256 x 128 tile costs 3/8 and of a 256 x 256 tile 4/8 of what a
 // lone 128 x 256 tile costs: each CTA stages 24 KB resp. 32 KB instead of 48 KB.
-int pick_bn(int m_tiles, int N, int splits, int sms, bool pair = false) {
+int pick_bn(int m_tiles, int N, int splits, int sms, bool pair = false, bool allow64 = false) {
     if (N % 256) return 128;
     const int workers = pair ? sms / 2 : sms;
     const int t128 = m_tiles * (N / 128) * splits, t256 = m_tiles * (N / 256) * splits;
     const int cost128 = ((t128 + workers - 1) / workers) * (pair ? 3 : 2), cost256 = ((t256 + workers - 1) / workers) * (pair ? 4 : 3);
+    // 64-wide tiles (forward, lone CTAs) when 128-wide ones leave half of the SMs without a tile: a CTA then takes
+    // in 128 + 64 operand rows per K block instead of 128 + 128 (cost 1.5 on the scale above)
+    if (allow64 && !pair && 2 * t128 <= workers && cost128 <= cost256) return 64;
     return cost256 < cost128 ? 256 : 128;
 }
 
@@ -853,7 +856,7 @@ int plan_step(int B, int H, int sms, size_t smem_limit, StepPlan *plan) {
     plan->pair = B >= 2 * BM && sms >= 2 && step_pair_enabled();
     const int rows = plan->pair ? 2 * BM : BM, workers = plan->pair ? sms / 2 : sms;
     const int m_tiles = (B + rows - 1) / rows;
-    plan->bn_fwd = pick_bn(m_tiles, 4 * H, 1, sms, plan->pair);
+    plan->bn_fwd = pick_bn(m_tiles, 4 * H, 1, sms, plan->pair, true);
     // backward: K = 4H is long and N = H short; split K until the tiles fill the machine
     int splits = 1;
     while (splits < 8 && m_tiles * (H / 128) * splits * 2 <= workers && ((4 * H / BK) % (splits * 2)) == 0) splits *= 2;
@@ -864,7 +867,9 @@ int plan_step(int B, int H, int sms, size_t smem_limit, StepPlan *plan) {
         need_fwd = plan->bn_fwd == 256 ? StepShape<256, EPI_LSTM_FWD, true>::kSmemBytes : StepShape<128, EPI_LSTM_FWD, true>::kSmemBytes;
         need_bwd = plan->bn_bwd == 256 ? StepShape<256, EPI_F32_PARTS, true>::kSmemBytes : StepShape<128, EPI_F32_PARTS, true>::kSmemBytes;
     } else {
-        need_fwd = plan->bn_fwd == 256 ? StepShape<256, EPI_LSTM_FWD, false>::kSmemBytes : StepShape<128, EPI_LSTM_FWD, false>::kSmemBytes;
+        need_fwd = plan->bn_fwd == 256 ? StepShape<256, EPI_LSTM_FWD, false>::kSmemBytes
+                   : plan->bn_fwd == 128 ? StepShape<128, EPI_LSTM_FWD, false>::kSmemBytes
+                                         : StepShape<64, EPI_LSTM_FWD, false>::kSmemBytes;
         need_bwd = plan->bn_bwd == 256 ? StepShape<256, EPI_F32_PARTS, false>::kSmemBytes : StepShape<128, EPI_F32_PARTS, false>::kSmemBytes;
     }
     if (need_fwd > smem_limit || need_bwd > smem_limit) plan->use = false;  // the step kernels do not fit this device
@@ -892,6 +897,9 @@ int lstm_step_forward(int dtype, const StepPlan &plan, const StepFwdMaps &m, con
     if (plan.bn_fwd == 256)
         return bf16 ? launch_step<256, EPI_LSTM_FWD, false, true>(plan.pair, *m.hs, *m.w, em, a, sms, s)
                     : launch_step<256, EPI_LSTM_FWD, false, false>(plan.pair, *m.hs, *m.w, em, a, sms, s);
+    if (plan.bn_fwd == 64)  // lone CTAs only (the planner never pairs 64-wide tiles)
+        return bf16 ? launch_step_one<64, EPI_LSTM_FWD, false, true, false>(*m.hs, *m.w, em, a, sms, s)
+                    : launch_step_one<64, EPI_LSTM_FWD, false, false, false>(*m.hs, *m.w, em, a, sms, s);
     return bf16 ? launch_step<128, EPI_LSTM_FWD, false, true>(plan.pair, *m.hs, *m.w, em, a, sms, s)
                 : launch_step<128, EPI_LSTM_FWD, false, false>(plan.pair, *m.hs, *m.w, em, a, sms, s);
 }
@@ -933,6 +941,7 @@ int lstm_wide_forward(int dtype, const StepPlan &plan, const StepFwdMaps &m, con
     a.wait_ns = p.wait_ns;
     a.extra_arrivals = p.extra_arrivals;
     if (plan.bn_fwd == 256) return bf16 ? launch_wide_fwd<256, true>(m, a, sms, s) : launch_wide_fwd<256, false>(m, a, sms, s);
+    if (plan.bn_fwd == 64) return bf16 ? launch_wide_fwd<64, true>(m, a, sms, s) : launch_wide_fwd<64, false>(m, a, sms, s);
     return bf16 ? launch_wide_fwd<128, true>(m, a, sms, s) : launch_wide_fwd<128, false>(m, a, sms, s);
 }
 

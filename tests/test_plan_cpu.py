@@ -30,7 +30,7 @@ def test_plans_fit_the_machine(lib, B, H):
     if p.step_path:
         # one output-tiled GEMM launch per step; K = 4H split while tiles are scarce
         assert H % 128 == 0 and p.fwd_grid == 0
-        assert p.step_bn_fwd in (128, 256) and p.step_bn_bwd in (128, 256) and (4 * H) % p.step_bn_fwd == 0
+        assert p.step_bn_fwd in (64, 128, 256) and p.step_bn_bwd in (128, 256) and (4 * H) % p.step_bn_fwd == 0
         assert H % p.step_bn_bwd == 0 and p.step_splits in (1, 2, 4, 8) and (4 * H // 64) % p.step_splits == 0
         return
     assert p.fwd_tiles_per_group == 1 or H % 128 != 0  # the persistent kernels keep the single-tile shapes
@@ -101,6 +101,9 @@ def test_wide_batch_plans(lib):
     assert st == 0 and (p.step_path, p.step_bn_fwd, p.step_splits) == (1, 128, 4)
     st, p = plan(lib, 2048, 1024)
     assert st == 0 and (p.step_path, p.step_bn_fwd, p.step_splits) == (1, 256, 1)
+    # config 3's 2-GPU shard (B=128): 128-wide forward tiles would leave 84 SMs idle -> 128 tiles of 128 x 64
+    st, p = plan(lib, 128, 2048)
+    assert st == 0 and (p.step_path, p.step_bn_fwd, p.step_splits) == (1, 64, 8)
 
 
 def test_unsupported_shapes_are_reported(lib):

@@ -40,12 +40,13 @@ def _step(eng, inp, dev, td):
     ("f16", "tc", "forward"), ("f16", "tc", "backward"), ("bf16", "tc", "forward"),
     ("f32", "simt", "forward"), ("f32", "simt", "backward"),
     ("bf16", "tc", "forward-wide"),  # 96 sequences at H = 1024: the wide-batch forward kernel (all steps in one launch)
+    # H = 2048: W_hh is streamed, and part of it is fetched into the ring ahead of the barrier that then fails
+    ("bf16", "tc", "forward-streamed"), ("bf16", "tc", "backward-streamed"),
 ])
 def test_step_barrier_timeout_returns_and_engine_recovers(dtype, backend, where):
-    wide = where.endswith("-wide")
-    where = where.split("-")[0]
-    w = (Workload("timeout", dtype, 1, 128, 1024, 96, 4, seed=11, state_std=0.1) if wide
-         else Workload("timeout", dtype, 1, 64, 64, 8, 4, seed=11, state_std=0.1))
+    where, _, variant = where.partition("-")
+    shape = {"": (64, 64, 8), "wide": (128, 1024, 96), "streamed": (128, 2048, 8)}[variant]
+    w = Workload("timeout", dtype, 1, *shape, 4, seed=11, state_std=0.1)
     inp = make_inputs(w)
     td = TORCH_DTYPES[dtype]
     eng, dev = _engine(w, inp, backend)

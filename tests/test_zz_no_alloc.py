@@ -47,3 +47,34 @@ def test_static_bias_grad_rejects_widths_beyond_its_fixed_scratch():
     assert b"at most 16384 columns" in lib.flstm_last_error()
     st, out = _run(lib.flstm_bias_grad_static, 1, dg[:, :16384].contiguous())
     assert st == 0 and float(out.abs().max()) == 0.0
+
+
+def test_static_bias_grad_allocates_nothing_and_runs_inside_a_stream_capture():
+    """After one warm call (which looks the scratch array's address up) the entry point leaves the device's free
+    memory untouched, and it can be captured into a CUDA graph and replayed -- the use its header names."""
+    lib = _lib.load()
+    torch.manual_seed(1)
+    dg = torch.randn(2048, 2048, device="cuda").half()
+    _, want = _run(lib.flstm_bias_grad, 1, dg)
+    st, _ = _run(lib.flstm_bias_grad_static, 1, dg)  # warm call
+    assert st == 0
+    out = torch.zeros(2048, device="cuda")
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(5):
+        st = lib.flstm_bias_grad_static(1, dg.data_ptr(), 2048, 2048, 0, out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.equal(out, want)
+
+    graph = torch.cuda.CUDAGraph()
+    out.zero_()
+    with torch.cuda.graph(graph):
+        st = lib.flstm_bias_grad_static(1, dg.data_ptr(), 2048, 2048, 0, out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert st == 0, lib.flstm_last_error()
+    for _ in range(2):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want)
