@@ -668,11 +668,14 @@ def dp_check(args, eng, w, inp, P, B, dev, td, world, rank):
     from flashlstm_poc_b200.engine import Engine
     from oracle import lstm_oracle as orc
 
-    T, H, I, L = w.seq_len, w.hidden_size, w.input_size, w.layers
+    H, I, L = w.hidden_size, w.input_size, w.layers
+    # the first 128 time steps: enough BPTT depth for the check, and the CPU oracle (memory-bound on the weights
+    # at a handful of sequences) stays within tens of seconds
+    T = min(w.seq_len, 128)
     rows = list(range(max(1, 4 // world)))  # local rows whose dY is kept
-    x = inp.x.to(dev, td)
+    x = inp.x[:T].to(dev, td)
     dy = torch.zeros(T, B, H, dtype=td, device=dev)
-    dy[:, rows] = inp.dy[:, rows].to(dev, td)
+    dy[:, rows] = inp.dy[:T, rows].to(dev, td)
     eng.forward_into(T, x, None, None, None, None, None)
     eng.backward_into(T, dy, None, None, None, None, None)
     torch.cuda.synchronize()
@@ -723,7 +726,7 @@ def dp_check(args, eng, w, inp, P, B, dev, td, world, rank):
     return {"ok": bool(ok), "tensors": "dW_ih, dW_hh, db of every layer",
             "rel_l2_vs_cpu_oracle": worst_oracle, "tolerance_vs_oracle": 1e-2,
             "rel_l2_vs_sum_of_unreduced_rank_gradients": worst_sum, "tolerance_vs_sum": 1e-4,
-            "sequences_with_nonzero_dY": len(rows) * world, "oracle_seconds": oracle_s,
+            "sequences_with_nonzero_dY": len(rows) * world, "time_steps": T, "oracle_seconds": oracle_s,
             "note": "dY is zero for all other sequences of this check step, so they add nothing to dW / db"}
 
 

@@ -1,6 +1,6 @@
 """Per-time-step clock trace of the persistent recurrent kernels (tensor-core backend).
 
-    python -m flashlstm_poc_b200.step_trace [workload-name] [--steps N]
+    python -m flashlstm_poc_b200.step_trace [workload-name] [--steps N] [--batch B] [--seq-len T]
 
 CTA 0 of the forward and of the BPTT kernel stamps clock64() at fixed points of each of the first N time steps
 (flstm_engine_enable_trace / flstm_engine_read_trace in include/flashlstm_b200/engine.h).  `trace_report`
@@ -56,8 +56,11 @@ def summarize(stamps: np.ndarray, skip: int = 10) -> Dict[str, Dict[str, float]]
     return out
 
 
-def trace_report(workload: str = "c2_fp16_h1024", steps: int = 64) -> Dict[str, Dict[str, float]]:
+def trace_report(workload: str = "c2_fp16_h1024", steps: int = 64, **scale) -> Dict[str, Dict[str, float]]:
+    """`scale` (batch=, seq_len=, ...) shrinks the named workload, e.g. to one GPU's shard of its batch."""
     w = WORKLOADS[workload]
+    if scale:
+        w = w.scaled(**scale)
     inp = make_inputs(w)
     dev = torch.device("cuda", torch.cuda.current_device())
     td = TORCH_DTYPES[w.dtype]
@@ -88,5 +91,8 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("workload", nargs="?", default="c2_fp16_h1024")
     ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--seq-len", type=int, default=0)
     a = ap.parse_args()
-    trace_report(a.workload, a.steps)
+    scale = {k: v for k, v in (("batch", a.batch), ("seq_len", a.seq_len)) if v > 0}
+    trace_report(a.workload, a.steps, **scale)
