@@ -48,8 +48,14 @@ SHARDED = ("c3_bf16_l2_h2048", "c5_bf16_l4_h1024")  # the configurations the bat
 # DRAM bytes per launch of the recurrent kernels from ncu captures of small cases (dram__bytes_read.sum +
 # dram__bytes_write.sum, summaries under profiles/).  Stored figures, not measured by this run.
 STORED_TRAFFIC = {
-    ("c2_fp16_h1024", "recurrent_fwd"): {"bytes_per_timestep": 1.20e6,
+    ("c2_fp16_h1024", "recurrent_fwd"): {"bytes_per_timestep": 1.20e6, "batch_per_gpu": 64,
                                          "source": "profiles/lstm_fwd_kernel_c2_fp16_h1024_T128.md (T=128, per step)"},
+    # per-step path at 256 sequences per GPU: split-K GEMM 37.8 MB + pointwise kernel 19.9 MB per time step,
+    # each launch captured cold (caches flushed); the forward kernel keeps W_hh in L2 across its steps
+    ("c3_bf16_l2_h2048", "bptt"): {"bytes_per_timestep": 57.7e6, "batch_per_gpu": 256,
+                                   "source": "profiles/step_kernel_c3_bf16_l2_h2048_T8.md (T=8, per time step, cold launches)"},
+    ("c3_bf16_l2_h2048", "recurrent_fwd"): {"bytes_per_timestep": 12.4e6, "batch_per_gpu": 256,
+                                            "source": "profiles/step_kernel_c3_bf16_l2_h2048_T8.md (wide_fwd_kernel, T=8, per time step)"},
 }
 
 
@@ -287,6 +293,8 @@ def recurrent_roofline(w, B, plan, phase_ms, peaks, tc):
     step_path = bool(plan and plan.step_path)
     if not tc:
         kernel, per_launch_steps, launches = "simt::persistent_%s" % dom, T, L
+    elif step_path and dom == "recurrent_fwd" and os.environ.get("FLSTM_WIDE_PERSIST", "1") != "0":
+        kernel, per_launch_steps, launches = "tc::wide_fwd_kernel (all time steps of a layer in one launch)", T, L
     elif step_path:
         kernel = ("tc::step_kernel<LSTM_FWD> (one launch per time step)" if dom == "recurrent_fwd" else
                   "tc::step_bwd_pointwise_kernel + tc::step_kernel<F32_PARTS> (one pair per time step)")
@@ -305,11 +313,12 @@ def recurrent_roofline(w, B, plan, phase_ms, peaks, tc):
     else:
         achieved = dom_bytes * per_launch_steps / dur_s / 1e9 if dur_s > 0 else 0.0
         out.update(bound="hbm", achieved=achieved, peak=peaks["hbm_gbs"], unit="GB/s", frac=achieved / peaks["hbm_gbs"])
-    stored = STORED_TRAFFIC.get((w.name, dom)) or STORED_TRAFFIC.get((w.name, "recurrent_fwd"))
-    if stored:
-        key = "traffic" if (w.name, dom) in STORED_TRAFFIC else "traffic_recurrent_fwd_kernel"
-        out[key] = stored["bytes_per_timestep"] * per_launch_steps
-        out["traffic_source"] = "stored figure, " + stored["source"]
+    for key, name in (("traffic", dom), ("traffic_recurrent_fwd_kernel", "recurrent_fwd")):
+        stored = STORED_TRAFFIC.get((w.name, name))
+        if stored and stored["batch_per_gpu"] == B and (key == "traffic" or name != dom):
+            steps_per_launch = per_launch_steps if name == dom else (T if tc and not (step_path and os.environ.get("FLSTM_WIDE_PERSIST", "1") == "0") else 1)
+            out[key] = stored["bytes_per_timestep"] * steps_per_launch
+            out[key + "_source"] = "stored figure, " + stored["source"]
     return out
 
 
