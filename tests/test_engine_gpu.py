@@ -87,7 +87,9 @@ def test_scaled_baseline_configs(name, scale):
     ("bf16", 1, 3, 256, 128, 512, False, "step"),    # per-step path, inference
     ("f16", 1, 4, 40, 128, 128, True, "step"),       # per-step path with a single, mostly empty 128-row tile
     ("f16", 1, 6, 200, 192, 192, True, "auto"),      # ragged batch tile, K chunks not a multiple of 4
-    ("bf16", 2, 4, 256, 256, 1024, True, "persistent"),  # the persistent kernels with several batch tiles per CTA
+    ("bf16", 2, 4, 320, 256, 1024, True, "persistent"),  # the persistent kernels with several batch tiles per CTA: five
+                                                         # 64-wide tiles over two batch groups, one slot without sequences
+    ("f16", 1, 4, 96, 128, 2048, True, "persistent"),    # streamed weights with three 32-wide tiles per CTA
 ])
 def test_wide_and_large_batch_regimes(dtype, L, T, B, I, H, training, path, monkeypatch):
     if path == "persistent":
