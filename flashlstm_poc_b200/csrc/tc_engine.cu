@@ -190,7 +190,7 @@ int on_capacity_change(Engine &e) {
                 FLSTM_TRY(make_tensor_map_3d(&t.tm_dg3, l.dg, dg_steps, B, 4 * H, 4 * H, B * 4 * H, 128, 64, true));
             continue;
         }
-        FLSTM_TRY(make_tensor_map_chunked(&t.tm_h, l.hs, cap + 1, B, H, st->fwd.BT, st->fwd.ch));
+        FLSTM_TRY(make_tensor_map_chunked(&t.tm_h, l.hs, cap + 1, B, H, st->fwd.pair ? st->fwd.BT / 2 : st->fwd.BT, st->fwd.ch));
         FLSTM_TRY(make_tensor_map_3d(&t.tm_g, l.gates, cap, B, 4 * H, 4 * H, B * 4 * H, st->fwd.BT, 64, false));
         if (e.cfg.training && l.dg)
             FLSTM_TRY(make_tensor_map_chunked(&t.tm_dg, l.dg, dg_steps, B, 4 * H, st->bwd.BT, st->bwd.ch));

@@ -31,6 +31,7 @@ struct FwdPlan {
     int stages;    // TMA ring depth
     int ch;        // 64-wide K chunks per ring stage (one TMA copy each)
     bool resident; // W_hh slice stays in shared memory for the whole sequence
+    bool pair;     // neighbouring row-tile CTAs form cta_group::2 pairs; the h map then has BT/2 rows per box
     int smem_bytes;
     int grid;
 };
@@ -58,7 +59,7 @@ int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan);
 bool wide_tile_enabled();   // 33..64 sequences as one 64-wide batch tile when a CTA would otherwise take two
 bool wider_tile_enabled();  // 65..128 sequences as one 128-wide batch tile likewise
 // tm_w: W_hh rows tile-interleaved (4H, H), box 64x64, 128B swizzle.  tm_h: hidden states as a
-// chunked map (make_tensor_map_chunked) with box rows BT and plan.ch chunks.  tm_g: projection as
+// chunked map (make_tensor_map_chunked) with box rows BT (BT/2 for plan.pair) and plan.ch chunks.  tm_g: projection as
 // (T, B, 4H), box 1 x BT x 64, no swizzle.
 int lstm_forward_persistent(int dtype, const FwdPlan &plan, const CUtensorMap &tm_w, const CUtensorMap &tm_h,
                             const CUtensorMap &tm_g, FwdParams p, cudaStream_t s);

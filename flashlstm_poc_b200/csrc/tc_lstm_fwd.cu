@@ -53,11 +53,13 @@ struct FwdSmemLayout {
 };
 
 // One ring stage holds `ch` consecutive 64-wide K chunks of an h tile (and of W when streamed).
-__host__ __device__ inline FwdSmemLayout fwd_smem_layout(int BT, int H, int rt, bool resident, int stages, int ch) {
+// pair: the CTA is one half of a CTA pair (cta_group::2) and stages only its BT/2 sequences of every h chunk.
+__host__ __device__ inline FwdSmemLayout fwd_smem_layout(int BT, int H, int rt, bool resident, int stages, int ch,
+                                                         bool pair = false) {
     FwdSmemLayout l;
     const int kc = H / 64;
     l.w_bytes = resident ? rt * kc * kChunkBytesW : 0;
-    l.ring_stage_bytes = ch * (BT * 128 + (resident ? 0 : kChunkBytesW));
+    l.ring_stage_bytes = ch * ((pair ? BT / 2 : BT) * 128 + (resident ? 0 : kChunkBytesW));
     l.stages = stages;
     l.p_bytes = 2 * BT * 128;
     l.ex_bytes = 2 * 64 * (BT + 4) * 4;
@@ -65,7 +67,13 @@ __host__ __device__ inline FwdSmemLayout fwd_smem_layout(int BT, int H, int rt, 
     return l;
 }
 
-template <int BT, bool W_RESIDENT, bool BF16>
+// PAIR: two CTAs with neighbouring row tiles (ranks 0 and 1 of a cluster) run ONE tcgen05.mma.cta_group::2 of
+// M = 128: each keeps its own 64 rows of W_hh, but stages only HALF of the h tile (BT/2 sequences) -- the UMMA reads
+// the other half from the peer's shared memory -- so a step pulls half as many h bytes through L2 into every SM.
+// Only the leader (rank 0) issues UMMAs; both CTAs' loads are counted on the leader's barriers, its commits
+// signal both CTAs.  Each CTA finds its 64 x BT accumulator in its own tensor memory, sequences [0, BT/2) in lanes
+// 0-63 and [BT/2, BT) in lanes 64-127 (BT/2 columns).  Nothing is multicast.
+template <int BT, bool W_RESIDENT, bool BF16, bool PAIR>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_h,
                 const __grid_constant__ CUtensorMap tm_g, FwdParams p) {
@@ -73,7 +81,8 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int EXS = BT + 4;  // row stride of the exchange buffer (floats), keeps float4 alignment
     const int KC = p.H / 64, CH = p.ch, NLOAD = KC / CH;
-    const FwdSmemLayout L = fwd_smem_layout(BT, p.H, p.rt, W_RESIDENT, p.stages, CH);
+    const FwdSmemLayout L = fwd_smem_layout(BT, p.H, p.rt, W_RESIDENT, p.stages, CH, PAIR);
+    constexpr int BTH = PAIR ? BT / 2 : BT;  // sequences of an h chunk this CTA stages
     uint8_t *s_w = smem;                                   // resident W slice: rt*KC chunks of 8 KB
     uint8_t *s_ring = s_w + L.w_bytes;                     // stages x [CH h chunks | (CH W chunks)]
     uint8_t *s_p = s_ring + L.stages * L.ring_stage_bytes;  // 2 P tiles, BT rows x 128 B, not swizzled
@@ -90,7 +99,10 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     const int ng = blockIdx.x / p.cta_rows;        // batch group
     const int jr = blockIdx.x % p.cta_rows;        // first row tile = jr * rt
     unsigned int *counter = p.counters + ng;
-    constexpr int kTmemCols = (2 * BT < 32) ? 32 : 2 * BT;
+    constexpr int kAccCols = PAIR ? BT / 2 : BT;  // tensor-memory columns of one accumulator
+    constexpr int kTmemCols = (2 * kAccCols < 32) ? 32 : 2 * kAccCols;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    const bool leader = rank == 0;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < L.stages; ++i) {
@@ -99,7 +111,7 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&tfull[i], 1);
-            mbar_init(&tempty[i], 4);
+            mbar_init(&tempty[i], PAIR ? 8 : 4);  // the epilogue warps of both CTAs report to the leader
             mbar_init(&pfull[i], 1);
             mbar_init(&pempty[i], kFwdEpilogueThreads / 32);
         }
@@ -111,13 +123,32 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         tma_prefetch_desc(&tm_g);
     }
     if (warp == 5) {
-        tmem_alloc(tmem_slot, kTmemCols);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(tmem_slot, kTmemCols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, kTmemCols);
+            tmem_relinquish();
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();  // both CTAs' barriers and tensor memory exist before anything crosses the pair
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // barriers the loads of this CTA complete: its own, or (PAIR) the leader's at the same offsets
+    const uint32_t full_c = PAIR ? map_to_rank(smem_u32(full), 0) : smem_u32(full);
+    const uint32_t wbar_c = PAIR ? map_to_rank(smem_u32(wbar), 0) : smem_u32(wbar);
+    const uint32_t tempty_c = PAIR ? map_to_rank(smem_u32(tempty), 0) : smem_u32(tempty);
+    const uint32_t stage_tx = (PAIR ? 2u : 1u) * (uint32_t)L.ring_stage_bytes;
+    auto load_w = [&](void *dst, int x, int y, uint32_t bar) {  // a W_hh chunk
+        if (PAIR) tma_load_2d_pair(dst, &tm_w, x, y, bar);
+        else tma_load_2d_addr(dst, &tm_w, x, y, bar);
+    };
+    auto load_h = [&](void *dst, int b0, int chunk0, int t, uint32_t bar) {  // CH chunks of this CTA's part of an h tile
+        if (PAIR) tma_load_4d_pair(dst, &tm_h, 0, b0 + (int)rank * BTH, chunk0, t, bar);
+        else tma_load_4d_addr(dst, &tm_h, 0, b0, chunk0, t, bar);
+    };
 
     const unsigned long long wait_ns = p.wait_ns ? p.wait_ns : kWaitLimitNs;
     const int nt_count = p.nt;  // batch tiles per group
@@ -133,10 +164,10 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         if (elect_one()) {
             bool ok = true;
             if (W_RESIDENT) {
-                mbar_expect_tx(wbar, (uint32_t)(p.rt * KC * kChunkBytesW));
+                if (leader) mbar_expect_tx(wbar, (PAIR ? 2u : 1u) * (uint32_t)(p.rt * KC * kChunkBytesW));
                 for (int r = 0; r < p.rt; ++r)
                     for (int kc = 0; kc < KC; ++kc)
-                        tma_load_2d(s_w + (r * KC + kc) * kChunkBytesW, &tm_w, kc * 64, (jr * p.rt + r) * 64, wbar);
+                        load_w(s_w + (r * KC + kc) * kChunkBytesW, kc * 64, (jr * p.rt + r) * 64, wbar_c);
             }
             int stage = 0;
             uint32_t phase = 0, wi = 0;
@@ -167,12 +198,12 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                                 ok = mbar_wait(&empty[stage], phase ^ 1, abort_w, wait_ns);
                                 if (!ok) break;
                                 uint8_t *sh = s_ring + stage * L.ring_stage_bytes;
-                                mbar_expect_tx(&full[stage], (uint32_t)L.ring_stage_bytes);
+                                if (leader) mbar_expect_tx(&full[stage], stage_tx);
                                 ring_issued |= 1u << stage;
                                 ring_parity = (ring_parity & ~(1u << stage)) | (phase << stage);
                                 for (int c = 0; c < CH; ++c)
-                                    tma_load_2d(sh + CH * BT * 128 + c * kChunkBytesW, &tm_w, (ld * CH + c) * 64, j * 64,
-                                                &full[stage]);
+                                    load_w(sh + CH * BTH * 128 + c * kChunkBytesW, (ld * CH + c) * 64, j * 64,
+                                           full_c + 8u * (uint32_t)stage);
                                 pre_stage[ld] = stage;
                                 if (++stage == L.stages) { stage = 0; phase ^= 1; }
                             }
@@ -191,21 +222,21 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         if (first) FLSTM_STAMP(tt, 0);
                         first = false;
                         for (int ld = 0; ld < npre; ++ld)
-                            tma_load_4d(s_ring + pre_stage[ld] * L.ring_stage_bytes, &tm_h, 0, b0, ld * CH, t,
-                                        &full[pre_stage[ld]]);
+                            load_h(s_ring + pre_stage[ld] * L.ring_stage_bytes, b0, ld * CH, t,
+                                   full_c + 8u * (uint32_t)pre_stage[ld]);
                         for (int ld = npre; ld < NLOAD; ++ld) {
                             ok = mbar_wait(&empty[stage], phase ^ 1, abort_w, wait_ns);
                             if (!ok) break;
                             uint8_t *sh = s_ring + stage * L.ring_stage_bytes;
-                            mbar_expect_tx(&full[stage], (uint32_t)L.ring_stage_bytes);
+                            if (leader) mbar_expect_tx(&full[stage], stage_tx);
                             ring_issued |= 1u << stage;
                             ring_parity = (ring_parity & ~(1u << stage)) | (phase << stage);
                             // CH chunks of the h tile with one copy: (x, row, chunk, step)
-                            tma_load_4d(sh, &tm_h, 0, b0, ld * CH, t, &full[stage]);
+                            load_h(sh, b0, ld * CH, t, full_c + 8u * (uint32_t)stage);
                             if (!W_RESIDENT)
                                 for (int c = 0; c < CH; ++c)
-                                    tma_load_2d(sh + CH * BT * 128 + c * kChunkBytesW, &tm_w, (ld * CH + c) * 64, j * 64,
-                                                &full[stage]);
+                                    load_w(sh + CH * BTH * 128 + c * kChunkBytesW, (ld * CH + c) * 64, j * 64,
+                                           full_c + 8u * (uint32_t)stage);
                             if (++stage == L.stages) { stage = 0; phase ^= 1; }
                         }
                         FLSTM_STAMP(tt, 1);
@@ -216,29 +247,33 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             // exits.  After a normal run the consumers have already waited for all of them, so this costs nothing.
             // (a stage whose W_hh chunks went ahead of a barrier that then failed never gets its h chunks: after an
             // abort the wait for it is cut short, long after the chunks that were started have landed)
-            if (W_RESIDENT) mbar_drain(wbar, 0, wait_ns);
-            for (int i = 0; i < L.stages; ++i)
+            // (PAIR: the peer's copies complete the LEADER's barriers, which it cannot wait on; after a normal run
+            // the UMMAs have consumed them all, after an abort the whole CTA lingers before it leaves, see below)
+            if (W_RESIDENT && leader) mbar_drain(wbar, 0, wait_ns);
+            for (int i = 0; i < L.stages && leader; ++i)
                 if (ring_issued >> i & 1u) mbar_drain(&full[i], ring_parity >> i & 1u, ok ? wait_ns : kAbortDrainNs);
             for (int i = 0; i < 2; ++i)
                 if (p_issued >> i & 1u) mbar_drain(&pfull[i], p_parity >> i & 1u, wait_ns);
         }
     } else if (warp == 5) {
-        // ------------------------------------------------------------ MMA issuer
-        if (elect_one()) {
+        // ------------------------------------------------------------ MMA issuer (PAIR: the leader's only)
+        if (leader && elect_one()) {
             bool ok = true;
             if (W_RESIDENT) ok = mbar_wait(wbar, 0, abort_w, wait_ns);
             int stage = 0;
             uint32_t phase = 0, wi = 0;
             const uint32_t s_w_u32 = smem_u32(s_w), idesc = p.idesc;
+            const uint32_t empty_l = smem_u32(empty), tfull_l = smem_u32(tfull);
             const uint32_t total_items = (uint32_t)p.T * items_per_step;
             int last_commit = -1;
             for (uint32_t it = 0; it < total_items && ok; ++it, ++wi) {
                 const int r = (it % items_per_step) / nt_count;
                 const int buf = wi & 1;
-                ok = mbar_wait(&tempty[buf], ((wi >> 1) & 1) ^ 1, abort_w, wait_ns);
+                ok = PAIR ? mbar_wait_cluster(&tempty[buf], ((wi >> 1) & 1) ^ 1, abort_w, wait_ns)
+                          : mbar_wait(&tempty[buf], ((wi >> 1) & 1) ^ 1, abort_w, wait_ns);
                 if (!ok) break;
                 tcgen05_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * BT;
+                const uint32_t d_tmem = tmem_base + buf * kAccCols;
                 for (int ld = 0; ld < NLOAD; ++ld) {
                     ok = mbar_wait(&full[stage], phase, abort_w, wait_ns);
                     if (!ok) break;
@@ -248,23 +283,33 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     const uint32_t st_base = smem_u32(s_ring + stage * L.ring_stage_bytes);
                     for (int c = 0; c < CH; ++c) {
                         const int kc = ld * CH + c;
-                        const uint32_t h_base = st_base + c * BT * 128;
+                        const uint32_t h_base = st_base + c * BTH * 128;
                         const uint32_t w_base = W_RESIDENT ? s_w_u32 + (uint32_t)(r * KC + kc) * kChunkBytesW
-                                                           : st_base + CH * BT * 128 + c * kChunkBytesW;
+                                                           : st_base + CH * BTH * 128 + c * kChunkBytesW;
                         // one descriptor per chunk; the three further K steps of 16 elements advance the
                         // start-address field by 32 bytes (2 in descriptor units)
                         const uint64_t dw = umma_desc_kmajor_sw128(w_base), dh = umma_desc_kmajor_sw128(h_base);
-                        if (kc == 0) umma_f16_imm<false>(d_tmem, dw, dh, idesc);
-                        else umma_f16_imm<true>(d_tmem, dw, dh, idesc);
-                        umma_f16_imm<true>(d_tmem, dw + 2, dh + 2, idesc);
-                        umma_f16_imm<true>(d_tmem, dw + 4, dh + 4, idesc);
-                        umma_f16_imm<true>(d_tmem, dw + 6, dh + 6, idesc);
+                        if (PAIR) {
+                            umma_f16_pair(d_tmem, dw, dh, idesc, kc != 0);
+                            umma_f16_pair(d_tmem, dw + 2, dh + 2, idesc, 1u);
+                            umma_f16_pair(d_tmem, dw + 4, dh + 4, idesc, 1u);
+                            umma_f16_pair(d_tmem, dw + 6, dh + 6, idesc, 1u);
+                        } else {
+                            if (kc == 0) umma_f16_imm<false>(d_tmem, dw, dh, idesc);
+                            else umma_f16_imm<true>(d_tmem, dw, dh, idesc);
+                            umma_f16_imm<true>(d_tmem, dw + 2, dh + 2, idesc);
+                            umma_f16_imm<true>(d_tmem, dw + 4, dh + 4, idesc);
+                            umma_f16_imm<true>(d_tmem, dw + 6, dh + 6, idesc);
+                        }
                     }
-                    umma_commit(&empty[stage]);
+                    // the stage may be refilled (PAIR: in both CTAs) once these UMMAs have read it
+                    if (PAIR) umma_commit_pair_both(empty_l + 8u * (uint32_t)stage);
+                    else umma_commit(&empty[stage]);
                     if (++stage == L.stages) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
-                umma_commit(&tfull[buf]);
+                if (PAIR) umma_commit_pair_both(tfull_l + 8u * (uint32_t)buf);
+                else umma_commit(&tfull[buf]);
                 last_commit = (int)wi;
                 FLSTM_STAMP((int)(it / items_per_step), 4);
             }
@@ -311,7 +356,7 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     float *ex = s_ex + (wi & 1) * 64 * EXS;
                     // phase A (warps 0-3): lanes 0..15 of warp g hold the recurrent sums of gate g, units 0..15,
                     // all BT sequences; they go to shared memory as they are
-                    if (warp < 4) {
+                    if (warp < 4 && !PAIR) {
 #pragma unroll
                         for (int c0 = 0; c0 < BT; c0 += 32) {
                             uint32_t acc[32];
@@ -328,6 +373,28 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                         tcgen05_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&tempty[buf]);
+                    }
+                    if (warp < 4 && PAIR) {
+                        // M = 128 over the pair: lane quadrant w holds rows 32 (w & 1) + lane of this CTA's 64 and
+                        // the sequences [(w >> 1) BT/2, +BT/2); every lane carries a row
+                        const int row = 32 * (warp & 1) + lane, seq0 = (warp >> 1) * (BT / 2);
+                        constexpr int W16 = (BT / 2 < 32) ? 16 : 32;  // columns per tensor-memory load
+#pragma unroll
+                        for (int c0 = 0; c0 < BT / 2; c0 += W16) {
+                            uint32_t acc[W16];
+                            const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * kAccCols + c0;
+                            if (W16 == 16) tmem_ld_32x32b_x16(taddr, *reinterpret_cast<uint32_t(*)[16]>(&acc[0]));
+                            else tmem_ld_32x32b_x32(taddr, *reinterpret_cast<uint32_t(*)[32]>(&acc[0]));
+                            tmem_ld_wait();
+                            float4 *dst = reinterpret_cast<float4 *>(ex + row * EXS + seq0 + c0);
+#pragma unroll
+                            for (int i = 0; i < W16 / 4; ++i)
+                                dst[i] = make_float4(__uint_as_float(acc[4 * i]), __uint_as_float(acc[4 * i + 1]),
+                                                     __uint_as_float(acc[4 * i + 2]), __uint_as_float(acc[4 * i + 3]));
+                        }
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster_relaxed(tempty_c + 8u * (uint32_t)buf);
                     }
                     if (good) good = mbar_wait(&pfull[pb], (wi >> 1) & 1, abort_w, wait_ns);
                     if (named_barrier_or(1, kFwdEpilogueThreads, !good)) {
@@ -390,29 +457,49 @@ lstm_fwd_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     }
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 5) tmem_dealloc(tmem_base, kTmemCols);
+    if (PAIR) {
+        // after an abort this CTA's own copies may still be landing on barriers it cannot see (the leader's)
+        if (*abort_w) {
+            const unsigned long long t0 = global_timer_ns();
+            while (global_timer_ns() - t0 < kAbortDrainNs) {}
+        }
+        cluster_sync_all();  // the peer's shared and tensor memory stay valid until the leader's last UMMA is consumed
+        if (warp == 5) tmem_dealloc_pair(tmem_base, kTmemCols);
+    } else if (warp == 5) {
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
     if (threadIdx.x == 0 && *abort_w) atomicCAS(p.err, 0u, 1u);
 }
 
 // ------------------------------------------------------------------ host launcher
-template <int BT, bool RES, bool BF16>
+template <int BT, bool RES, bool BF16, bool PAIR>
 static int launch_fwd(const CUtensorMap &tw, const CUtensorMap &th, const CUtensorMap &tg, const FwdParams &p, int grid,
                       int smem_bytes, cudaStream_t s) {
-    auto kern = lstm_fwd_kernel<BT, RES, BF16>;
+    auto kern = lstm_fwd_kernel<BT, RES, BF16, PAIR>;
     FLSTM_CUDA_TRY(ensure_smem_limit(kern, (size_t)smem_bytes));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kFwdThreads);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeCooperative;  // all CTAs must be co-resident: they wait on one another
     attr[0].val.cooperative = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;  // PAIR: neighbouring row tiles form a cluster of two
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = PAIR ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, th, tg, p);
     if (e != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "recurrent forward launch failed: %s", cudaGetErrorString(e));
     return FLSTM_OK;
+}
+
+// FLSTM_FWD_PAIR=0: no CTA pairs in the forward kernel; =1: pairs wherever the shape allows them
+static int fwd_pair_mode() {
+    const char *env = std::getenv("FLSTM_FWD_PAIR");
+    return !env ? -1 : (env[0] == '0' ? 0 : 1);
 }
 
 // FLSTM_BT64=0 keeps 32-wide batch tiles for 33..64 sequences (two tiles per CTA when H >= 2048)
@@ -467,6 +554,14 @@ int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan) {
         }
         if (!found) split(BT);
     }
+    // CTA pairs (each CTA stages half of the h tile) need an even number of row-tile CTAs per batch group: the two
+    // CTAs of a pair share a batch tile.  They pay where a step is bound by what the SMs pull through L2 --
+    // streamed weights (H = 2048, 32 / 64 sequences: forward 13.1 -> 12.3 / 15.7 -> 14.0 ms per config-3 shard
+    // step) and wide tiles (256 sequences at H = 1024: 8.3 -> 7.9 ms) -- and measured neutral on the latency-bound
+    // 32-wide resident case (config 2) and slower with two row tiles per CTA (H = 4096: 47.7 -> 48.8 ms).
+    const int pair_mode = fwd_pair_mode();
+    const bool pair_pays = rt == 1 && ((size_t)(H / 64) * kChunkBytesW > 128 * 1024 || BT >= 64);
+    const bool pair = cta_rows % 2 == 0 && (pair_mode == 1 || (pair_mode < 0 && pair_pays));
     // One TMA copy brings `ch` 64-wide K chunks of an h tile; the ring holds a whole tile when it can.
     // The W_hh slice stays resident if it fits next to a ring of at least two stages.
     const int kc = H / 64;
@@ -475,35 +570,36 @@ int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan) {
     // (measured: the streamed-weight and multi-tile regimes need several smaller stages in flight instead)
     int ch16 = 16;
     while (kc % ch16) --ch16;
-    const bool one_tile_resident = nt == 1 && (size_t)fwd_smem_layout(BT, H, rt, true, kc / ch16, ch16).total <= smem_limit;
+    const bool one_tile_resident = nt == 1 && (size_t)fwd_smem_layout(BT, H, rt, true, kc / ch16, ch16, pair).total <= smem_limit;
     int ch = one_tile_resident ? 16 : 4;
     if (const char *env = std::getenv("FLSTM_CH")) ch = std::atoi(env) > 0 ? std::atoi(env) : ch;
     while (kc % ch) --ch;
     bool resident = true;
     int stages = kc / ch;
-    FwdSmemLayout l = fwd_smem_layout(BT, H, rt, true, stages, ch);
-    while ((size_t)l.total > smem_limit && stages > 2) l = fwd_smem_layout(BT, H, rt, true, --stages, ch);
+    FwdSmemLayout l = fwd_smem_layout(BT, H, rt, true, stages, ch, pair);
+    while ((size_t)l.total > smem_limit && stages > 2) l = fwd_smem_layout(BT, H, rt, true, --stages, ch, pair);
     if ((size_t)l.total > smem_limit || (stages < 2 && kc / ch >= 2)) {
         resident = false;
         stages = kc / ch < 4 ? kc / ch : 4;
-        l = fwd_smem_layout(BT, H, rt, false, stages, ch);
-        while ((size_t)l.total > smem_limit && stages > 1) l = fwd_smem_layout(BT, H, rt, false, --stages, ch);
+        l = fwd_smem_layout(BT, H, rt, false, stages, ch, pair);
+        while ((size_t)l.total > smem_limit && stages > 1) l = fwd_smem_layout(BT, H, rt, false, --stages, ch, pair);
         // a single stage cannot overlap the copy with the UMMAs: rather two stages of half the chunks
         while (stages < 2 && ch > 1 && kc / (ch / 2) >= 2) {
             ch /= 2;
             stages = 2;
-            l = fwd_smem_layout(BT, H, rt, false, stages, ch);
+            l = fwd_smem_layout(BT, H, rt, false, stages, ch, pair);
             if ((size_t)l.total > smem_limit) stages = 1;
         }
-        l = fwd_smem_layout(BT, H, rt, false, stages, ch);
+        l = fwd_smem_layout(BT, H, rt, false, stages, ch, pair);
         while ((size_t)l.total > smem_limit && ch > 1) {
             --ch;
             while (kc % ch) --ch;
-            l = fwd_smem_layout(BT, H, rt, false, stages, ch);
+            l = fwd_smem_layout(BT, H, rt, false, stages, ch, pair);
         }
         if ((size_t)l.total > smem_limit) return set_error(FLSTM_ERR_UNSUPPORTED, "recurrent kernel does not fit shared memory");
     }
     plan->ch = ch;
+    plan->pair = pair;
     plan->BT = BT;
     plan->rt = rt;
     plan->cta_rows = cta_rows;
@@ -524,11 +620,15 @@ int lstm_forward_persistent(int dtype, const FwdPlan &plan, const CUtensorMap &t
     p.nt = plan.nt;
     p.stages = plan.stages;
     p.ch = plan.ch;
-    p.idesc = umma_idesc_f16(64, plan.BT, bf16 ? 1 : 0, 0, 0);
-#define FLSTM_FWD_CASE(BT_, RES_)                                                                              \
-    if (plan.BT == BT_ && plan.resident == RES_)                                                               \
-        return bf16 ? launch_fwd<BT_, RES_, true>(tm_w, tm_h, tm_g, p, plan.grid, plan.smem_bytes, s)          \
-                    : launch_fwd<BT_, RES_, false>(tm_w, tm_h, tm_g, p, plan.grid, plan.smem_bytes, s);
+    p.idesc = umma_idesc_f16(plan.pair ? 128 : 64, plan.BT, bf16 ? 1 : 0, 0, 0);
+#define FLSTM_FWD_CASE(BT_, RES_)                                                                                  \
+    if (plan.BT == BT_ && plan.resident == RES_) {                                                                 \
+        if (plan.pair)                                                                                             \
+            return bf16 ? launch_fwd<BT_, RES_, true, true>(tm_w, tm_h, tm_g, p, plan.grid, plan.smem_bytes, s)    \
+                        : launch_fwd<BT_, RES_, false, true>(tm_w, tm_h, tm_g, p, plan.grid, plan.smem_bytes, s);  \
+        return bf16 ? launch_fwd<BT_, RES_, true, false>(tm_w, tm_h, tm_g, p, plan.grid, plan.smem_bytes, s)       \
+                    : launch_fwd<BT_, RES_, false, false>(tm_w, tm_h, tm_g, p, plan.grid, plan.smem_bytes, s);     \
+    }
     FLSTM_FWD_CASE(32, true)
     FLSTM_FWD_CASE(32, false)
     FLSTM_FWD_CASE(64, true)
