@@ -477,7 +477,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     if (c + 64 >= BN) {  // accumulator drained: the leader may start the tile after next
                         tcgen05_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive_cluster(tempty0 + 8u * (uint32_t)buf);
+                        if (lane == 0) mbar_arrive_cluster_relaxed(tempty0 + 8u * (uint32_t)buf);
                     }
                     const int n_valid = N - (n0 + c);
                     if (row0 >= M || n_valid <= 0) continue;
@@ -509,7 +509,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             }
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(tempty0 + 8u * (uint32_t)buf);
+            if (lane == 0) mbar_arrive_cluster_relaxed(tempty0 + 8u * (uint32_t)buf);
         }
         if (TMA_OUT && lane == 0) tma_store_wait_all<0>();
     }
@@ -643,9 +643,11 @@ int gemm(int dtype, int out_dtype, size_t M, size_t N, size_t K, const void *A, 
         return set_error(FLSTM_ERR_UNSUPPORTED, "tensor-core GEMM needs 16-byte aligned operands and row pitches");
     const int BN = (N > 128) ? 256 : 128;
     GemmArgs g{};
-    // measured on B200 (bf16): pairs win for K-major A with 16-bit output from K = 2048 on (projection 1465 -> 1529,
-    // input gradient 1304 -> 1451 TFLOP/s, 8192^3 1159 -> 1377); with short K the 256-wide epilogue of both CTAs is
-    // the bottleneck (K = 1024: 1218 -> 753) and the MN-major weight-gradient form does not gain (1367 -> 1230)
+    // measured on B200 (bf16) inside the engine's step: pairs win for K-major A from K = 2048 on (config 3:
+    // projection 1465 -> 1529, input gradient 1507 -> 1540 TFLOP/s; 8192^3 1159 -> 1377).  With K = 1024 and the
+    // bias epilogue (every projection) they lose (config 5: 12.8 -> 20.5 ms per step, 1351 -> 790 TFLOP/s in
+    // isolation; without a bias the same shape gains, 1036 -> 1275), and the MN-major weight-gradient form is
+    // neutral in isolation (1158 -> 1205) and 2 % slower inside the step, so both stay on lone CTAs.
     g.pair = pair_enabled() && !a_mn && K >= 2048 && M >= 256 && N % 256 == 0 && sms >= 2;
     if (pair_forced()) g.pair = M >= 256 && N % 256 == 0 && sms >= 2;
     // K-major: (rows, K) with K contiguous, box rows x 64.  MN-major: stored (K, rows), 64 x 64 boxes.

@@ -496,10 +496,10 @@ static int launch_fwd(const CUtensorMap &tw, const CUtensorMap &th, const CUtens
     return FLSTM_OK;
 }
 
-// FLSTM_FWD_PAIR=0: no CTA pairs in the forward kernel; =1: pairs wherever the shape allows them
+// FLSTM_FWD_PAIR=0: no CTA pairs in the forward kernel
 static int fwd_pair_mode() {
     const char *env = std::getenv("FLSTM_FWD_PAIR");
-    return !env ? -1 : (env[0] == '0' ? 0 : 1);
+    return (env && env[0] == '0') ? 0 : 1;
 }
 
 // FLSTM_BT64=0 keeps 32-wide batch tiles for 33..64 sequences (two tiles per CTA when H >= 2048)
@@ -555,13 +555,10 @@ int plan_fwd(int B, int H, int sms, size_t smem_limit, FwdPlan *plan) {
         if (!found) split(BT);
     }
     // CTA pairs (each CTA stages half of the h tile) need an even number of row-tile CTAs per batch group: the two
-    // CTAs of a pair share a batch tile.  They pay where a step is bound by what the SMs pull through L2 --
-    // streamed weights (H = 2048, 32 / 64 sequences: forward 13.1 -> 12.3 / 15.7 -> 14.0 ms per config-3 shard
-    // step) and wide tiles (256 sequences at H = 1024: 8.3 -> 7.9 ms) -- and measured neutral on the latency-bound
-    // 32-wide resident case (config 2) and slower with two row tiles per CTA (H = 4096: 47.7 -> 48.8 ms).
-    const int pair_mode = fwd_pair_mode();
-    const bool pair_pays = rt == 1 && ((size_t)(H / 64) * kChunkBytesW > 128 * 1024 || BT >= 64);
-    const bool pair = cta_rows % 2 == 0 && (pair_mode == 1 || (pair_mode < 0 && pair_pays));
+    // CTAs of a pair share a batch tile.  Measured forward phases, lone CTAs -> pairs: config 2 2.05 -> 1.83 ms;
+    // config 3 at 16 / 32 / 64 sequences per GPU 12.7 -> 10.6 / 13.1 -> 10.9 / 15.7 -> 12.4 ms; config 5 at 256
+    // sequences 8.3 -> 7.3 ms; config 4 (two row tiles per CTA, HBM-bound) 47.7 -> 47.1 ms.
+    const bool pair = cta_rows % 2 == 0 && fwd_pair_mode() != 0;
     // One TMA copy brings `ch` 64-wide K chunks of an h tile; the ring holds a whole tile when it can.
     // The W_hh slice stays resident if it fits next to a ring of at least two stages.
     const int kc = H / 64;
