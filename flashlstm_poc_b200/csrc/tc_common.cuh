@@ -147,6 +147,12 @@ __device__ __forceinline__ void tma_load_2d_addr(void *smem_dst, const CUtensorM
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_addr(void *smem_dst, const CUtensorMap *m, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
 __device__ __forceinline__ void tma_load_4d_addr(void *smem_dst, const CUtensorMap *m, int x, int y, int z, int w, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"

@@ -182,7 +182,7 @@ int on_capacity_change(Engine &e) {
         FLSTM_TRY(make_tensor_map_2d(&t.tm_w, l.w_hh, 4 * H, H, H, 64, 64, true));
         if (st->step.use) {
             FLSTM_TRY(make_tensor_map_3d(&t.tm_hs3, l.hs, cap + 1, B, H, H, B * H, 128, 64, true));
-            FLSTM_TRY(make_tensor_map_2d(&t.tm_wstep, l.w_hh, 4 * H, H, H, st->step.pair ? st->step.bn_fwd / 2 : st->step.bn_fwd, 64, true));
+            FLSTM_TRY(make_tensor_map_2d(&t.tm_wstep, l.w_hh, 4 * H, H, H, (st->step.pair || st->step.fwd_pair) ? st->step.bn_fwd / 2 : st->step.bn_fwd, 64, true));
             FLSTM_TRY(make_tensor_map_3d_tile(&t.tm_g_ep, l.gates, 2, cap, B, 4 * H, 32, 64));
             FLSTM_TRY(make_tensor_map_3d_tile(&t.tm_c_ep, l.cs, 4, cap + 1, B, H, 32, 16));
             FLSTM_TRY(make_tensor_map_3d_tile(&t.tm_h_ep, l.hs, 2, cap + 1, B, H, 32, 16));

@@ -475,12 +475,14 @@ struct WideFwdArgs {
     unsigned int extra_arrivals;  // self-test of the timeout path: arrivals nobody makes
 };
 
-template <int BN, bool BF16>
+template <int BN, bool BF16, bool PAIR>
 __global__ void __launch_bounds__(kStepThreads, 1)
 wide_fwd_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_c,
                 const __grid_constant__ CUtensorMap tm_h, const __grid_constant__ CUtensorMap tm_y, const WideFwdArgs a) {
-    using S = StepShape<BN, EPI_LSTM_FWD, false>;
+    using S = StepShape<BN, EPI_LSTM_FWD, PAIR>;
+    constexpr int BNB = PAIR ? BN / 2 : BN;  // rows of W_hh this CTA stages per K block
+    constexpr int BMT = PAIR ? 2 * BM : BM;  // sequences of a tile (both CTAs of a pair)
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *epi = smem + S::kStages * S::kStageBytes;
@@ -492,6 +494,10 @@ wide_fwd_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     volatile uint32_t *abort_w = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    const bool leader = rank == 0;
+    // tiles are dealt to CTAs (lone) or to CTA pairs
+    const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     const unsigned long long wait_ns = a.wait_ns ? a.wait_ns : kWaitLimitNs;
     if (threadIdx.x == 0) {
         for (int i = 0; i < S::kStages; ++i) {
@@ -500,7 +506,7 @@ wide_fwd_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&tfull[i], 1);
-            mbar_init(&tempty[i], 4);
+            mbar_init(&tempty[i], PAIR ? 8 : 4);  // PAIR: the leader's barrier takes both CTAs' epilogue warps
         }
         for (int i = 0; i < 8; ++i) mbar_init(&ldbars[i], 1);
         *abort_w = 0;
@@ -512,17 +518,34 @@ wide_fwd_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         tma_prefetch_desc(&tm_h);
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, S::kTmemCols);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(tmem_slot, S::kTmemCols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, S::kTmemCols);
+            tmem_relinquish();
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();  // both CTAs' barriers and tensor memory exist before anything crosses the pair
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // the barriers this CTA's operand copies complete: its own, or (PAIR) the leader's at the same offsets
+    const uint32_t full_c = PAIR ? map_to_rank(smem_u32(full), 0) : smem_u32(full);
+    const uint32_t stage_tx = (PAIR ? 2u : 1u) * (uint32_t)S::kStageBytes;
+    auto load_a = [&](void *dst, int x, int y, int z, uint32_t bar) {
+        if (PAIR) tma_load_3d_pair(dst, &tm_a, x, y, z, bar);
+        else tma_load_3d_addr(dst, &tm_a, x, y, z, bar);
+    };
+    auto load_b = [&](void *dst, int x, int y, uint32_t bar) {
+        if (PAIR) tma_load_2d_pair(dst, &tm_b, x, y, bar);
+        else tma_load_2d_addr(dst, &tm_b, x, y, bar);
+    };
 
-    const int num_m = (a.M + BM - 1) / BM, num_n = a.N / BN;
+    const int num_m = (a.M + BMT - 1) / BMT, num_n = a.N / BN;
     const int tiles = num_m * num_n, kblocks = a.K / BK;
-    const int my_tiles = (tiles > (int)blockIdx.x) ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int my_tiles = (tiles > worker) ? (tiles - worker + workers - 1) / workers : 0;
     // k-blocks a CTA streams per step, in order: tile after tile
     const int blocks_per_step = my_tiles * kblocks;
 
@@ -533,9 +556,9 @@ wide_fwd_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             uint32_t issued = 0, parity = 0;  // the last copy started into every stage (drained on the way out)
             bool ok = true;
             auto coords = [&](int blk, int &m0, int &n0, int &kb) {
-                const int tile = blockIdx.x + (blk / kblocks) * gridDim.x;
-                m0 = (tile / num_n) * BM;
-                n0 = (tile % num_n) * BN;
+                const int tile = worker + (blk / kblocks) * workers;
+                m0 = (tile / num_n) * BMT + (int)rank * BM;
+                n0 = (tile % num_n) * BN + (int)rank * BNB;
                 kb = blk % kblocks;
             };
             for (int tt = 0; tt < a.nsteps && ok; ++tt) {
@@ -549,10 +572,10 @@ wide_fwd_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     ok = mbar_wait(&empty[stage], phase ^ 1, abort_w, wait_ns);
                     if (!ok) break;
                     uint8_t *sb = smem + stage * S::kStageBytes + S::kABytes;
-                    mbar_expect_tx(&full[stage], S::kStageBytes);
+                    if (leader) mbar_expect_tx(&full[stage], stage_tx);
                     issued |= 1u << stage;
                     parity = (parity & ~(1u << stage)) | (phase << stage);
-                    tma_load_2d(sb, &tm_b, kb * BK, n0, &full[stage]);
+                    load_b(sb, kb * BK, n0, full_c + 8u * (uint32_t)stage);
                     pre_stage[b] = stage;
                     if (++stage == S::kStages) { stage = 0; phase ^= 1; }
                 }
@@ -566,7 +589,7 @@ wide_fwd_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 for (int b = 0; b < npre; ++b) {
                     int m0, n0, kb;
                     coords(b, m0, n0, kb);
-                    tma_load_3d(smem + pre_stage[b] * S::kStageBytes, &tm_a, kb * BK, m0, t, &full[pre_stage[b]]);
+                    load_a(smem + pre_stage[b] * S::kStageBytes, kb * BK, m0, t, full_c + 8u * (uint32_t)pre_stage[b]);
                 }
                 // 3. the rest of the step
                 for (int b = npre; b < blocks_per_step && ok; ++b) {
@@ -575,21 +598,24 @@ wide_fwd_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     ok = mbar_wait(&empty[stage], phase ^ 1, abort_w, wait_ns);
                     if (!ok) break;
                     uint8_t *sa = smem + stage * S::kStageBytes, *sb = sa + S::kABytes;
-                    mbar_expect_tx(&full[stage], S::kStageBytes);
+                    if (leader) mbar_expect_tx(&full[stage], stage_tx);
                     issued |= 1u << stage;
                     parity = (parity & ~(1u << stage)) | (phase << stage);
-                    tma_load_3d(sa, &tm_a, kb * BK, m0, t, &full[stage]);
-                    tma_load_2d(sb, &tm_b, kb * BK, n0, &full[stage]);
+                    load_a(sa, kb * BK, m0, t, full_c + 8u * (uint32_t)stage);
+                    load_b(sb, kb * BK, n0, full_c + 8u * (uint32_t)stage);
                     if (++stage == S::kStages) { stage = 0; phase ^= 1; }
                 }
             }
             // way out: every copy this thread started has landed before the CTA exits.  A stage whose W_hh block was
             // fetched ahead of a barrier that then failed never gets its h block: that wait runs into its limit.
-            for (int i = 0; i < S::kStages; ++i)
+            // (PAIR: the peer's copies complete the LEADER's barriers, which it cannot wait on; after a normal run the
+            // UMMAs have consumed them all, after an abort the whole CTA lingers before it leaves)
+            for (int i = 0; i < S::kStages && leader; ++i)
                 if (issued >> i & 1u) mbar_drain(&full[i], parity >> i & 1u, ok ? wait_ns : kAbortDrainNs);
         }
     } else if (warp == 1) {
-        if (elect_one()) {
+        if (leader && elect_one()) {
+            const uint32_t empty_l = smem_u32(empty), tfull_l = smem_u32(tfull);
             int stage = 0;
             uint32_t phase = 0;
             int it = 0, last_commit = -1;
@@ -597,7 +623,8 @@ wide_fwd_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             for (int tt = 0; tt < a.nsteps && ok; ++tt) {
                 for (int i = 0; i < my_tiles && ok; ++i, ++it) {
                     const int buf = it & 1;
-                    ok = mbar_wait(&tempty[buf], ((it >> 1) & 1) ^ 1, abort_w, wait_ns);
+                    ok = PAIR ? mbar_wait_cluster(&tempty[buf], ((it >> 1) & 1) ^ 1, abort_w, wait_ns)
+                              : mbar_wait(&tempty[buf], ((it >> 1) & 1) ^ 1, abort_w, wait_ns);
                     if (!ok) break;
                     tcgen05_fence_after();
                     const uint32_t d_tmem = tmem_base + buf * BN;
@@ -607,14 +634,21 @@ wide_fwd_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         tcgen05_fence_after();
                         const uint32_t a_base = smem_u32(smem + stage * S::kStageBytes), b_base = a_base + S::kABytes;
 #pragma unroll
-                        for (int k = 0; k < BK / 16; ++k)
-                            umma_f16(d_tmem, umma_desc_kmajor_sw128(a_base + k * 32), umma_desc_kmajor_sw128(b_base + k * 32),
-                                     a.idesc, (kb | k) != 0);
-                        umma_commit(&empty[stage]);
+                        for (int k = 0; k < BK / 16; ++k) {
+                            if (PAIR)
+                                umma_f16_pair(d_tmem, umma_desc_kmajor_sw128(a_base + k * 32),
+                                              umma_desc_kmajor_sw128(b_base + k * 32), a.idesc, (kb | k) != 0);
+                            else
+                                umma_f16(d_tmem, umma_desc_kmajor_sw128(a_base + k * 32),
+                                         umma_desc_kmajor_sw128(b_base + k * 32), a.idesc, (kb | k) != 0);
+                        }
+                        if (PAIR) umma_commit_pair_both(empty_l + 8u * (uint32_t)stage);
+                        else umma_commit(&empty[stage]);
                         if (++stage == S::kStages) { stage = 0; phase ^= 1; }
                     }
                     if (!ok) break;
-                    umma_commit(&tfull[buf]);
+                    if (PAIR) umma_commit_pair_both(tfull_l + 8u * (uint32_t)buf);
+                    else umma_commit(&tfull[buf]);
                     last_commit = it;
                 }
             }
@@ -627,9 +661,10 @@ wide_fwd_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         uint8_t *sH = wb + 2 * kEpiPBytes + 2 * kEpiCBytes;
         uint64_t *ldbar = ldbars + q * 2;
         const int items_per_step = my_tiles * kGroups;
+        const uint32_t tempty_c = PAIR ? map_to_rank(smem_u32(tempty), 0) : 0u;
         auto item_coords = [&](int idx, int &row0, int &col0) {  // idx within a step
-            const int tl = blockIdx.x + (idx / kGroups) * gridDim.x;
-            row0 = (tl / num_n) * BM + q * 32;
+            const int tl = worker + (idx / kGroups) * workers;
+            row0 = (tl / num_n) * BMT + (int)rank * BM + q * 32;
             col0 = (tl % num_n) * BN + (idx % kGroups) * 64;
         };
         // Items (tile, 64-column unit group) are numbered through the whole launch: item n stages its tiles in
@@ -676,7 +711,10 @@ wide_fwd_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     if (g == kGroups - 1) {  // the accumulator is in registers: hand it back to the UMMA warp
                         tcgen05_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(&tempty[tbuf]);
+                        if (lane == 0) {
+                            if (PAIR) mbar_arrive_cluster_relaxed(tempty_c + 8u * (uint32_t)tbuf);
+                            else mbar_arrive(&tempty[tbuf]);
+                        }
                     }
                     if (row0 >= a.M || !good) continue;
                     good = __all_sync(0xffffffffu, mbar_wait(&ldbar[buf], (ldphase >> buf) & 1u, abort_w, wait_ns));
@@ -712,7 +750,17 @@ wide_fwd_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     }
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, S::kTmemCols);
+    if (PAIR) {
+        // after an abort this CTA's own copies may still be landing on barriers it cannot see (the leader's)
+        if (*abort_w) {
+            const unsigned long long t0 = global_timer_ns();
+            while (global_timer_ns() - t0 < kAbortDrainNs) {}
+        }
+        cluster_sync_all();  // the peer's shared and tensor memory stay valid until the leader's last UMMA is consumed
+        if (warp == 1) tmem_dealloc_pair(tmem_base, S::kTmemCols);
+    } else if (warp == 1) {
+        tmem_dealloc(tmem_base, S::kTmemCols);
+    }
     if (threadIdx.x == 0 && *abort_w) atomicCAS(a.err, 0u, 1u);
 }
 
@@ -873,9 +921,20 @@ int plan_step(int B, int H, int sms, size_t smem_limit, StepPlan *plan) {
         need_bwd = plan->bn_bwd == 256 ? StepShape<256, EPI_F32_PARTS, false>::kSmemBytes : StepShape<128, EPI_F32_PARTS, false>::kSmemBytes;
     }
     if (need_fwd > smem_limit || need_bwd > smem_limit) plan->use = false;  // the step kernels do not fit this device
-    // forward: all steps of a range in one cooperative launch (lone-CTA tiles); FLSTM_WIDE_PERSIST=0 = one launch per step
+    // forward: all steps of a range in one cooperative launch; FLSTM_WIDE_PERSIST=0 = one launch per step
     const char *wp = std::getenv("FLSTM_WIDE_PERSIST");
     plan->fwd_persistent = plan->use && !plan->pair && !(wp && wp[0] == '0');
+    // ... on CTA pairs from 256 sequences on (the forward tile width is then chosen for pairs; FLSTM_WIDE_PAIR=0 keeps
+    // lone CTAs).  Measured forward phases, lone -> pairs: config 3 33.5-35.0 -> 31.9-32.1 ms, config 5 26.7 -> 24.6 ms.
+    const char *wpair = std::getenv("FLSTM_WIDE_PAIR");
+    const char *wave = std::getenv("FLSTM_WAVE_CHUNK");  // the cross-layer wavefront launches per step (lone CTAs)
+    plan->fwd_pair = plan->fwd_persistent && B >= 2 * BM && sms >= 2 && !(wpair && wpair[0] == '0') &&
+                     !(wave && std::atoi(wave) > 0);
+    if (plan->fwd_pair) {
+        plan->bn_fwd = pick_bn((B + 2 * BM - 1) / (2 * BM), 4 * H, 1, sms, true);
+        const size_t need = plan->bn_fwd == 256 ? StepShape<256, EPI_LSTM_FWD, true>::kSmemBytes : StepShape<128, EPI_LSTM_FWD, true>::kSmemBytes;
+        if (need > smem_limit) plan->fwd_pair = false, plan->bn_fwd = pick_bn(m_tiles, 4 * H, 1, sms, plan->pair, true);
+    }
     return FLSTM_OK;
 }
 
@@ -904,22 +963,27 @@ int lstm_step_forward(int dtype, const StepPlan &plan, const StepFwdMaps &m, con
                 : launch_step<128, EPI_LSTM_FWD, false, false>(plan.pair, *m.hs, *m.w, em, a, sms, s);
 }
 
-template <int BN, bool BF16>
+template <int BN, bool BF16, bool PAIR>
 static int launch_wide_fwd(const StepFwdMaps &m, const WideFwdArgs &a, int sms, cudaStream_t s) {
-    using S = StepShape<BN, EPI_LSTM_FWD, false>;
-    auto kern = wide_fwd_kernel<BN, BF16>;
+    using S = StepShape<BN, EPI_LSTM_FWD, PAIR>;
+    auto kern = wide_fwd_kernel<BN, BF16, PAIR>;
     FLSTM_CUDA_TRY(ensure_smem_limit(kern, (size_t)S::kSmemBytes));
-    const int tiles = ((a.M + BM - 1) / BM) * (a.N / BN);
+    const int rows = PAIR ? 2 * BM : BM, workers = PAIR ? sms / 2 : sms;
+    const int tiles = ((a.M + rows - 1) / rows) * (a.N / BN);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(tiles < sms ? tiles : sms);
+    cfg.gridDim = dim3((tiles < workers ? tiles : workers) * (PAIR ? 2 : 1));
     cfg.blockDim = dim3(kStepThreads);
     cfg.dynamicSmemBytes = S::kSmemBytes;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeCooperative;  // the CTAs wait on one another: all of them must be resident
     attr[0].val.cooperative = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;  // PAIR: clusters of two
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = PAIR ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *m.hs, *m.w, *m.gates, *m.cs, *m.hs_out, m.y ? *m.y : *m.hs_out, a);
     if (e != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "wide-batch forward launch failed: %s", cudaGetErrorString(e));
     return FLSTM_OK;
@@ -933,16 +997,23 @@ int lstm_wide_forward(int dtype, const StepPlan &plan, const StepFwdMaps &m, con
     a.K = p.H;
     a.t0 = p.t0;
     a.nsteps = p.nsteps;
-    a.idesc = umma_idesc_f16(BM, plan.bn_fwd, bf16 ? 1 : 0, 0, 0);
+    a.idesc = umma_idesc_f16(plan.fwd_pair ? 2 * BM : BM, plan.bn_fwd, bf16 ? 1 : 0, 0, 0);
     a.err = p.err;
     a.counter = p.counter;
     a.has_y = m.y ? 1 : 0;
     a.store_gates = p.store_gates;
     a.wait_ns = p.wait_ns;
     a.extra_arrivals = p.extra_arrivals;
-    if (plan.bn_fwd == 256) return bf16 ? launch_wide_fwd<256, true>(m, a, sms, s) : launch_wide_fwd<256, false>(m, a, sms, s);
-    if (plan.bn_fwd == 64) return bf16 ? launch_wide_fwd<64, true>(m, a, sms, s) : launch_wide_fwd<64, false>(m, a, sms, s);
-    return bf16 ? launch_wide_fwd<128, true>(m, a, sms, s) : launch_wide_fwd<128, false>(m, a, sms, s);
+    if (plan.fwd_pair) {
+        if (plan.bn_fwd == 256)
+            return bf16 ? launch_wide_fwd<256, true, true>(m, a, sms, s) : launch_wide_fwd<256, false, true>(m, a, sms, s);
+        return bf16 ? launch_wide_fwd<128, true, true>(m, a, sms, s) : launch_wide_fwd<128, false, true>(m, a, sms, s);
+    }
+    if (plan.bn_fwd == 256)
+        return bf16 ? launch_wide_fwd<256, true, false>(m, a, sms, s) : launch_wide_fwd<256, false, false>(m, a, sms, s);
+    if (plan.bn_fwd == 64)
+        return bf16 ? launch_wide_fwd<64, true, false>(m, a, sms, s) : launch_wide_fwd<64, false, false>(m, a, sms, s);
+    return bf16 ? launch_wide_fwd<128, true, false>(m, a, sms, s) : launch_wide_fwd<128, false, false>(m, a, sms, s);
 }
 
 int lstm_step_backward_gemm(int dtype, const StepPlan &plan, const CUtensorMap &tm_dg, const CUtensorMap &tm_w64, int t,
