@@ -48,7 +48,7 @@ class TcPlanInfo(ctypes.Structure):
         "fwd_stages", "fwd_chunks_per_stage", "fwd_weights_resident", "fwd_smem_bytes",
         "bwd_batch_tile", "bwd_cluster_size", "bwd_grid", "bwd_batch_groups", "bwd_tiles_per_group",
         "bwd_stages", "bwd_chunks_per_stage", "bwd_weights_resident", "bwd_smem_bytes",
-        "step_path", "step_bn_fwd", "step_bn_bwd", "step_splits", "step_pair")]
+        "step_path", "step_bn_fwd", "step_bn_bwd", "step_splits", "step_pair", "fwd_pair", "step_fwd_pair")]
 
 
 class LstmBuffers(ctypes.Structure):

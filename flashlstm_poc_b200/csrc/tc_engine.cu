@@ -485,10 +485,12 @@ extern "C" int flstm_tc_plan(size_t batch, size_t hidden_size, int training, int
     out->step_bn_bwd = sp.bn_bwd;
     out->step_splits = sp.splits;
     out->step_pair = sp.pair ? 1 : 0;
+    out->step_fwd_pair = sp.fwd_pair ? 1 : 0;
     if (sp.use) return FLSTM_OK;
     tc::FwdPlan f{};
     FLSTM_TRY(tc::plan_fwd((int)batch, (int)hidden_size, sm_count, smem_limit, &f));
     out->fwd_batch_tile = f.BT;
+    out->fwd_pair = f.pair ? 1 : 0;
     out->fwd_row_tiles_per_cta = f.rt;
     out->fwd_grid = f.grid;
     out->fwd_batch_groups = f.ngroups;

@@ -204,6 +204,8 @@ typedef struct {
     /* wide batches run one GEMM launch per time step instead (then the fields above are zero) */
     int step_path, step_bn_fwd, step_bn_bwd, step_splits;
     int step_pair; /* the per-step GEMMs run on CTA pairs (256-sequence tiles, tcgen05 cta_group::2) */
+    int fwd_pair;      /* persistent forward kernel: neighbouring row-tile CTAs form cta_group::2 pairs */
+    int step_fwd_pair; /* wide batches: the all-steps forward kernel runs on CTA pairs (256-sequence tiles) */
 } flstm_tc_plan_info;
 int flstm_tc_plan(size_t batch, size_t hidden_size, int training, int sm_count, size_t smem_limit,
                   flstm_tc_plan_info *out);

@@ -99,11 +99,15 @@ def test_wide_batch_plans(lib):
     Config 5 (B=2048, H=1024): 256-wide forward tiles, no K split."""
     st, p = plan(lib, 256, 2048)
     assert st == 0 and (p.step_path, p.step_bn_fwd, p.step_splits) == (1, 128, 4)
+    assert p.step_fwd_pair == 1  # 256 sequences: the all-steps forward kernel on CTA pairs
     st, p = plan(lib, 2048, 1024)
-    assert st == 0 and (p.step_path, p.step_bn_fwd, p.step_splits) == (1, 256, 1)
+    assert st == 0 and (p.step_path, p.step_bn_fwd, p.step_splits, p.step_fwd_pair) == (1, 256, 1, 1)
     # config 3's 2-GPU shard (B=128): 128-wide forward tiles would leave 84 SMs idle -> 128 tiles of 128 x 64
     st, p = plan(lib, 128, 2048)
-    assert st == 0 and (p.step_path, p.step_bn_fwd, p.step_splits) == (1, 64, 8)
+    assert st == 0 and (p.step_path, p.step_bn_fwd, p.step_splits, p.step_fwd_pair) == (1, 64, 8, 0)
+    # the persistent forward kernel pairs neighbouring row tiles whenever their number is even
+    st, p = plan(lib, 64, 1024)
+    assert st == 0 and (p.step_path, p.fwd_pair, p.fwd_grid) == (0, 1, 128)
 
 
 def test_unsupported_shapes_are_reported(lib):
