@@ -9,7 +9,7 @@ and, at one shape, the v2 forward+backward entry points of both libraries (confi
 FP16, B=64, I=H=1024, T=512, R=1).  No FlashAttention curve and no plot.  Every result is checked against fp32 CPU
 torch.nn.LSTM on a short prefix before it is timed.
 
-    python -m baseline.seq_len_sweep [--out gpurun_out/seq_len_sweep.md] [--lengths 64,192,...]
+    python -m baseline.seq_len_sweep [--out seq_len_sweep.md] [--lengths 64,192,...]
 """
 from __future__ import annotations
 
@@ -46,7 +46,7 @@ def check_v1(lib, name, lstm, B, I, H):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "seq_len_sweep.md"))
+    ap.add_argument("--out", default="seq_len_sweep.md", help="where the table is written (markdown)")
     ap.add_argument("--lengths", default="64,192,448,960,1984,4032,8128")
     ap.add_argument("--iters", type=int, default=7)
     ap.add_argument("--warmup", type=int, default=2)
@@ -147,7 +147,7 @@ def main():
             v2[name] = {"failed": str(exc)[:300]}
         print(json.dumps({name: v2[name]}), flush=True)
 
-    os.makedirs(os.path.dirname(a.out), exist_ok=True)
+    os.makedirs(os.path.dirname(os.path.abspath(a.out)), exist_ok=True)
     cols = [c for c in rows[0] if c != "T"] if rows else []
     with open(a.out, "w") as f:
         f.write("# Sequence-length sweep: B=32, I=H=1024, forward only (ms per call, median of %d)\n\n" % a.iters)

@@ -71,13 +71,20 @@ struct StepArgs {
     int t;             // time step: projection / gate cache and y at slot t, states read at slot t, written at t+1
     int has_y;         // also store h_t into the caller's y
     int store_gates;   // write the activated gates back (the gate cache)
+    int early;         // fetch the first weight blocks ahead of the previous kernel's completion (FLSTM_PDL_EARLY=0: off)
 };
 
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Kernels of the per-step chain start while the previous one drains (programmatic dependent launch); each
-// waits for its predecessor with griddepcontrol.wait before touching global memory.  FLSTM_PDL=0 turns it off.
+// waits for its predecessor with griddepcontrol.wait before touching what that one wrote.  FLSTM_PDL=0 turns it off.
+// FLSTM_PDL_EARLY=0 keeps every global access behind that wait (no weight blocks / forward-pass operands fetched
+// ahead of it).
+bool pdl_early_enabled() {
+    const char *env = std::getenv("FLSTM_PDL_EARLY");
+    return !(env && env[0] == '0');
+}
 bool pdl_enabled() {
     static int on = -1;
     if (on < 0) {
@@ -247,8 +254,10 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     // Launched with programmatic stream serialization: everything above overlapped the tail of the previous
-    // step's kernel; its results (h, c, dG, partial sums) may be touched only from here on.
-    grid_dependency_wait();
+    // step's kernel; its results (h, c, dG, partial sums) may be touched only from here on.  The producer warp
+    // waits a little later: W_hh does not change along the chain, so it first fetches the weight blocks of its
+    // first ring stages.
+    if (warp != 0) grid_dependency_wait();
 
     const int num_m = (a.M + BMT - 1) / BMT, num_n = a.N / BN;
     const int kblocks = a.K / BK, kper = kblocks / a.splits;
@@ -260,14 +269,38 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             int stage = 0;
             uint32_t phase = 0;
             const uint32_t full0 = PAIR ? map_to_rank(smem_u32(full), 0) : 0u;  // the leader's "operands landed" barriers
+            auto load_b_block = [&](uint8_t *sb, int kb, int n0, uint64_t *bar) {  // lone CTAs
+                if (!B_MN) {
+                    tma_load_2d(sb, &tm_b, kb * BK, n0, bar);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tm_b, n0 + j * 64, kb * BK, bar);
+                }
+            };
+            // weight blocks of the first tile's first K blocks, ahead of the previous kernel's completion
+            int npre = 0;
+            if (!PAIR && a.early && worker < tiles) {
+                const int ks = worker / (num_m * num_n), n0 = ((worker % (num_m * num_n)) % num_n) * BN;
+                npre = kper < S::kStages ? kper : S::kStages;
+                for (int b = 0; b < npre; ++b) {
+                    mbar_expect_tx(&full[b], S::kStageBytes);
+                    load_b_block(smem + b * S::kStageBytes + S::kABytes, ks * kper + b, n0, &full[b]);
+                }
+            }
+            grid_dependency_wait();
             for (int tile = worker; tile < tiles; tile += workers) {
                 const int ks = tile / (num_m * num_n), mn = tile % (num_m * num_n);
                 const int m0 = (mn / num_n) * BMT + (int)rank * BM, n0 = (mn % num_n) * BN + (int)rank * BNB;
                 bool ok = true;
                 for (int kb = ks * kper; kb < (ks + 1) * kper && ok; ++kb) {
+                    uint8_t *sa = smem + stage * S::kStageBytes, *sb = sa + S::kABytes;
+                    if (tile == worker && kb - ks * kper < npre) {  // the weights of this stage are already on their way
+                        tma_load_3d(sa, &tm_a, kb * BK, m0, a.a_z, &full[stage]);
+                        if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+                        continue;
+                    }
                     ok = mbar_wait(&empty[stage], phase ^ 1, abort_w);
                     if (!ok) break;
-                    uint8_t *sa = smem + stage * S::kStageBytes, *sb = sa + S::kABytes;
                     if (PAIR) {
                         // each CTA fetches its own halves; the bytes of both are counted on the leader's barrier
                         const uint32_t bar = full0 + 8u * (uint32_t)stage;
@@ -282,12 +315,7 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     } else {
                         mbar_expect_tx(&full[stage], S::kStageBytes);
                         tma_load_3d(sa, &tm_a, kb * BK, m0, a.a_z, &full[stage]);
-                        if (!B_MN) {
-                            tma_load_2d(sb, &tm_b, kb * BK, n0, &full[stage]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tm_b, n0 + j * 64, kb * BK, &full[stage]);
-                        }
+                        load_b_block(sb, kb, n0, &full[stage]);
                     }
                     if (++stage == S::kStages) { stage = 0; phase ^= 1; }
                 }
@@ -771,10 +799,13 @@ __global__ void __launch_bounds__(256)
 step_bwd_pointwise_kernel(const uint16_t *__restrict__ gates_t, const float *__restrict__ c_t,
                           const float *__restrict__ c_prev, const uint16_t *__restrict__ dy_t,
                           const float *__restrict__ parts, int nparts, float *__restrict__ dc,
-                          uint16_t *__restrict__ dg_t, int B, int H) {
+                          uint16_t *__restrict__ dg_t, int B, int H, int early) {
     const int quads = H >> 2;
     const size_t total = (size_t)B * quads, slab = (size_t)B * H;
-    grid_dependency_wait();
+    // The split-K GEMM that follows may start its prologue and fetch its first weight blocks while this kernel
+    // runs; it waits for this whole grid before it touches dG_t.
+    if (early) grid_launch_dependents();
+    else grid_dependency_wait();
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int b = (int)(i / quads), U0 = (int)(i % quads) * 4;
         const size_t sidx = (size_t)b * H + U0;
@@ -794,6 +825,9 @@ step_bwd_pointwise_kernel(const uint16_t *__restrict__ gates_t, const float *__r
         }
         const float4 ctv = *reinterpret_cast<const float4 *>(c_t + sidx);
         const float4 cpv = *reinterpret_cast<const float4 *>(c_prev + sidx);
+        // everything above was written by the forward pass; the partial sums and the cell-gradient carry come from
+        // the kernels right before this one in the chain
+        if (early) grid_dependency_wait();
         const float4 dcv4 = *reinterpret_cast<const float4 *>(dc + sidx);
         const float ct[4] = {ctv.x, ctv.y, ctv.z, ctv.w}, cp[4] = {cpv.x, cpv.y, cpv.z, cpv.w};
         const float dcin[4] = {dcv4.x, dcv4.y, dcv4.z, dcv4.w};
@@ -942,6 +976,7 @@ int lstm_step_forward(int dtype, const StepPlan &plan, const StepFwdMaps &m, con
                       cudaStream_t s) {
     const bool bf16 = dtype == FLSTM_DTYPE_BF16;
     StepArgs a{};
+    a.early = pdl_early_enabled() ? 1 : 0;
     a.M = p.B;
     a.N = 4 * p.H;
     a.K = p.H;
@@ -1020,6 +1055,7 @@ int lstm_step_backward_gemm(int dtype, const StepPlan &plan, const CUtensorMap &
                             int B, int H, float *parts, unsigned int *err, int sms, cudaStream_t s) {
     const bool bf16 = dtype == FLSTM_DTYPE_BF16;
     StepArgs a{};
+    a.early = pdl_early_enabled() ? 1 : 0;
     a.M = B;
     a.N = H;
     a.K = 4 * H;
@@ -1041,8 +1077,8 @@ int lstm_step_backward_pointwise(int dtype, const void *gates_t, const float *c_
     const uint16_t *g16 = static_cast<const uint16_t *>(gates_t), *dy16 = static_cast<const uint16_t *>(dy_t);
     uint16_t *dg16 = static_cast<uint16_t *>(dg_t);
     cudaError_t e = dtype == FLSTM_DTYPE_BF16
-                        ? launch_chained(step_bwd_pointwise_kernel<true>, grid, 256, 0, s, 1, g16, c_t, c_prev, dy16, parts, nparts, dc, dg16, B, H)
-                        : launch_chained(step_bwd_pointwise_kernel<false>, grid, 256, 0, s, 1, g16, c_t, c_prev, dy16, parts, nparts, dc, dg16, B, H);
+                        ? launch_chained(step_bwd_pointwise_kernel<true>, grid, 256, 0, s, 1, g16, c_t, c_prev, dy16, parts, nparts, dc, dg16, B, H, pdl_early_enabled() ? 1 : 0)
+                        : launch_chained(step_bwd_pointwise_kernel<false>, grid, 256, 0, s, 1, g16, c_t, c_prev, dy16, parts, nparts, dc, dg16, B, H, pdl_early_enabled() ? 1 : 0);
     if (e != cudaSuccess) return set_error(FLSTM_ERR_CUDA, "step pointwise launch failed: %s", cudaGetErrorString(e));
     return FLSTM_OK;
 }
