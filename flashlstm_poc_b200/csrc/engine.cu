@@ -97,6 +97,17 @@ Engine::~Engine() {
     if (comm_stream) cudaStreamDestroy(comm_stream);
     if (comm_fork) cudaEventDestroy(comm_fork);
     if (comm_join) cudaEventDestroy(comm_join);
+    if (aux_stream) cudaStreamDestroy(aux_stream);
+    if (aux_fork) cudaEventDestroy(aux_fork);
+    if (aux_join) cudaEventDestroy(aux_join);
+}
+
+int Engine::ensure_aux_stream() {
+    if (aux_stream) return FLSTM_OK;
+    FLSTM_CUDA_TRY(cudaStreamCreateWithFlags(&aux_stream, cudaStreamNonBlocking));
+    FLSTM_CUDA_TRY(cudaEventCreateWithFlags(&aux_fork, cudaEventDisableTiming));
+    FLSTM_CUDA_TRY(cudaEventCreateWithFlags(&aux_join, cudaEventDisableTiming));
+    return FLSTM_OK;
 }
 
 int Engine::reduce_grads(size_t offset, size_t count, cudaStream_t from) {

@@ -90,6 +90,11 @@ struct Engine {
     bool comm_aborted = false;  // the watchdog gave up on a step: no collective until a new communicator is attached
     cudaStream_t comm_stream = nullptr;
     cudaEvent_t comm_fork = nullptr, comm_join = nullptr;
+    // second compute stream (created on first use): the two weight-gradient GEMMs of a layer run side by side on
+    // disjoint halves of the SMs when that saves a round of tiles
+    cudaStream_t aux_stream = nullptr;
+    cudaEvent_t aux_fork = nullptr, aux_join = nullptr;
+    int ensure_aux_stream();
     long long *trace = nullptr;  // device: [2 (fwd,bwd)][trace_steps][16] clock stamps of CTA 0
     int trace_steps = 0;
     void *tc_state = nullptr;  // tensor-core path: cached tensor maps etc. (tc_engine.cu)

@@ -6,6 +6,7 @@
 //     index(g, u) = ((u / 16) * 4 + g) * 16 + u % 16
 // so that the 64 rows a recurrent CTA owns are the four gates of 16 hidden units.  Weight and bias
 // gradients are written back in torch order (g*H + u) by the GEMM epilogue / a small kernel.
+#include <algorithm>
 #include <cstdlib>
 #include <vector>
 
@@ -414,11 +415,39 @@ int backward_layer(Engine &e, int li, size_t T, size_t t0, size_t t1, const void
         const size_t steps = e.seg.active ? n : T;
         const bool acc = e.seg.active && !e.seg.first_segment, last = !e.seg.active || e.seg.final_segment;
         const size_t n_ih = 4 * H * l.in_size;
-        FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, l.in_size, steps * B, l.dg, 4 * H, true, x_l, l.in_size, true,
-                       l.dw_ih, l.in_size, nullptr, (int)H, err, st->sms, s, acc));
-        if (last) FLSTM_TRY(e.reduce_grads(l.grad_offset, n_ih, s));
-        FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, H, steps * B, l.dg, 4 * H, true, l.hs, H, true, l.dw_hh, H, nullptr,
-                       (int)H, err, st->sms, s, acc));
+        // Opt-in (FLSTM_DW_SIDE_BY_SIDE=1, without a communicator): the two GEMMs run SIDE BY SIDE, each on its share of
+        // the SMs.  Their 128 x 256 tiles run for milliseconds (K = T*B), so a last, partly filled round of tiles is
+        // expensive -- config 3: 512 tiles each, 4 + 4 rounds on 148 SMs one after the other, 7 rounds on 74 + 74 SMs.
+        // Measured: the phase drops from 27.7 to 26.0 ms, the whole step does not (122.2 against 120.7 ms): the board
+        // is at its power cap in this phase, and SMs that idle through a partial round let the others clock higher.
+        const size_t tiles_ih = ((4 * H + 127) / 128) * ((l.in_size + 255) / 256), tiles_hh = ((4 * H + 127) / 128) * ((H + 255) / 256);
+        int sms_ih = (int)((size_t)st->sms * tiles_ih / (tiles_ih + tiles_hh));
+        if (sms_ih < 1) sms_ih = 1;
+        if (sms_ih > st->sms - 1) sms_ih = st->sms - 1;
+        const int sms_hh = st->sms - sms_ih;
+        auto rounds = [](size_t tiles, int sms) { return (tiles + sms - 1) / sms; };
+        const size_t seq_rounds = rounds(tiles_ih, st->sms) + rounds(tiles_hh, st->sms);
+        // a round = the time of one tile, whatever the number of CTAs working
+        const size_t par_rounds = std::max(rounds(tiles_ih, sms_ih), rounds(tiles_hh, sms_hh));
+        const char *sbs = std::getenv("FLSTM_DW_SIDE_BY_SIDE");
+        const bool side_by_side = !e.comm && st->sms >= 2 && sbs && sbs[0] == '1' && par_rounds < seq_rounds;
+        if (side_by_side) {
+            FLSTM_TRY(e.ensure_aux_stream());
+            FLSTM_CUDA_TRY(cudaEventRecord(e.aux_fork, s));
+            FLSTM_CUDA_TRY(cudaStreamWaitEvent(e.aux_stream, e.aux_fork, 0));
+            FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, H, steps * B, l.dg, 4 * H, true, l.hs, H, true, l.dw_hh, H,
+                           nullptr, (int)H, err, sms_hh, e.aux_stream, acc));
+            FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, l.in_size, steps * B, l.dg, 4 * H, true, x_l, l.in_size, true,
+                           l.dw_ih, l.in_size, nullptr, (int)H, err, sms_ih, s, acc));
+            FLSTM_CUDA_TRY(cudaEventRecord(e.aux_join, e.aux_stream));
+            FLSTM_CUDA_TRY(cudaStreamWaitEvent(s, e.aux_join, 0));
+        } else {
+            FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, l.in_size, steps * B, l.dg, 4 * H, true, x_l, l.in_size, true,
+                           l.dw_ih, l.in_size, nullptr, (int)H, err, st->sms, s, acc));
+            if (last) FLSTM_TRY(e.reduce_grads(l.grad_offset, n_ih, s));
+            FLSTM_TRY(gemm(e.cfg.dtype, FLSTM_DTYPE_F32, 4 * H, H, steps * B, l.dg, 4 * H, true, l.hs, H, true, l.dw_hh, H,
+                           nullptr, (int)H, err, st->sms, s, acc));
+        }
         FLSTM_TRY(simt::column_sum_two_pass(e.cfg.dtype, l.dg, steps * B, 4 * H,
                                             e.db_part + (size_t)li * simt::column_sum_scratch_floats(4 * H), l.db, (int)H, s,
                                             acc));

@@ -104,6 +104,17 @@ def test_wide_and_large_batch_regimes(dtype, L, T, B, I, H, training, path, monk
     eng.close()
 
 
+def test_weight_gradient_gemms_side_by_side(monkeypatch):
+    """FLSTM_DW_SIDE_BY_SIDE=1: dW_ih and dW_hh of a layer are computed at the same time on two streams, each GEMM on
+    its share of the SMs; same results as one after the other."""
+    monkeypatch.setenv("FLSTM_DW_SIDE_BY_SIDE", "1")
+    w = Workload("t", "bf16", 2, 256, 256, 32, 6, seed=5, state_std=0.2)
+    inp = make_inputs(w)
+    got, eng = run_engine(w, inp, backend="tc", repeat=2)
+    assert_parity(got, run_oracle(inp), "bf16")
+    eng.close()
+
+
 def test_repeatable_and_cache_layout():
     """Two runs give bit-identical results (a race in a persistent kernel's barrier would not), and
     the gate cache read back in torch order matches the oracle's activations."""
