@@ -113,6 +113,7 @@ struct StepPlan {
     int bn_bwd;   // output-tile width of the backward step GEMM (hidden units): 128 or 256
     int splits;   // K = 4H splits of the backward step GEMM (fp32 partial sums, added by the pointwise kernel)
     bool pair;    // tiles of 256 sequences on CTA pairs (cta_group::2); the forward W_hh map then has bn_fwd / 2 rows per box
+    bool bwd_pair;        // the backward split-K GEMM runs on CTA pairs (256-sequence tiles)
     bool fwd_persistent;  // forward: one cooperative launch per range of steps (lstm_wide_forward) instead of one per step
     bool fwd_pair;        // that launch runs on CTA pairs (256-sequence tiles); the forward W_hh map has bn_fwd / 2 rows per box
 };

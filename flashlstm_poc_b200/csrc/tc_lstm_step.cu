@@ -279,12 +279,25 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             };
             // weight blocks of the first tile's first K blocks, ahead of the previous kernel's completion
             int npre = 0;
-            if (!PAIR && a.early && worker < tiles) {
-                const int ks = worker / (num_m * num_n), n0 = ((worker % (num_m * num_n)) % num_n) * BN;
+            if (a.early && worker < tiles) {
+                const int ks = worker / (num_m * num_n), n0 = ((worker % (num_m * num_n)) % num_n) * BN + (int)rank * BNB;
                 npre = kper < S::kStages ? kper : S::kStages;
                 for (int b = 0; b < npre; ++b) {
-                    mbar_expect_tx(&full[b], S::kStageBytes);
-                    load_b_block(smem + b * S::kStageBytes + S::kABytes, ks * kper + b, n0, &full[b]);
+                    uint8_t *sb = smem + b * S::kStageBytes + S::kABytes;
+                    const int kb = ks * kper + b;
+                    if (PAIR) {
+                        const uint32_t bar = full0 + 8u * (uint32_t)b;
+                        if (leader) mbar_expect_tx(&full[b], 2 * S::kStageBytes);
+                        if (!B_MN) {
+                            tma_load_2d_pair(sb, &tm_b, kb * BK, n0, bar);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < BNB / 64; ++j) tma_load_2d_pair(sb + j * 8192, &tm_b, n0 + j * 64, kb * BK, bar);
+                        }
+                    } else {
+                        mbar_expect_tx(&full[b], S::kStageBytes);
+                        load_b_block(sb, kb, n0, &full[b]);
+                    }
                 }
             }
             grid_dependency_wait();
@@ -295,7 +308,8 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 for (int kb = ks * kper; kb < (ks + 1) * kper && ok; ++kb) {
                     uint8_t *sa = smem + stage * S::kStageBytes, *sb = sa + S::kABytes;
                     if (tile == worker && kb - ks * kper < npre) {  // the weights of this stage are already on their way
-                        tma_load_3d(sa, &tm_a, kb * BK, m0, a.a_z, &full[stage]);
+                        if (PAIR) tma_load_3d_pair(sa, &tm_a, kb * BK, m0, a.a_z, full0 + 8u * (uint32_t)stage);
+                        else tma_load_3d(sa, &tm_a, kb * BK, m0, a.a_z, &full[stage]);
                         if (++stage == S::kStages) { stage = 0; phase ^= 1; }
                         continue;
                     }
@@ -368,7 +382,7 @@ step_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         const uint32_t tempty0 = PAIR ? map_to_rank(smem_u32(tempty), 0) : 0u;
         // this warp is done with accumulator `b`: tell the UMMA issuer (in a pair: the leader's barrier)
         auto release_accumulator = [&](int b) {
-            if (PAIR) mbar_arrive_cluster(tempty0 + 8u * (uint32_t)b);
+            if (PAIR) mbar_arrive_cluster_relaxed(tempty0 + 8u * (uint32_t)b);
             else mbar_arrive(&tempty[b]);
         };
         if (EPI == EPI_LSTM_FWD) {
@@ -936,24 +950,31 @@ int plan_step(int B, int H, int sms, size_t smem_limit, StepPlan *plan) {
     plan->use = use && H % 128 == 0;  // the backward tiles are 128 or 256 units wide
     // from 256 sequences on a tile is 256 rows on a CTA pair (cta_group::2)
     plan->pair = B >= 2 * BM && sms >= 2 && step_pair_enabled();
-    const int rows = plan->pair ? 2 * BM : BM, workers = plan->pair ? sms / 2 : sms;
+    // FLSTM_STEP_BWD_PAIR=1: only the backward split-K GEMM on CTA pairs (the forward keeps its all-steps kernel)
+    const char *bp = std::getenv("FLSTM_STEP_BWD_PAIR");
+    plan->bwd_pair = plan->pair || (B >= 2 * BM && sms >= 2 && bp && bp[0] == '1');
+    const int rows = plan->pair ? 2 * BM : BM;
     const int m_tiles = (B + rows - 1) / rows;
     plan->bn_fwd = pick_bn(m_tiles, 4 * H, 1, sms, plan->pair, true);
     // backward: K = 4H is long and N = H short; split K until the tiles fill the machine
+    const int rows_b = plan->bwd_pair ? 2 * BM : BM, workers_b = plan->bwd_pair ? sms / 2 : sms;
+    const int m_tiles_b = (B + rows_b - 1) / rows_b;
     int splits = 1;
-    while (splits < 8 && m_tiles * (H / 128) * splits * 2 <= workers && ((4 * H / BK) % (splits * 2)) == 0) splits *= 2;
+    while (splits < 8 && m_tiles_b * (H / 128) * splits * 2 <= workers_b && ((4 * H / BK) % (splits * 2)) == 0) splits *= 2;
     plan->splits = splits;
-    plan->bn_bwd = pick_bn(m_tiles, H, splits, sms, plan->pair);
+    plan->bn_bwd = pick_bn(m_tiles_b, H, splits, sms, plan->bwd_pair);
     size_t need_fwd, need_bwd;
     if (plan->pair) {
         need_fwd = plan->bn_fwd == 256 ? StepShape<256, EPI_LSTM_FWD, true>::kSmemBytes : StepShape<128, EPI_LSTM_FWD, true>::kSmemBytes;
-        need_bwd = plan->bn_bwd == 256 ? StepShape<256, EPI_F32_PARTS, true>::kSmemBytes : StepShape<128, EPI_F32_PARTS, true>::kSmemBytes;
     } else {
         need_fwd = plan->bn_fwd == 256 ? StepShape<256, EPI_LSTM_FWD, false>::kSmemBytes
                    : plan->bn_fwd == 128 ? StepShape<128, EPI_LSTM_FWD, false>::kSmemBytes
                                          : StepShape<64, EPI_LSTM_FWD, false>::kSmemBytes;
-        need_bwd = plan->bn_bwd == 256 ? StepShape<256, EPI_F32_PARTS, false>::kSmemBytes : StepShape<128, EPI_F32_PARTS, false>::kSmemBytes;
     }
+    if (plan->bwd_pair)
+        need_bwd = plan->bn_bwd == 256 ? StepShape<256, EPI_F32_PARTS, true>::kSmemBytes : StepShape<128, EPI_F32_PARTS, true>::kSmemBytes;
+    else
+        need_bwd = plan->bn_bwd == 256 ? StepShape<256, EPI_F32_PARTS, false>::kSmemBytes : StepShape<128, EPI_F32_PARTS, false>::kSmemBytes;
     if (need_fwd > smem_limit || need_bwd > smem_limit) plan->use = false;  // the step kernels do not fit this device
     // forward: all steps of a range in one cooperative launch; FLSTM_WIDE_PERSIST=0 = one launch per step
     const char *wp = std::getenv("FLSTM_WIDE_PERSIST");
@@ -1061,12 +1082,12 @@ int lstm_step_backward_gemm(int dtype, const StepPlan &plan, const CUtensorMap &
     a.K = 4 * H;
     a.a_z = t;
     a.splits = plan.splits;
-    a.idesc = umma_idesc_f16(plan.pair ? 2 * BM : BM, plan.bn_bwd, bf16 ? 1 : 0, 0, 1);
+    a.idesc = umma_idesc_f16(plan.bwd_pair ? 2 * BM : BM, plan.bn_bwd, bf16 ? 1 : 0, 0, 1);
     a.err = err;
     a.parts = parts;
     const EpilogueMaps em{&tm_dg, &tm_dg, &tm_dg, &tm_dg};  // unused by this epilogue
-    if (plan.bn_bwd == 256) return launch_step<256, EPI_F32_PARTS, true, false>(plan.pair, tm_dg, tm_w64, em, a, sms, s);
-    return launch_step<128, EPI_F32_PARTS, true, false>(plan.pair, tm_dg, tm_w64, em, a, sms, s);
+    if (plan.bn_bwd == 256) return launch_step<256, EPI_F32_PARTS, true, false>(plan.bwd_pair, tm_dg, tm_w64, em, a, sms, s);
+    return launch_step<128, EPI_F32_PARTS, true, false>(plan.bwd_pair, tm_dg, tm_w64, em, a, sms, s);
 }
 
 int lstm_step_backward_pointwise(int dtype, const void *gates_t, const float *c_t, const float *c_prev, const void *dy_t,
