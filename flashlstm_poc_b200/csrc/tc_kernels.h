@@ -23,7 +23,7 @@ int device_sm_count();
 
 // ------------------------------------------------------------------ persistent recurrent forward
 struct FwdPlan {
-    int BT;        // sequences per batch tile (UMMA N): 32 or 64
+    int BT;        // sequences per batch tile (UMMA N): 32, 64 or 128
     int rt;        // row tiles (64 gate rows = 16 hidden units x 4 gates) per CTA
     int cta_rows;  // CTAs along the row-tile axis = (H/16) / rt
     int ngroups;   // batch groups (each with its own step barrier)

@@ -2,13 +2,16 @@
 //
 // Work split.  The 4H gate rows are stored tile-interleaved: row tile j (64 rows) holds the four
 // gates i,f,g,o of hidden units [16j, 16j+16).  A CTA owns `rt` consecutive row tiles and a group
-// of batch tiles (BT = 32 or 64 sequences each); its slice of W_hh stays in shared memory for the
-// whole sequence when it fits (W_RESIDENT), otherwise it is streamed through the TMA ring from L2.
+// of batch tiles (BT = 32, 64 or 128 sequences each); its slice of W_hh stays in shared memory for the
+// whole sequence when it fits (W_RESIDENT), otherwise it is streamed through the TMA ring from L2 (the chunks of a
+// step's first ring stages ahead of the step barrier).  Neighbouring row-tile CTAs normally work as a CTA PAIR
+// (template parameter PAIR, see the kernel): one UMMA of M = 128 over both, each CTA staging half of the h tile.
 //
 // Per step and (row tile, batch tile):
 //   producer warp : TMA-loads the P_t tile (input projection + bias, 16-bit), waits on the grid
 //                   barrier for h_{t-1}, then streams h_{t-1} (BT x 64 chunks) through the ring
-//   MMA warp      : tcgen05.mma M=64 (gate rows) x N=BT (batch) x K=16, accumulating over K = H into TMEM
+//   MMA warp      : tcgen05.mma M=64 (gate rows; M=128 over a pair) x N=BT (batch) x K=16, accumulating over K = H
+//                   into TMEM
 //   4 epilogue warps: tcgen05.ld -> exchange through shared memory so that one thread sees all four
 //                   gate sums of its (unit, sequence) pair -> + P_t -> sigmoid/tanh -> c_t (fp32),
 //                   h_t (16-bit).  h_t is stored and published first; the cell state and the activated
@@ -21,7 +24,8 @@
 //   * the 256 epilogue threads never leave between their waits and the named barrier that follows: the barrier
 //     ORs "my wait failed" over all of them (barrier.cta.red.or), so they continue or break TOGETHER and nobody is
 //     left at a bar.sync; no wait lies between that barrier and the release barrier of the same step;
-//   * all 320 threads meet at the final __syncthreads, after which the tensor memory is freed.
+//   * all 320 threads meet at the final __syncthreads (a pair also at a final barrier.cluster, which each CTA reaches
+//     on its own once its bounded waits have returned), after which the tensor memory is freed.
 // Other CTAs learn of an abort through the global error word, which their counter polls read.
 //
 // Replaces, per step, the reference's ScaleAndPackColumnsKernel + GemmTN + ForwardPointwiseKernel

@@ -988,7 +988,10 @@ int plan_step(int B, int H, int sms, size_t smem_limit, StepPlan *plan) {
     if (plan->fwd_pair) {
         plan->bn_fwd = pick_bn((B + 2 * BM - 1) / (2 * BM), 4 * H, 1, sms, true);
         const size_t need = plan->bn_fwd == 256 ? StepShape<256, EPI_LSTM_FWD, true>::kSmemBytes : StepShape<128, EPI_LSTM_FWD, true>::kSmemBytes;
-        if (need > smem_limit) plan->fwd_pair = false, plan->bn_fwd = pick_bn(m_tiles, 4 * H, 1, sms, plan->pair, true);
+        if (need > smem_limit) {
+            plan->fwd_pair = false;
+            plan->bn_fwd = pick_bn(m_tiles, 4 * H, 1, sms, plan->pair, true);
+        }
     }
     return FLSTM_OK;
 }
